@@ -1,0 +1,454 @@
+#!/usr/bin/env python
+"""Benchmark of the Q8_0 hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload (BASELINE.json configs[2], the shape the target is quoted on):
+the lm_head GEMV, 151936 rows x K=2560, Q8_0 weights ~N(0, 0.02), fp32
+activation ~N(0, 1), batch 1.  A step is one full matvec.  The metric is
+weight-GB/s: rows * (K/32) * 34 bytes per step, over the device time of the
+step.  With N > 1 the rows are split evenly over the ranks (fixed total work:
+strong scaling) and every step ends with the all-gather of the fp32 logits.
+
+One JSON line is printed by rank 0.  Beside the contract keys it carries
+`roofline` (the GEMV kernel against measured HBM bandwidth), `cpu_baseline` (the
+reference's own CPU matvec on this host), `e2e` (the same step through the
+host-buffer entry point with pinned buffers) and `mmq` (the batched prefill
+product at M=512, K=2560, N=9728 in int8 TOPS).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+ROWS, WIDTH = 151936, 2560
+BLOCKS = WIDTH // 32
+WEIGHT_BYTES = ROWS * BLOCKS * 34
+MMQ_M, MMQ_K, MMQ_N = 512, 2560, 9728
+FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMV launch, from the ncu
+# capture summarised in profiles/ (None until a capture exists)
+GEMV_DRAM_TRAFFIC_BYTES = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": FALLBACK_HBM_GBS}, "fallback"
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.samples = []
+        self.proc = None
+        self.device_index = device_index
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.device_index), "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.time(), line.strip()))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, t0: float, t1: float):
+        rows = [s for (t, s) in self.samples if t0 <= t <= t1 + 0.06] or [s for (_, s) in self.samples]
+        sm, smax, reasons = [], [], set()
+        for row in rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                    "sw_power_cap"), parts[5:9]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)),
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------ reference arm
+def reference_library():
+    from oracle import q8_oracle as o
+    o.build()
+    if o.Reference.available(fast=True):
+        return o, o.Reference(fast=True), "reference"
+    return o, None, "port"
+
+
+def time_cpu_matvec(o, ref, weights, rows, x, repeats):
+    """Seconds for `repeats` matvecs of the first `rows` rows on all host threads."""
+    if ref is not None:
+        t = time.perf_counter()
+        ref.matvec_repeat(weights, rows, WIDTH, x, repeats)
+        return time.perf_counter() - t
+    t = time.perf_counter()
+    for _ in range(repeats):
+        o.matvec(weights, rows, WIDTH, x)
+    return time.perf_counter() - t
+
+
+def cpu_baseline_block(weights_host, x, budget_s=12.0):
+    """The reference's CPU matvec (oracle/_ref, its own C arithmetic compiled with its
+    native-profile flags) on a bounded sample of the same workload."""
+    o, ref, kind = reference_library()
+    threads = ref.thread_count() if ref is not None else o.thread_count()
+    w = np.ascontiguousarray(weights_host).view(np.int8).reshape(-1)
+    time_cpu_matvec(o, ref, w, ROWS, x, 1)                       # warm
+    once = time_cpu_matvec(o, ref, w, ROWS, x, 2) / 2
+    repeats = int(max(3, min(2000, budget_s / max(once, 1e-6))))
+    seconds = time_cpu_matvec(o, ref, w, ROWS, x, repeats)
+    value = WEIGHT_BYTES * repeats / seconds / 1e9
+    return {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
+            "sample": f"{repeats} repeats of the full {ROWS}x{WIDTH} matvec, "
+                      f"{seconds:.1f} s, OMP threads={threads}, "
+                      f"avx2={'yes' if (ref is None or ref.uses_avx2()) else 'no'}",
+            "ms_per_matvec": seconds / repeats * 1e3}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    o, ref, kind = reference_library()
+    threads = ref.thread_count() if ref is not None else o.thread_count()
+    weights = o.make_weights(ROWS, WIDTH, seed=0, sigma=0.02)
+    x = o.normal(WIDTH, seed=1)
+    time_cpu_matvec(o, ref, weights, ROWS, x, 1)
+    full = time_cpu_matvec(o, ref, weights, ROWS, x, 2) / 2
+    # bound the whole run to about two minutes: a step is the matvec of the first
+    # `rows` rows (all of them when that fits)
+    budget = 120.0
+    total_steps = max(1, args.steps + args.warmup)
+    rows = ROWS
+    if full * total_steps > budget:
+        rows = int(max(1024, min(ROWS, ROWS * budget / (full * total_steps))))
+    time_cpu_matvec(o, ref, weights, rows, x, max(1, args.warmup))
+    seconds = time_cpu_matvec(o, ref, weights, rows, x, args.steps)
+    sample_bytes = rows * BLOCKS * 34
+    value = sample_bytes * args.steps / seconds / 1e9
+    sample = (f"each step = matvec of the first {rows} of {ROWS} rows x {WIDTH} "
+              f"({sample_bytes} weight bytes), OMP threads={threads}")
+    line = {
+        "impl": "reference", "metric": "q8_0_gemv_weight_bandwidth", "value": value,
+        "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": seconds / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 scales",
+        "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(n_gpus):
+    return {
+        "workload": f"lm_head Q8_0 GEMV {ROWS}x{WIDTH} batch 1 (BASELINE configs[2])",
+        "rows": ROWS, "width": WIDTH, "weight_bytes": WEIGHT_BYTES,
+        "sharding": "none" if n_gpus == 1 else f"rows/{n_gpus} per rank + all-gather of fp32 logits",
+        "cache": "inputs larger than L2 (413 MB of weights per step, L2 is 126 MB)",
+        "inputs": "weights ~N(0,0.02) quantized to Q8_0 on the device, activation ~N(0,1), seed 0",
+    }
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def make_device_weights(torch, backend, ctx, first_row, rows, width, seed):
+    """Q8_0 bytes (GGUF order, host numpy) of rows [first_row, first_row+rows) of a
+    seeded N(0, 0.02) matrix; sampled and quantized on the device."""
+    out = np.empty(rows * (width // 32) * 34, dtype=np.int8)
+    chunk = 16384
+    done = 0
+    while done < rows:
+        n = min(chunk, rows - done)
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(seed * 1000003 + first_row + done)
+        values = torch.randn(n, width, generator=gen, device="cuda", dtype=torch.float32) * 0.02
+        q = torch.empty(n * (width // 32) * 34, dtype=torch.int8, device="cuda")
+        torch.cuda.current_stream().synchronize()
+        stat = backend.cuda_q8_quantize_device(ctx, values.data_ptr(), values.numel(),
+                                               q.data_ptr(), q.numel())
+        if not stat.is_ok():
+            raise RuntimeError(f"device quantize failed: {stat}")
+        ctx.synchronize()
+        out[done * (width // 32) * 34:(done + n) * (width // 32) * 34] = q.cpu().numpy()
+        done += n
+    return out
+
+
+def run_gpu_arm(args):
+    import torch
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    from fortai_b200 import backend_cuda as backend
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    stream = torch.cuda.current_stream()
+
+    ctx = backend.cuda_q8_context_t()
+    stat = ctx.create(local_rank, stream=stream.cuda_stream)
+    if not stat.is_ok():
+        raise SystemExit(f"context creation failed: {stat}")
+
+    # ---- this rank's shard of the lm_head
+    base, extra = divmod(ROWS, world)
+    counts = [base + (1 if r < extra else 0) for r in range(world)]
+    first_row = sum(counts[:rank])
+    my_rows = counts[rank]
+    host_weights = make_device_weights(torch, backend, ctx, first_row, my_rows, WIDTH, seed=0)
+    weights = backend.cuda_q8_weights_t()
+    stat = weights.upload(ctx, host_weights, host_weights.size, my_rows, WIDTH)
+    if not stat.is_ok():
+        raise SystemExit(f"weight upload failed: {stat}")
+
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    x = torch.randn(WIDTH, generator=gen, device="cuda", dtype=torch.float32)
+    logits = torch.empty(ROWS, device="cuda", dtype=torch.float32)
+    equal_split = extra == 0
+    my_slice = logits[first_row:first_row + my_rows]
+    pieces = [logits[sum(counts[:r]):sum(counts[:r]) + counts[r]] for r in range(world)]
+
+    def step():
+        stat = backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH,
+                                                 my_slice.data_ptr(), my_rows)
+        if not stat.is_ok():
+            raise RuntimeError(f"matvec failed: {stat}")
+        if world > 1:
+            if equal_split:
+                dist.all_gather_into_tensor(logits, my_slice)
+            else:
+                dist.all_gather(pieces, my_slice)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    launches_before = ctx.launch_count()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    start.record(stream)
+    for _ in range(args.steps):
+        step()
+    stop.record(stream)
+    barrier()
+    t1 = time.time()
+    launches = ctx.launch_count() - launches_before
+    elapsed_ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    stat = ctx.synchronize()
+    if not stat.is_ok():
+        raise SystemExit(f"device reported: {stat}")
+
+    # ---- kernel alone on this rank (no collective), for the roofline
+    for _ in range(3):
+        backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH, my_slice.data_ptr(),
+                                          my_rows)
+    torch.cuda.synchronize()
+    k_iters = max(20, min(args.steps, 2000))
+    start.record(stream)
+    for _ in range(k_iters):
+        backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH, my_slice.data_ptr(),
+                                          my_rows)
+    stop.record(stream)
+    torch.cuda.synchronize()
+    kernel_ms = start.elapsed_time(stop) / k_iters
+
+    # ---- end to end through the host-buffer entry point, pinned buffers
+    host_x = torch.empty(WIDTH, dtype=torch.float32).pin_memory()
+    host_x.copy_(x.cpu())
+    host_out = torch.empty(my_rows, dtype=torch.float32).pin_memory()
+    hx, ho = host_x.numpy(), host_out.numpy()
+    e2e_steps = max(10, min(args.steps, 500))
+    for _ in range(3):
+        backend.cuda_q8_matvec_host_f32(ctx, weights, hx, ho)
+    barrier()
+    te = time.perf_counter()
+    for _ in range(e2e_steps):
+        _, stat = backend.cuda_q8_matvec_host_f32(ctx, weights, hx, ho)
+        if world > 1:
+            my_slice.copy_(host_out, non_blocking=True)
+            if equal_split:
+                dist.all_gather_into_tensor(logits, my_slice)
+            else:
+                dist.all_gather(pieces, my_slice)
+            torch.cuda.synchronize()
+    barrier()
+    e2e_s = time.perf_counter() - te
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    if rank == 0:
+        sampler.stop()
+
+    # ---- prefill product at M=512 (rank 0, single GPU run only)
+    mmq = None
+    if world == 1:
+        mmq = bench_mmq(torch, backend, ctx)
+
+    if rank != 0:
+        ctx_cleanup(weights, ctx, dist)
+        return 0
+
+    peaks, peak_kind = measured_peaks()
+    hbm_peak = float(peaks.get("hbm_gbs", FALLBACK_HBM_GBS))
+    ms_per_step = elapsed_ms / args.steps
+    value = WEIGHT_BYTES / (ms_per_step * 1e-3) / 1e9
+    shard_bytes = my_rows * BLOCKS * 34
+    achieved = shard_bytes / (kernel_ms * 1e-3) / 1e9
+    line = {
+        "metric": "q8_0_gemv_weight_bandwidth", "value": value, "unit": "GB/s",
+        "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 scales", "data": "synthetic",
+        "config": workload_config(world),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": achieved / hbm_peak, "traffic": GEMV_DRAM_TRAFFIC_BYTES,
+                     "peak_source": f"of {peak_kind}",
+                     "kernel": "q8_gemv (quantize prologue + streaming dot), this rank's shard",
+                     "kernel_ms": kernel_ms, "algorithmic_bytes": shard_bytes,
+                     "frac_of_8TBs_nominal": achieved / 8000.0},
+        "e2e": {"value": WEIGHT_BYTES * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
+                "h2d_bytes_per_step": WIDTH * 4, "d2h_bytes_per_step": my_rows * 4,
+                "ms_per_step": e2e_s / e2e_steps * 1e3,
+                "api": "fortai_cuda_q8_matvec_host_f32 (pinned host buffers)"},
+        "gpu_launches": int(launches),
+        "clocks": sampler.summary(t0, t1),
+    }
+    if mmq is not None:
+        line["mmq"] = mmq
+    if world == 1:
+        xs = x.cpu().numpy()
+        line["cpu_baseline"] = cpu_baseline_block(host_weights, xs)
+    print(json.dumps(line), flush=True)
+    ctx_cleanup(weights, ctx, dist)
+    return 0
+
+
+def bench_mmq(torch, backend, ctx):
+    """Batched prefill product, M=512 x K=2560 x N=9728 (BASELINE configs[3])."""
+    host_weights = make_device_weights(torch, backend, ctx, 0, MMQ_N, MMQ_K, seed=2)
+    w = backend.cuda_q8_weights_t()
+    if not w.upload(ctx, host_weights, host_weights.size, MMQ_N, MMQ_K).is_ok():
+        return None
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(3)
+    act = torch.randn(MMQ_M, MMQ_K, generator=gen, device="cuda", dtype=torch.float32)
+    out = torch.empty(MMQ_M, MMQ_N, device="cuda", dtype=torch.float32)
+    stream = torch.cuda.current_stream()
+
+    def once():
+        return backend.cuda_q8_matmul_device_f32(ctx, w, act.data_ptr(), MMQ_M, out.data_ptr(),
+                                                 out.numel())
+    for _ in range(3):
+        if not once().is_ok():
+            w.destroy()
+            return None
+    torch.cuda.synchronize()
+    iters = 50
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = ctx.launch_count()
+    start.record(stream)
+    for _ in range(iters):
+        once()
+    stop.record(stream)
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop) / iters
+    launches = (ctx.launch_count() - launches) // iters
+    ok = ctx.synchronize().is_ok()
+    w.destroy()
+    ops = 2.0 * MMQ_M * MMQ_K * MMQ_N
+    return {"metric": "q8_0_mmq_int8_throughput", "value": ops / (ms * 1e-3) / 1e12,
+            "unit": "TOPS", "ms": ms, "m": MMQ_M, "k": MMQ_K, "n": MMQ_N,
+            "includes": "activation quantization + product", "launches_per_call": int(launches),
+            "frac_of_4500_TOPS_nominal": ops / (ms * 1e-3) / 1e12 / 4500.0, "ok": ok}
+
+
+def ctx_cleanup(weights, ctx, dist):
+    weights.destroy()
+    ctx.destroy()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20000)
+    parser.add_argument("--warmup", type=int, default=200)
+    parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = parser.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,595 @@
+"""Host-side mirror of the reference's Fortran wrapper module `fortai_backend_cuda`
+(src/backend/cuda/fortai_backend_cuda.f90) over the C ABI.
+
+The image has no Fortran compiler, so the wrapper's types and free procedures are
+restated here with the same names, argument meaning and error behaviour:
+
+* `cuda_q8_context_t`, `cuda_q8_weights_t` hold an opaque handle (`.handle`,
+  0 when unassociated), as the Fortran derived types hold a `c_ptr`
+  (fortai_backend_cuda.f90:10-33);
+* every procedure reports through a `status_t` (src/fortai_status.f90): argument
+  problems caught before the C call give `FORTAI_INVALID` with the wrapper's
+  message; any non-zero code from the C side collapses to `FORTAI_UNSUPPORTED`
+  with the wrapper's fixed message (e.g. fortai_backend_cuda.f90:427-430,
+  :775-797).  `status_t.detail` additionally carries `fortai_cuda_q8_last_error`.
+* Fortran `intent(out)` arguments become return values: procedures return
+  `(outputs..., stat)` or just `stat`.
+
+Host arrays are numpy arrays (int8 for Q8_0 bytes, float32 for vectors); device
+buffers are integer addresses, as Fortran holds them in `type(c_ptr)`.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import byref, c_float, c_int, c_void_p
+
+import numpy as np
+
+from . import abi
+
+FORTAI_OK = 0
+FORTAI_INVALID = 1
+FORTAI_UNSUPPORTED = 2
+FORTAI_CUDA_OK = 0
+
+Q8_BLOCK_ELEMS = 32
+Q8_BLOCK_BYTES = 34
+
+
+class status_t:
+    """src/fortai_status.f90:13-20"""
+
+    def __init__(self):
+        self.code = FORTAI_OK
+        self.message = ""
+        self.detail = ""
+
+    def clear(self):
+        self.code = FORTAI_OK
+        self.message = ""
+        self.detail = ""
+
+    def is_ok(self) -> bool:
+        return self.code == FORTAI_OK
+
+    def set(self, code: int, message: str = "", detail: str = ""):
+        self.code = code
+        self.message = message
+        self.detail = detail
+
+    def __repr__(self):
+        return f"status_t(code={self.code}, message={self.message!r}, detail={self.detail!r})"
+
+
+def _lib():
+    return abi.load()
+
+
+def _host_ptr(array: np.ndarray) -> c_void_p:
+    return array.ctypes.data_as(c_void_p)
+
+
+def _as_bytes(array) -> np.ndarray:
+    a = np.ascontiguousarray(array)
+    return a.view(np.int8).reshape(-1)
+
+
+def _failed(stat: status_t, context, message: str) -> status_t:
+    detail = ""
+    if context is not None and context.handle:
+        raw = _lib().fortai_cuda_q8_last_error(context.handle)
+        detail = raw.decode(errors="replace") if raw else ""
+    stat.set(FORTAI_UNSUPPORTED, message, detail)
+    return stat
+
+
+class cuda_q8_context_t:
+    """fortai_backend_cuda.f90:10-26"""
+
+    def __init__(self):
+        self.handle = 0
+
+    # -- lifetime
+    def create(self, device: int, stream: int | None = None) -> status_t:
+        """`stream` (a cudaStream_t address) is an extension: the context then
+        borrows that stream instead of creating its own."""
+        stat = status_t()
+        if self.handle:
+            self.destroy()
+        out = c_void_p()
+        if stream is None:
+            code = _lib().fortai_cuda_q8_context_create(int(device), byref(out))
+        else:
+            code = _lib().fortai_cuda_q8_context_create_on_stream(int(device), c_void_p(stream),
+                                                                 byref(out))
+        if code != FORTAI_CUDA_OK:
+            self.handle = 0
+            stat.set(FORTAI_UNSUPPORTED, "CUDA Q8 context creation failed")
+        else:
+            self.handle = out.value
+        return stat
+
+    def destroy(self) -> status_t:
+        stat = status_t()
+        if not self.handle:
+            return stat
+        code = _lib().fortai_cuda_q8_context_destroy(self.handle)
+        self.handle = 0
+        if code != FORTAI_CUDA_OK:
+            stat.set(FORTAI_UNSUPPORTED, "CUDA Q8 context destruction failed")
+        return stat
+
+    # -- position / graphs
+    def set_position(self, position: int) -> status_t:
+        stat = status_t()
+        if not self.handle or position < 0:
+            stat.set(FORTAI_INVALID, "invalid CUDA device position")
+            return stat
+        if _lib().fortai_cuda_q8_context_set_position(self.handle, int(position)) != FORTAI_CUDA_OK:
+            return _failed(stat, self, "CUDA device position update failed")
+        return stat
+
+    def _graph(self, fn, message) -> status_t:
+        stat = status_t()
+        if not self.handle:
+            stat.set(FORTAI_INVALID, "invalid CUDA graph context")
+            return stat
+        if fn(self.handle) != FORTAI_CUDA_OK:
+            return _failed(stat, self, message)
+        return stat
+
+    def capture_begin(self) -> status_t:
+        return self._graph(_lib().fortai_cuda_q8_context_capture_begin,
+                           "CUDA graph capture begin failed")
+
+    def capture_end(self) -> status_t:
+        return self._graph(_lib().fortai_cuda_q8_context_capture_end,
+                           "CUDA graph capture end failed")
+
+    def graph_launch(self) -> status_t:
+        return self._graph(_lib().fortai_cuda_q8_context_graph_launch, "CUDA graph launch failed")
+
+    # -- device buffers
+    def allocate_buffer(self, nbytes: int):
+        stat = status_t()
+        if not self.handle or nbytes <= 0:
+            stat.set(FORTAI_INVALID, "invalid CUDA device buffer allocation")
+            return 0, stat
+        out = c_void_p()
+        if _lib().fortai_cuda_q8_device_buffer_create(self.handle, nbytes, byref(out)) != FORTAI_CUDA_OK:
+            return 0, _failed(stat, self, "CUDA device buffer allocation failed")
+        return out.value, stat
+
+    def free_buffer(self, device_buffer: int) -> status_t:
+        stat = status_t()
+        if not self.handle or not device_buffer:
+            return stat
+        if _lib().fortai_cuda_q8_device_buffer_destroy(self.handle, device_buffer) != FORTAI_CUDA_OK:
+            return _failed(stat, self, "CUDA device buffer free failed")
+        return stat
+
+    def upload(self, device_buffer: int, host_data: np.ndarray, nbytes: int | None = None) -> status_t:
+        stat = status_t()
+        data = _as_bytes(host_data)
+        nbytes = data.size if nbytes is None else nbytes
+        if not self.handle or not device_buffer or data.size <= 0 or nbytes <= 0 or nbytes > data.size:
+            stat.set(FORTAI_INVALID, "invalid CUDA device upload")
+            return stat
+        if _lib().fortai_cuda_q8_device_buffer_upload(self.handle, device_buffer, _host_ptr(data),
+                                                     nbytes) != FORTAI_CUDA_OK:
+            return _failed(stat, self, "CUDA device upload failed")
+        return stat
+
+    def upload_real(self, device_buffer: int, host_data: np.ndarray) -> status_t:
+        return self.upload(device_buffer, np.ascontiguousarray(host_data, dtype=np.float32))
+
+    def download(self, device_buffer: int, nbytes: int):
+        stat = status_t()
+        out = np.zeros(max(nbytes, 0), dtype=np.int8)
+        if not self.handle or not device_buffer or nbytes <= 0:
+            stat.set(FORTAI_INVALID, "invalid CUDA device download")
+            return out, stat
+        if _lib().fortai_cuda_q8_device_buffer_download(self.handle, _host_ptr(out), device_buffer,
+                                                       nbytes) != FORTAI_CUDA_OK:
+            return out, _failed(stat, self, "CUDA device download failed")
+        return out, stat
+
+    def download_real(self, device_buffer: int, elements: int):
+        raw, stat = self.download(device_buffer, elements * 4)
+        return raw.view(np.float32), stat
+
+    def last_error(self) -> str:
+        raw = _lib().fortai_cuda_q8_last_error(self.handle if self.handle else None)
+        return raw.decode(errors="replace") if raw else ""
+
+    # -- extensions
+    def stream(self) -> int:
+        return int(_lib().fortai_cuda_q8_context_stream(self.handle) or 0)
+
+    def launch_count(self) -> int:
+        return int(_lib().fortai_cuda_q8_context_launch_count(self.handle))
+
+    def synchronize(self) -> status_t:
+        stat = status_t()
+        if not self.handle:
+            stat.set(FORTAI_INVALID, "invalid CUDA Q8 context")
+            return stat
+        if _lib().fortai_cuda_q8_context_synchronize(self.handle) != FORTAI_CUDA_OK:
+            return _failed(stat, self, "CUDA synchronize failed")
+        return stat
+
+    def set_option(self, name: str, value: int) -> status_t:
+        stat = status_t()
+        if not self.handle or _lib().fortai_cuda_q8_context_set_option(
+                self.handle, name.encode(), int(value)) != FORTAI_CUDA_OK:
+            stat.set(FORTAI_INVALID, "invalid CUDA Q8 option")
+        return stat
+
+
+class cuda_q8_weights_t:
+    """fortai_backend_cuda.f90:28-33"""
+
+    def __init__(self):
+        self.handle = 0
+        self.rows = 0
+        self.width = 0
+
+    def upload(self, context: cuda_q8_context_t, host_weights: np.ndarray, weight_bytes: int,
+               rows: int, width: int) -> status_t:
+        stat = status_t()
+        data = _as_bytes(host_weights)
+        if not context.handle or data.size <= 0 or rows <= 0 or width <= 0:
+            stat.set(FORTAI_INVALID, "invalid CUDA Q8 weight upload")
+            return stat
+        if self.handle:
+            self.destroy()
+        out = c_void_p()
+        code = _lib().fortai_cuda_q8_weights_upload(context.handle, _host_ptr(data), weight_bytes,
+                                                    int(rows), int(width), byref(out))
+        if code != FORTAI_CUDA_OK:
+            self.handle = 0
+            return _failed(stat, context, "CUDA Q8 weight upload failed")
+        self.handle, self.rows, self.width = out.value, rows, width
+        return stat
+
+    def upload_columns(self, context: cuda_q8_context_t, host_weights: np.ndarray, rows: int,
+                       width: int, first_block: int, block_count: int) -> status_t:
+        """Extension: keep only a K-slice of every row (column-sharded projections)."""
+        stat = status_t()
+        data = _as_bytes(host_weights)
+        if not context.handle or data.size <= 0 or rows <= 0 or width <= 0:
+            stat.set(FORTAI_INVALID, "invalid CUDA Q8 weight upload")
+            return stat
+        if self.handle:
+            self.destroy()
+        out = c_void_p()
+        code = _lib().fortai_cuda_q8_weights_upload_columns(
+            context.handle, _host_ptr(data), data.size, int(rows), int(width), int(first_block),
+            int(block_count), byref(out))
+        if code != FORTAI_CUDA_OK:
+            self.handle = 0
+            return _failed(stat, context, "CUDA Q8 weight upload failed")
+        self.handle, self.rows, self.width = out.value, rows, block_count * Q8_BLOCK_ELEMS
+        return stat
+
+    def destroy(self) -> status_t:
+        stat = status_t()
+        if not self.handle:
+            return stat
+        code = _lib().fortai_cuda_q8_weights_destroy(self.handle)
+        self.handle = 0
+        if code != FORTAI_CUDA_OK:
+            stat.set(FORTAI_UNSUPPORTED, "CUDA Q8 weight destruction failed")
+        return stat
+
+
+def _f32_out(elements: int) -> np.ndarray:
+    return np.zeros(max(int(elements), 0), dtype=np.float32)
+
+
+# --------------------------------------------------------------------------- host calls
+def cuda_q8_matvec_host(context, weights, activation, activation_bytes, output, output_bytes):
+    """fortai_backend_cuda.f90:775-797.  Returns (elapsed_ms, stat); `output` is filled."""
+    stat = status_t()
+    act = _as_bytes(activation)
+    if not context.handle or not weights.handle or act.size <= 0 or output.size <= 0:
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 host matvec")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matvec_host(context.handle, weights.handle, _host_ptr(act),
+                                             activation_bytes, _host_ptr(output), output_bytes,
+                                             byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 host matvec failed")
+    return ms.value, stat
+
+
+def cuda_q8_matvec_host_pair(context, first_weights, second_weights, activation, activation_bytes,
+                             first_output, first_output_bytes, second_output, second_output_bytes):
+    """fortai_backend_cuda.f90:799-825"""
+    stat = status_t()
+    act = _as_bytes(activation)
+    if (not context.handle or not first_weights.handle or not second_weights.handle or
+            act.size <= 0 or first_output.size <= 0 or second_output.size <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 host matvec pair")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matvec_host_pair(
+        context.handle, first_weights.handle, second_weights.handle, _host_ptr(act),
+        activation_bytes, _host_ptr(first_output), first_output_bytes, _host_ptr(second_output),
+        second_output_bytes, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 host matvec pair failed")
+    return ms.value, stat
+
+
+def cuda_q8_matvec_host_triplet(context, first_weights, second_weights, third_weights, activation,
+                                activation_bytes, first_output, first_output_bytes, second_output,
+                                second_output_bytes, third_output, third_output_bytes):
+    """fortai_backend_cuda.f90:827-858"""
+    stat = status_t()
+    act = _as_bytes(activation)
+    if (not context.handle or not first_weights.handle or not second_weights.handle or
+            not third_weights.handle or act.size <= 0 or first_output.size <= 0 or
+            second_output.size <= 0 or third_output.size <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 host matvec triplet")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matvec_host_triplet(
+        context.handle, first_weights.handle, second_weights.handle, third_weights.handle,
+        _host_ptr(act), activation_bytes, _host_ptr(first_output), first_output_bytes,
+        _host_ptr(second_output), second_output_bytes, _host_ptr(third_output),
+        third_output_bytes, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 host matvec triplet failed")
+    return ms.value, stat
+
+
+def cuda_q8_matvec_host_triplet_contiguous(context, first_weights, second_weights, third_weights,
+                                           activation, activation_bytes, output, output_bytes):
+    """fortai_backend_cuda.f90:860-888"""
+    stat = status_t()
+    act = _as_bytes(activation)
+    if (not context.handle or not first_weights.handle or not second_weights.handle or
+            not third_weights.handle or act.size <= 0 or output.size <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 host matvec triplet")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matvec_host_triplet_contiguous(
+        context.handle, first_weights.handle, second_weights.handle, third_weights.handle,
+        _host_ptr(act), activation_bytes, _host_ptr(output), output_bytes, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 host matvec triplet failed")
+    return ms.value, stat
+
+
+def cuda_q8_ffn_host(context, gate_weights, up_weights, down_weights, activation, activation_bytes,
+                     output, output_bytes):
+    """fortai_backend_cuda.f90:890-918"""
+    stat = status_t()
+    act = _as_bytes(activation)
+    if (not context.handle or not gate_weights.handle or not up_weights.handle or
+            not down_weights.handle or act.size <= 0 or output.size <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 FFN")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_ffn_host(context.handle, gate_weights.handle, up_weights.handle,
+                                          down_weights.handle, _host_ptr(act), activation_bytes,
+                                          _host_ptr(output), output_bytes, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 FFN failed")
+    return ms.value, stat
+
+
+# --------------------------------------------------------------------------- device calls
+def cuda_q8_ffn_device(context, gate_weights, up_weights, down_weights, device_activation,
+                       activation_elements, device_output, output_elements) -> status_t:
+    """fortai_backend_cuda.f90:920-946"""
+    stat = status_t()
+    if (not context.handle or not gate_weights.handle or not up_weights.handle or
+            not down_weights.handle or not device_activation or not device_output or
+            activation_elements <= 0 or output_elements <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 device FFN")
+        return stat
+    code = _lib().fortai_cuda_q8_ffn_device(context.handle, gate_weights.handle, up_weights.handle,
+                                            down_weights.handle, device_activation,
+                                            activation_elements, device_output, output_elements)
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 device FFN failed")
+    return stat
+
+
+def cuda_q8_matvec_resident(context, weights, device_activation, device_output):
+    """fortai_backend_cuda.f90:1014-1036.  Returns (kernel_ms, stat)."""
+    stat = status_t()
+    if not context.handle or not weights.handle or not device_activation or not device_output:
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 resident matvec")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matvec_resident(context.handle, weights.handle, device_activation,
+                                                 device_output, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 resident matvec failed")
+    return ms.value, stat
+
+
+def cuda_q8_matvec_device_f32(context, weights, device_activation, activation_elements,
+                              device_output, output_elements) -> status_t:
+    """fortai_backend_cuda.f90:1038-1062"""
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not device_output or
+            activation_elements <= 0 or output_elements <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 device F32 matvec")
+        return stat
+    code = _lib().fortai_cuda_q8_matvec_device_f32(context.handle, weights.handle,
+                                                   device_activation, activation_elements,
+                                                   device_output, output_elements)
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 device F32 matvec failed")
+    return stat
+
+
+def cuda_qwen35_embedding_device(context, weights, token_id, device_output, output_elements):
+    """fortai_backend_cuda.f90:1064-1086"""
+    stat = status_t()
+    if not context.handle or not weights.handle or not device_output or output_elements <= 0:
+        stat.set(FORTAI_INVALID, "invalid CUDA device embedding")
+        return stat
+    code = _lib().fortai_cuda_qwen35_embedding_device(context.handle, weights.handle,
+                                                      int(token_id), device_output,
+                                                      output_elements)
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA device embedding failed")
+    return stat
+
+
+def cuda_qwen35_copy_device(context, device_input, device_output, nbytes) -> status_t:
+    """fortai_backend_cuda.f90:720-738"""
+    stat = status_t()
+    if not context.handle or not device_input or not device_output or nbytes <= 0:
+        stat.set(FORTAI_INVALID, "invalid CUDA device copy")
+        return stat
+    if _lib().fortai_cuda_qwen35_copy_device(context.handle, device_input, device_output,
+                                             nbytes) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA device copy failed")
+    return stat
+
+
+def cuda_qwen35_add_device(context, device_left, device_right, device_output, elements) -> status_t:
+    """fortai_backend_cuda.f90:740-758"""
+    stat = status_t()
+    if (not context.handle or not device_left or not device_right or not device_output or
+            elements <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA device add")
+        return stat
+    if _lib().fortai_cuda_qwen35_add_device(context.handle, device_left, device_right,
+                                            device_output, elements) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA device add failed")
+    return stat
+
+
+def cuda_qwen35_rms_norm_device(context, device_input, device_weights, device_output, elements,
+                                epsilon) -> status_t:
+    """fortai_backend_cuda.f90:760-773"""
+    stat = status_t()
+    if (not context.handle or not device_input or not device_weights or not device_output or
+            elements <= 0 or epsilon <= 0.0):
+        stat.set(FORTAI_INVALID, "invalid CUDA device RMS norm")
+        return stat
+    if _lib().fortai_cuda_qwen35_rms_norm_device(context.handle, device_input, device_weights,
+                                                 device_output, elements,
+                                                 c_float(epsilon)) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA device RMS norm failed")
+    return stat
+
+
+# --------------------------------------------------------------------------- extensions
+def cuda_q8_quantize_device(context, device_input, elements, device_output, output_bytes) -> status_t:
+    stat = status_t()
+    if not context.handle or not device_input or not device_output or elements <= 0:
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 device quantize")
+        return stat
+    if _lib().fortai_cuda_q8_quantize_device(context.handle, device_input, elements, device_output,
+                                             output_bytes) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 device quantize failed")
+    return stat
+
+
+def cuda_q8_block_dots_device(context, weights, device_activation, device_output,
+                              output_elements) -> status_t:
+    stat = status_t()
+    if not context.handle or not weights.handle or not device_activation or not device_output:
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 block dots")
+        return stat
+    if _lib().fortai_cuda_q8_block_dots_device(context.handle, weights.handle, device_activation,
+                                               device_output, output_elements) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 block dots failed")
+    return stat
+
+
+def cuda_q8_matvec_host_f32(context, weights, activation, output):
+    """Host fp32 vector in, host fp32 vector out.  Returns (elapsed_ms, stat)."""
+    stat = status_t()
+    if (not context.handle or not weights.handle or activation.size <= 0 or output.size <= 0 or
+            activation.dtype != np.float32 or output.dtype != np.float32):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 host F32 matvec")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matvec_host_f32(context.handle, weights.handle,
+                                                 _host_ptr(activation), activation.size,
+                                                 _host_ptr(output), output.nbytes, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 host F32 matvec failed")
+    return ms.value, stat
+
+
+def cuda_q8_matmul_device_f32(context, weights, device_activation, tokens, device_output,
+                              output_elements) -> status_t:
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not device_output or
+            tokens <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 device matmul")
+        return stat
+    if _lib().fortai_cuda_q8_matmul_device_f32(context.handle, weights.handle, device_activation,
+                                               int(tokens), device_output,
+                                               output_elements) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 device matmul failed")
+    return stat
+
+
+def cuda_q8_matmul_resident(context, weights, device_activation, tokens, device_output):
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not device_output or
+            tokens <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 resident matmul")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matmul_resident(context.handle, weights.handle, device_activation,
+                                                 int(tokens), device_output, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 resident matmul failed")
+    return ms.value, stat
+
+
+def cuda_q8_matmul_host_f32(context, weights, activation, tokens, output):
+    stat = status_t()
+    if (not context.handle or not weights.handle or activation.size <= 0 or output.size <= 0 or
+            tokens <= 0 or activation.dtype != np.float32 or output.dtype != np.float32):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 host matmul")
+        return 0.0, stat
+    ms = c_float(0.0)
+    code = _lib().fortai_cuda_q8_matmul_host_f32(context.handle, weights.handle,
+                                                 _host_ptr(activation), int(tokens),
+                                                 _host_ptr(output), output.nbytes, byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, _failed(stat, context, "CUDA Q8 host matmul failed")
+    return ms.value, stat
+
+
+def cuda_q8_matmul_block_dots_device(context, weights, device_activation, tokens, device_output,
+                                     output_elements) -> status_t:
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not device_output or
+            tokens <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 matmul block dots")
+        return stat
+    if _lib().fortai_cuda_q8_matmul_block_dots_device(
+            context.handle, weights.handle, device_activation, int(tokens), device_output,
+            output_elements) != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 matmul block dots failed")
+    return stat
+
+
+def cuda_q8_matvec_device_f32_peers(context, weights, device_activation, activation_elements,
+                                    peer_outputs, first_row, output_elements) -> status_t:
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not peer_outputs):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 peer matvec")
+        return stat
+    array = (c_void_p * len(peer_outputs))(*[c_void_p(p) for p in peer_outputs])
+    code = _lib().fortai_cuda_q8_matvec_device_f32_peers(
+        context.handle, weights.handle, device_activation, activation_elements, array,
+        len(peer_outputs), int(first_row), int(output_elements))
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 peer matvec failed")
+    return stat

@@ -1,0 +1,1160 @@
+// C ABI of the B200 Q8_0 backend: handles, validation, scratch, launch policy.
+//
+// Mirrors the behaviour of the reference backend's entry points
+// (backend/cuda/fortai_cuda_backend.cu:789-1296, 1733-1736): same symbols, same
+// argument checks, same return codes, same blocking/enqueue split.  The kernels
+// behind them are in q8_gemv.cuh (batch 1) and q8_mmq.cuh (prefill).
+#include "../../include/fortai_cuda_backend_b200.h"
+
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "q8_common.cuh"
+#include "q8_gemv.cuh"
+#include "q8_mmq.cuh"
+
+using namespace fortai_b200;
+
+struct fortai_cuda_q8_context {
+    int device = 0;
+    int sm_count = kSmCountB200;
+    cudaStream_t stream = nullptr;
+    bool owns_stream = true;
+    cudaEvent_t start = nullptr;
+    cudaEvent_t stop = nullptr;
+    uint8_t *scratch_activation = nullptr;   // Q8_0 activation(s)
+    size_t scratch_activation_bytes = 0;
+    float *scratch_output = nullptr;         // fp32 intermediate / host-call output
+    size_t scratch_output_bytes = 0;
+    uint8_t *scratch_aux = nullptr;          // prefill: planar activation, partial tiles
+    size_t scratch_aux_bytes = 0;
+    int *position = nullptr;
+    int *status_host = nullptr;              // pinned + mapped: kernels write, host reads
+    int *status_device = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
+    uint64_t launches = 0;
+    // options
+    int gemv_variant = 0;      // 0 auto, 1 direct, 2 ring
+    int gemv_ctas_per_sm = 0;  // 0 = occupancy-derived
+    int gemv_rows_per_warp = 0;
+    int ring_stages = 0;
+    int ring_rows = 0;
+    int mmq_min_tokens = 0;
+    char error[256] = {};
+};
+
+struct fortai_cuda_q8_weights {
+    fortai_cuda_q8_context *context = nullptr;
+    int rows = 0;
+    int width = 0;
+    int blocks = 0;
+    int row_stride = 0;
+    uint8_t *data = nullptr;
+    MmqWeightsPlan mmq;   // tensor maps for the prefill kernel, built lazily
+};
+
+struct fortai_cuda_qwen35_recurrent {
+    fortai_cuda_q8_context *context = nullptr;
+};
+
+struct fortai_cuda_qwen35_attention {
+    fortai_cuda_q8_context *context = nullptr;
+};
+
+namespace {
+
+int fail(fortai_cuda_q8_context *context, const char *operation,
+    cudaError_t error = cudaSuccess) {
+    if (context) {
+        if (error == cudaSuccess)
+            std::snprintf(context->error, sizeof(context->error), "%s", operation);
+        else
+            std::snprintf(context->error, sizeof(context->error), "%s: %s", operation,
+                cudaGetErrorString(error));
+    }
+    return FORTAI_CUDA_RUNTIME_ERROR;
+}
+
+const char *status_text(int code) {
+    switch (code) {
+    case kStatusRingProducerTimeout: return "GEMV ring producer gave up waiting for a free stage";
+    case kStatusRingConsumerTimeout: return "GEMV ring consumer gave up waiting for a weight tile";
+    case kStatusMmqLoadTimeout: return "prefill kernel gave up waiting for an operand tile";
+    case kStatusMmqMmaTimeout: return "prefill kernel gave up waiting for the tensor core";
+    case kStatusMmqDrainTimeout: return "prefill kernel gave up waiting for an accumulator";
+    case kStatusPeerFlagTimeout: return "gave up waiting for a peer flag";
+    default: return "unknown device status";
+    }
+}
+
+// After a synchronizing call: turn a device-side give-up into a runtime error.
+int finish(fortai_cuda_q8_context *context, const char *operation, cudaError_t error) {
+    if (error != cudaSuccess) return fail(context, operation, error);
+    const int status = *static_cast<volatile int *>(context->status_host);
+    if (status != kStatusOk) {
+        *static_cast<volatile int *>(context->status_host) = kStatusOk;
+        std::snprintf(context->error, sizeof(context->error), "%s: %s", operation,
+            status_text(status));
+        return FORTAI_CUDA_RUNTIME_ERROR;
+    }
+    return FORTAI_CUDA_OK;
+}
+
+cudaError_t grow(void **pointer, size_t *have, size_t want) {
+    if (want <= *have) return cudaSuccess;
+    cudaError_t error = cudaFree(*pointer);
+    *pointer = nullptr;
+    *have = 0;
+    if (error != cudaSuccess) return error;
+    error = cudaMalloc(pointer, want);
+    if (error == cudaSuccess) *have = want;
+    return error;
+}
+
+cudaError_t ensure_scratch(fortai_cuda_q8_context *c, size_t activation_bytes,
+    size_t output_bytes, size_t aux_bytes = 0) {
+    cudaError_t error = grow(reinterpret_cast<void **>(&c->scratch_activation),
+        &c->scratch_activation_bytes, activation_bytes);
+    if (error == cudaSuccess)
+        error = grow(reinterpret_cast<void **>(&c->scratch_output), &c->scratch_output_bytes,
+            output_bytes);
+    if (error == cudaSuccess)
+        error = grow(reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes, aux_bytes);
+    return error;
+}
+
+// ---------------------------------------------------------------------------
+// GEMV launch policy
+// ---------------------------------------------------------------------------
+template <int U, int NR, int ACT, int EPI>
+cudaError_t launch_direct_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
+    auto kernel = q8_gemv_direct_kernel<U, NR, ACT, EPI>;
+    const size_t smem = activation_smem_bytes(p.width, p.blocks);
+    static int per_sm_cache[64] = {};   // indexed by device
+    cudaError_t error = cudaSuccess;
+    if (smem > 48 * 1024) {
+        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            static_cast<int>(smem));
+        if (error != cudaSuccess) return error;
+    }
+    int per_sm = c->gemv_ctas_per_sm;
+    if (per_sm <= 0) {
+        int &cached = per_sm_cache[c->device & 63];
+        if (cached == 0 || smem > 8 * 1024) {
+            int blocks = 0;
+            error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, kernel, kGemvThreads,
+                smem);
+            if (error != cudaSuccess) return error;
+            if (smem <= 8 * 1024) cached = blocks;
+            per_sm = blocks;
+        } else {
+            per_sm = cached;
+        }
+        if (per_sm < 1) per_sm = 1;
+    }
+    const int rows_per_cta = kGemvWarps * (EPI == kEpiSiluPair ? 1 : NR);
+    const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
+    const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
+    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+template <int ACT, int EPI>
+cudaError_t launch_direct(fortai_cuda_q8_context *c, const GemvParams &p) {
+    const int nchunks = p.width / 16;
+    const int per_lane = (nchunks + 31) / 32;
+    int rows_per_warp = c->gemv_rows_per_warp;
+    if (EPI == kEpiSiluPair || EPI == kEpiBlockDots) rows_per_warp = 1;
+    else if (rows_per_warp <= 0) rows_per_warp = per_lane <= 4 ? 2 : 1;
+    if (per_lane <= 2)
+        return rows_per_warp == 2 ? launch_direct_instance<2, 2, ACT, EPI>(c, p)
+                                  : launch_direct_instance<2, 1, ACT, EPI>(c, p);
+    if (per_lane <= 4)
+        return rows_per_warp == 2 ? launch_direct_instance<4, 2, ACT, EPI>(c, p)
+                                  : launch_direct_instance<4, 1, ACT, EPI>(c, p);
+    if (per_lane == 5 || per_lane == 10 || per_lane == 15 || per_lane == 19 || per_lane == 20)
+        return rows_per_warp == 2 ? launch_direct_instance<5, 2, ACT, EPI>(c, p)
+                                  : launch_direct_instance<5, 1, ACT, EPI>(c, p);
+    return rows_per_warp == 2 ? launch_direct_instance<8, 2, ACT, EPI>(c, p)
+                              : launch_direct_instance<8, 1, ACT, EPI>(c, p);
+}
+
+bool ring_plan(const fortai_cuda_q8_context *c, const GemvParams &p, int epi, RingConfig *cfg) {
+    const int copies = epi == kEpiSiluPair ? 2 : 1;
+    const size_t stride = static_cast<size_t>(p.row_stride);
+    int rows = c->ring_rows;
+    if (rows <= 0) {
+        rows = static_cast<int>((24 * 1024) / (stride * copies));
+        rows = std::max(kRingConsumerWarps, std::min(64, rows / kRingConsumerWarps *
+            kRingConsumerWarps));
+    }
+    const size_t stage = rows * stride * copies;
+    const size_t budget = 200 * 1024 - activation_smem_bytes(p.width, p.blocks) - 512;
+    if (stage * 2 > budget || stage * copies >= (1u << 20)) return false;
+    int stages = c->ring_stages > 0 ? c->ring_stages : kRingMaxStages;
+    stages = std::min<int>(stages, static_cast<int>(budget / stage));
+    stages = std::max(2, std::min(kRingMaxStages, stages));
+    cfg->stages = stages;
+    cfg->rows_per_tile = rows;
+    cfg->stage_bytes = static_cast<int>(stage);
+    cfg->tiles = (p.total_rows + rows - 1) / rows;
+    return true;
+}
+
+template <int ACT, int EPI>
+cudaError_t launch_ring(fortai_cuda_q8_context *c, const GemvParams &p, const RingConfig &cfg) {
+    auto kernel = q8_gemv_ring_kernel<ACT, EPI>;
+    const size_t smem = ring_smem_bytes(p.width, p.blocks, cfg);
+    cudaError_t error = cudaFuncSetAttribute(kernel,
+        cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (error != cudaSuccess) return error;
+    const int grid = std::max(1, std::min(cfg.tiles, c->sm_count));
+    kernel<<<grid, kRingThreads, smem, c->stream>>>(p, cfg);
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+// The automatic choice: the ring pays off once a matrix no longer fits in L2 and
+// is a single (or gate/up) stream; everything else takes the direct kernel.
+bool want_ring(const fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
+    if (epi == kEpiBlockDots) return false;
+    if (epi == kEpiPlain && p.segments != 1) return false;
+    if (c->gemv_variant == 1) return false;
+    if (c->gemv_variant == 2) return true;
+    return false;
+}
+
+template <int ACT>
+cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
+    RingConfig cfg;
+    const bool ring = want_ring(c, p, epi) && ring_plan(c, p, epi, &cfg);
+    switch (epi) {
+    case kEpiPlain:
+        return ring ? launch_ring<ACT, kEpiPlain>(c, p, cfg) : launch_direct<ACT, kEpiPlain>(c, p);
+    case kEpiSiluPair:
+        return ring ? launch_ring<ACT, kEpiSiluPair>(c, p, cfg)
+                    : launch_direct<ACT, kEpiSiluPair>(c, p);
+    case kEpiPeers:
+        return ring ? launch_ring<ACT, kEpiPeers>(c, p, cfg) : launch_direct<ACT, kEpiPeers>(c, p);
+    default:
+        return launch_direct<kActQ8, kEpiBlockDots>(c, p);
+    }
+}
+
+cudaError_t launch_gemv(fortai_cuda_q8_context *c, const GemvParams &p, int act, int epi) {
+    return act == kActF32 ? launch_gemv_act<kActF32>(c, p, epi)
+                          : launch_gemv_act<kActQ8>(c, p, epi);
+}
+
+GemvParams single_params(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
+    const void *activation, float *output) {
+    GemvParams p = {};
+    p.weights[0] = w->data;
+    p.outputs[0] = output;
+    p.rows[0] = w->rows;
+    p.segments = 1;
+    p.total_rows = w->rows;
+    p.width = w->width;
+    p.blocks = w->blocks;
+    p.row_stride = w->row_stride;
+    p.activation = activation;
+    p.status = c->status_device;
+    return p;
+}
+
+cudaError_t launch_quantize(fortai_cuda_q8_context *c, const float *input, uint8_t *output,
+    size_t blocks) {
+    const long long want = static_cast<long long>((blocks + 7) / 8);
+    const int grid = static_cast<int>(std::max<long long>(1,
+        std::min<long long>(want, static_cast<long long>(c->sm_count) * 16)));
+    q8_quantize_kernel<<<grid, 256, 0, c->stream>>>(input, output,
+        static_cast<long long>(blocks));
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+bool owned(const fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w) {
+    return c && w && w->context == c && w->data;
+}
+
+int create_context(int device, bool borrow, cudaStream_t stream, fortai_cuda_q8_context **out) {
+    if (!out || device < 0) return FORTAI_CUDA_INVALID;
+    *out = nullptr;
+    auto *c = new (std::nothrow) fortai_cuda_q8_context;
+    if (!c) return FORTAI_CUDA_RUNTIME_ERROR;
+    c->device = device;
+    c->owns_stream = !borrow;
+    c->stream = stream;
+    bool ok = cudaSetDevice(device) == cudaSuccess;
+    if (ok && !borrow)
+        ok = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaEventCreate(&c->start) == cudaSuccess &&
+        cudaEventCreate(&c->stop) == cudaSuccess;
+    ok = ok && cudaMalloc(reinterpret_cast<void **>(&c->position), sizeof(int)) == cudaSuccess &&
+        cudaMemsetAsync(c->position, 0, sizeof(int), c->stream) == cudaSuccess;
+    ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&c->status_host), sizeof(int),
+        cudaHostAllocMapped) == cudaSuccess;
+    if (ok) {
+        *c->status_host = kStatusOk;
+        ok = cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->status_device),
+            c->status_host, 0) == cudaSuccess;
+    }
+    int sms = 0;
+    if (ok && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess
+        && sms > 0)
+        c->sm_count = sms;
+    ok = ok && cudaStreamSynchronize(c->stream) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        fortai_cuda_q8_context_destroy(c);
+        return FORTAI_CUDA_RUNTIME_ERROR;
+    }
+    *out = c;
+    return FORTAI_CUDA_OK;
+}
+
+int upload_weights(fortai_cuda_q8_context *context, const void *host_weights,
+    size_t weight_bytes, int rows, int width, int first_block, int block_count,
+    fortai_cuda_q8_weights **weights) {
+    if (!context || !host_weights || !weights || rows <= 0 || width <= 0 ||
+        width % kBlockElems != 0) return FORTAI_CUDA_INVALID;
+    *weights = nullptr;
+    const int src_blocks = width / kBlockElems;
+    if (first_block < 0 || block_count <= 0 || first_block + block_count > src_blocks)
+        return FORTAI_CUDA_INVALID;
+    const size_t expected = static_cast<size_t>(rows) * src_blocks * kBlockBytes;
+    if (weight_bytes < expected) return FORTAI_CUDA_INVALID;
+    auto *w = new (std::nothrow) fortai_cuda_q8_weights;
+    if (!w) return FORTAI_CUDA_RUNTIME_ERROR;
+    w->context = context;
+    w->rows = rows;
+    w->width = block_count * kBlockElems;
+    w->blocks = block_count;
+    w->row_stride = static_cast<int>(row_stride_bytes(block_count));
+    cudaSetDevice(context->device);
+    uint8_t *staging = nullptr;
+    const size_t device_bytes = static_cast<size_t>(rows) * w->row_stride;
+    cudaError_t error = cudaMalloc(reinterpret_cast<void **>(&w->data), device_bytes);
+    if (error == cudaSuccess) error = cudaMalloc(reinterpret_cast<void **>(&staging), expected);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(staging, host_weights, expected, cudaMemcpyHostToDevice,
+            context->stream);
+    if (error == cudaSuccess && device_bytes != static_cast<size_t>(rows) * block_count * kBlockBytes)
+        error = cudaMemsetAsync(w->data, 0, device_bytes, context->stream);
+    if (error == cudaSuccess) {
+        const long long total = static_cast<long long>(rows) * block_count;
+        const int grid = static_cast<int>(std::max<long long>(1,
+            std::min<long long>((total + 255) / 256, 148LL * 32)));
+        q8_repack_kernel<<<grid, 256, 0, context->stream>>>(staging, w->data, rows, src_blocks,
+            first_block, block_count, w->row_stride);
+        ++context->launches;
+        error = cudaGetLastError();
+    }
+    if (error == cudaSuccess) error = cudaStreamSynchronize(context->stream);
+    cudaFree(staging);
+    if (error != cudaSuccess) {
+        cudaFree(w->data);
+        delete w;
+        return fail(context, "weight upload", error);
+    }
+    *weights = w;
+    return FORTAI_CUDA_OK;
+}
+
+struct HostRequest {
+    const fortai_cuda_q8_weights *weights;
+    float *output;
+    size_t output_bytes;
+};
+
+// reference: matvec_host_many, backend.cu:249-315
+int matvec_host_many(fortai_cuda_q8_context *c, const HostRequest *requests, int count,
+    const void *host_activation, size_t activation_bytes, float *elapsed_ms,
+    float *combined_output) {
+    if (!c || !requests || count <= 0 || count > kMaxSegments || !host_activation || !elapsed_ms)
+        return FORTAI_CUDA_INVALID;
+    const fortai_cuda_q8_weights *first = requests[0].weights;
+    if (!first || !first->data) return FORTAI_CUDA_INVALID;
+    const size_t expected_activation = static_cast<size_t>(first->blocks) * kBlockBytes;
+    // the reference returns the outputs back to back only when it fuses the
+    // launch, i.e. for fewer than 128 blocks per row
+    if (combined_output && first->blocks >= 128) return FORTAI_CUDA_INVALID;
+    size_t total_rows = 0;
+    for (int i = 0; i < count; ++i) {
+        const fortai_cuda_q8_weights *w = requests[i].weights;
+        if (!owned(c, w) || w->blocks != first->blocks || !requests[i].output)
+            return FORTAI_CUDA_INVALID;
+        if (activation_bytes < expected_activation ||
+            requests[i].output_bytes < static_cast<size_t>(w->rows) * sizeof(float))
+            return FORTAI_CUDA_INVALID;
+        total_rows += static_cast<size_t>(w->rows);
+    }
+    cudaSetDevice(c->device);
+    cudaError_t error = ensure_scratch(c, expected_activation, total_rows * sizeof(float));
+    if (error == cudaSuccess) error = cudaEventRecord(c->start, c->stream);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(c->scratch_activation, host_activation, expected_activation,
+            cudaMemcpyHostToDevice, c->stream);
+    if (error == cudaSuccess) {
+        GemvParams p = {};
+        size_t offset = 0;
+        for (int i = 0; i < count; ++i) {
+            p.weights[i] = requests[i].weights->data;
+            p.outputs[i] = c->scratch_output + offset;
+            p.rows[i] = requests[i].weights->rows;
+            offset += static_cast<size_t>(requests[i].weights->rows);
+        }
+        p.segments = count;
+        p.total_rows = static_cast<int>(total_rows);
+        p.width = first->width;
+        p.blocks = first->blocks;
+        p.row_stride = first->row_stride;
+        p.activation = c->scratch_activation;
+        p.status = c->status_device;
+        error = launch_gemv(c, p, kActQ8, kEpiPlain);
+    }
+    if (error == cudaSuccess) {
+        if (combined_output) {
+            error = cudaMemcpyAsync(combined_output, c->scratch_output,
+                total_rows * sizeof(float), cudaMemcpyDeviceToHost, c->stream);
+        } else {
+            size_t offset = 0;
+            for (int i = 0; i < count && error == cudaSuccess; ++i) {
+                const size_t rows = static_cast<size_t>(requests[i].weights->rows);
+                error = cudaMemcpyAsync(requests[i].output, c->scratch_output + offset,
+                    rows * sizeof(float), cudaMemcpyDeviceToHost, c->stream);
+                offset += rows;
+            }
+        }
+    }
+    if (error == cudaSuccess) error = cudaEventRecord(c->stop, c->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(c->stop);
+    if (error == cudaSuccess) error = cudaEventElapsedTime(elapsed_ms, c->start, c->stop);
+    return finish(c, "grouped host matvec", error);
+}
+
+bool ffn_shapes_ok(const fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *gate,
+    const fortai_cuda_q8_weights *up, const fortai_cuda_q8_weights *down) {
+    return owned(c, gate) && owned(c, up) && owned(c, down) && gate->blocks == up->blocks &&
+        gate->rows == up->rows && gate->rows == down->blocks * kBlockElems;
+}
+
+// quantize(x) is folded into the gate/up kernel when x is fp32; then
+// h = silu(gate.x) * (up.x) -> scratch_output, Q8(h) -> scratch_activation, down.
+cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *gate,
+    const fortai_cuda_q8_weights *up, const fortai_cuda_q8_weights *down, const void *activation,
+    int act, float *output) {
+    GemvParams p = single_params(c, gate, activation, c->scratch_output);
+    p.weights[1] = up->data;
+    p.rows[1] = up->rows;
+    p.segments = 2;
+    cudaError_t error = launch_gemv(c, p, act, kEpiSiluPair);
+    if (error == cudaSuccess)
+        error = launch_quantize(c, c->scratch_output, c->scratch_activation,
+            static_cast<size_t>(down->blocks));
+    if (error == cudaSuccess) {
+        GemvParams d = single_params(c, down, c->scratch_activation, output);
+        error = launch_gemv(c, d, kActQ8, kEpiPlain);
+    }
+    return error;
+}
+
+int not_built(fortai_cuda_q8_context *context, const char *what) {
+    // "unsupported backends fail explicitly and never fall back silently"
+    // (reference README.md:38)
+    if (context)
+        std::snprintf(context->error, sizeof(context->error),
+            "%s is not implemented in the B200 Q8_0 backend", what);
+    return FORTAI_CUDA_RUNTIME_ERROR;
+}
+
+}  // namespace
+
+// ===========================================================================
+// Part 1: reference interface
+// ===========================================================================
+extern "C" int fortai_cuda_q8_context_create(int device, fortai_cuda_q8_context **context) {
+    return create_context(device, false, nullptr, context);
+}
+
+extern "C" int fortai_cuda_q8_context_create_on_stream(int device, void *stream,
+    fortai_cuda_q8_context **context) {
+    return create_context(device, true, static_cast<cudaStream_t>(stream), context);
+}
+
+extern "C" int fortai_cuda_q8_context_destroy(fortai_cuda_q8_context *context) {
+    if (!context) return FORTAI_CUDA_OK;
+    cudaSetDevice(context->device);
+    if (context->graph_exec) cudaGraphExecDestroy(context->graph_exec);
+    if (context->graph) cudaGraphDestroy(context->graph);
+    cudaFree(context->position);
+    cudaFree(context->scratch_activation);
+    cudaFree(context->scratch_output);
+    cudaFree(context->scratch_aux);
+    if (context->status_host) cudaFreeHost(context->status_host);
+    if (context->start) cudaEventDestroy(context->start);
+    if (context->stop) cudaEventDestroy(context->stop);
+    if (context->owns_stream && context->stream) cudaStreamDestroy(context->stream);
+    delete context;
+    return FORTAI_CUDA_OK;
+}
+
+extern "C" int fortai_cuda_q8_context_set_position(fortai_cuda_q8_context *context,
+    int position) {
+    if (!context || !context->position || position < 0) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaMemcpyAsync(context->position, &position, sizeof(position),
+        cudaMemcpyHostToDevice, context->stream);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "set device position", error);
+}
+
+extern "C" int fortai_cuda_q8_context_capture_begin(fortai_cuda_q8_context *context) {
+    if (!context || context->graph || context->graph_exec) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaStreamBeginCapture(context->stream,
+        cudaStreamCaptureModeGlobal);
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(context, "begin CUDA graph capture", error);
+}
+
+extern "C" int fortai_cuda_q8_context_capture_end(fortai_cuda_q8_context *context) {
+    if (!context) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error = cudaStreamEndCapture(context->stream, &context->graph);
+    if (error == cudaSuccess)
+        error = cudaGraphInstantiate(&context->graph_exec, context->graph, nullptr, nullptr, 0);
+    if (error != cudaSuccess) {
+        if (context->graph_exec) cudaGraphExecDestroy(context->graph_exec);
+        if (context->graph) cudaGraphDestroy(context->graph);
+        context->graph_exec = nullptr;
+        context->graph = nullptr;
+        return fail(context, "end CUDA graph capture", error);
+    }
+    return FORTAI_CUDA_OK;
+}
+
+extern "C" int fortai_cuda_q8_context_graph_launch(fortai_cuda_q8_context *context) {
+    if (!context || !context->graph_exec) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaGraphLaunch(context->graph_exec, context->stream);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "launch CUDA graph", error);
+}
+
+extern "C" int fortai_cuda_q8_weights_upload(fortai_cuda_q8_context *context,
+    const void *host_weights, size_t weight_bytes, int rows, int width,
+    fortai_cuda_q8_weights **weights) {
+    if (width <= 0 || width % kBlockElems != 0) return FORTAI_CUDA_INVALID;
+    return upload_weights(context, host_weights, weight_bytes, rows, width, 0,
+        width / kBlockElems, weights);
+}
+
+extern "C" int fortai_cuda_q8_weights_upload_columns(fortai_cuda_q8_context *context,
+    const void *host_weights, size_t weight_bytes, int rows, int width, int first_block,
+    int block_count, fortai_cuda_q8_weights **weights) {
+    return upload_weights(context, host_weights, weight_bytes, rows, width, first_block,
+        block_count, weights);
+}
+
+extern "C" int fortai_cuda_q8_weights_destroy(fortai_cuda_q8_weights *weights) {
+    if (!weights) return FORTAI_CUDA_OK;
+    if (weights->context) cudaSetDevice(weights->context->device);
+    cudaFree(weights->data);
+    delete weights;
+    return FORTAI_CUDA_OK;
+}
+
+extern "C" int fortai_cuda_q8_weights_shape(const fortai_cuda_q8_weights *weights, int *rows,
+    int *width) {
+    if (!weights || !rows || !width) return FORTAI_CUDA_INVALID;
+    *rows = weights->rows;
+    *width = weights->width;
+    return FORTAI_CUDA_OK;
+}
+
+extern "C" int fortai_cuda_q8_device_buffer_create(fortai_cuda_q8_context *context, size_t bytes,
+    void **device_buffer) {
+    if (!context || !device_buffer || bytes == 0) return FORTAI_CUDA_INVALID;
+    *device_buffer = nullptr;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaMalloc(device_buffer, bytes);
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(context, "device buffer allocation", error);
+}
+
+extern "C" int fortai_cuda_q8_device_buffer_destroy(fortai_cuda_q8_context *context,
+    void *device_buffer) {
+    if (!context || !device_buffer) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaFree(device_buffer);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device buffer free", error);
+}
+
+extern "C" int fortai_cuda_q8_device_buffer_upload(fortai_cuda_q8_context *context,
+    void *device_buffer, const void *host_data, size_t bytes) {
+    if (!context || !device_buffer || !host_data || bytes == 0) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error = cudaMemcpyAsync(device_buffer, host_data, bytes, cudaMemcpyHostToDevice,
+        context->stream);
+    if (error == cudaSuccess) error = cudaStreamSynchronize(context->stream);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device upload", error);
+}
+
+extern "C" int fortai_cuda_q8_device_buffer_upload_ptr(fortai_cuda_q8_context *context,
+    void *device_buffer, const void *host_data, size_t bytes) {
+    if (!context || !device_buffer || !host_data || bytes == 0) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaMemcpyAsync(device_buffer, host_data, bytes,
+        cudaMemcpyHostToDevice, context->stream);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "async device upload", error);
+}
+
+extern "C" int fortai_cuda_q8_device_buffer_download(fortai_cuda_q8_context *context,
+    void *host_data, const void *device_buffer, size_t bytes) {
+    if (!context || !device_buffer || !host_data || bytes == 0) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error = cudaMemcpyAsync(host_data, device_buffer, bytes, cudaMemcpyDeviceToHost,
+        context->stream);
+    if (error == cudaSuccess) error = cudaStreamSynchronize(context->stream);
+    return finish(context, "device download", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_resident(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
+    float *kernel_ms) {
+    if (!owned(context, weights) || !device_activation || !device_output || !kernel_ms)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error = cudaEventRecord(context->start, context->stream);
+    if (error == cudaSuccess) {
+        const GemvParams p = single_params(context, weights, device_activation,
+            static_cast<float *>(device_output));
+        error = launch_gemv(context, p, kActQ8, kEpiPlain);
+    }
+    if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
+    if (error == cudaSuccess)
+        error = cudaEventElapsedTime(kernel_ms, context->start, context->stop);
+    return finish(context, "resident matvec", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_device_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *device_output, size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !device_output ||
+        activation_elements != static_cast<size_t>(weights->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(weights->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const GemvParams p = single_params(context, weights, device_activation,
+        static_cast<float *>(device_output));
+    const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPlain);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device F32 matvec", error);
+}
+
+extern "C" int fortai_cuda_qwen35_embedding_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, int64_t token_id, void *device_output,
+    size_t output_elements) {
+    if (!owned(context, weights) || !device_output || token_id < 0 ||
+        token_id >= weights->rows || output_elements < static_cast<size_t>(weights->width))
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    q8_dequantize_row_kernel<<<(weights->width + 255) / 256, 256, 0, context->stream>>>(
+        weights->data, token_id, weights->width, weights->row_stride,
+        static_cast<float *>(device_output));
+    ++context->launches;
+    const cudaError_t error = cudaGetLastError();
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device Q8 embedding", error);
+}
+
+extern "C" int fortai_cuda_qwen35_copy_device(fortai_cuda_q8_context *context,
+    const void *device_input, void *device_output, size_t bytes) {
+    if (!context || !device_input || !device_output || bytes == 0) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = cudaMemcpyAsync(device_output, device_input, bytes,
+        cudaMemcpyDeviceToDevice, context->stream);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device copy", error);
+}
+
+namespace {
+
+__global__ void add_kernel(const float *left, const float *right, float *output, int elements) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < elements) output[i] = left[i] + right[i];
+}
+
+// One CTA; squares are accumulated in double as in the reference
+// (qwen_rms_norm_float, backend.cu:518-537).
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const float *input, const float *weights, float *output, int elements,
+    float epsilon) {
+    __shared__ double partial[8];
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < elements; i += blockDim.x) {
+        const double v = static_cast<double>(input[i]);
+        sum += v * v;
+    }
+    for (int offset = 16; offset; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = sum;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < 8; ++w) total += partial[w];
+    const float inverse = 1.0f / sqrtf(static_cast<float>(total /
+        static_cast<double>(elements)) + epsilon);
+    for (int i = threadIdx.x; i < elements; i += blockDim.x)
+        output[i] = input[i] * inverse * weights[i];
+}
+
+}  // namespace
+
+extern "C" int fortai_cuda_qwen35_add_device(fortai_cuda_q8_context *context,
+    const void *device_left, const void *device_right, void *device_output, size_t elements) {
+    if (!context || !device_left || !device_right || !device_output || elements == 0 ||
+        elements > static_cast<size_t>(INT32_MAX)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    add_kernel<<<(static_cast<int>(elements) + 255) / 256, 256, 0, context->stream>>>(
+        static_cast<const float *>(device_left), static_cast<const float *>(device_right),
+        static_cast<float *>(device_output), static_cast<int>(elements));
+    ++context->launches;
+    const cudaError_t error = cudaGetLastError();
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device add", error);
+}
+
+extern "C" int fortai_cuda_qwen35_rms_norm_device(fortai_cuda_q8_context *context,
+    const void *device_input, const void *device_weights, void *device_output, size_t elements,
+    float epsilon) {
+    if (!context || !device_input || !device_weights || !device_output || elements == 0 ||
+        elements > static_cast<size_t>(INT32_MAX) || epsilon <= 0.0f)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    rms_norm_kernel<<<1, 256, 0, context->stream>>>(static_cast<const float *>(device_input),
+        static_cast<const float *>(device_weights), static_cast<float *>(device_output),
+        static_cast<int>(elements), epsilon);
+    ++context->launches;
+    const cudaError_t error = cudaGetLastError();
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device RMS norm", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_host(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *host_activation, size_t activation_bytes,
+    float *host_output, size_t output_bytes, float *elapsed_ms) {
+    if (!owned(context, weights) || !host_activation || !host_output || !elapsed_ms ||
+        activation_bytes < static_cast<size_t>(weights->blocks) * kBlockBytes ||
+        output_bytes < static_cast<size_t>(weights->rows) * sizeof(float))
+        return FORTAI_CUDA_INVALID;
+    const HostRequest request = {weights, host_output, output_bytes};
+    return matvec_host_many(context, &request, 1, host_activation, activation_bytes, elapsed_ms,
+        nullptr);
+}
+
+extern "C" int fortai_cuda_q8_matvec_host_pair(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *first_weights, const fortai_cuda_q8_weights *second_weights,
+    const void *host_activation, size_t activation_bytes, float *first_output,
+    size_t first_output_bytes, float *second_output, size_t second_output_bytes,
+    float *elapsed_ms) {
+    const HostRequest requests[] = {
+        {first_weights, first_output, first_output_bytes},
+        {second_weights, second_output, second_output_bytes}};
+    return matvec_host_many(context, requests, 2, host_activation, activation_bytes, elapsed_ms,
+        nullptr);
+}
+
+extern "C" int fortai_cuda_q8_matvec_host_triplet(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *first_weights, const fortai_cuda_q8_weights *second_weights,
+    const fortai_cuda_q8_weights *third_weights, const void *host_activation,
+    size_t activation_bytes, float *first_output, size_t first_output_bytes,
+    float *second_output, size_t second_output_bytes, float *third_output,
+    size_t third_output_bytes, float *elapsed_ms) {
+    const HostRequest requests[] = {
+        {first_weights, first_output, first_output_bytes},
+        {second_weights, second_output, second_output_bytes},
+        {third_weights, third_output, third_output_bytes}};
+    return matvec_host_many(context, requests, 3, host_activation, activation_bytes, elapsed_ms,
+        nullptr);
+}
+
+extern "C" int fortai_cuda_q8_matvec_host_triplet_contiguous(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *first_weights, const fortai_cuda_q8_weights *second_weights,
+    const fortai_cuda_q8_weights *third_weights, const void *host_activation,
+    size_t activation_bytes, float *host_output, size_t host_output_bytes, float *elapsed_ms) {
+    if (!first_weights || !second_weights || !third_weights || !host_output)
+        return FORTAI_CUDA_INVALID;
+    const size_t first_bytes = static_cast<size_t>(first_weights->rows) * sizeof(float);
+    const size_t second_bytes = static_cast<size_t>(second_weights->rows) * sizeof(float);
+    const size_t third_bytes = static_cast<size_t>(third_weights->rows) * sizeof(float);
+    if (host_output_bytes < first_bytes + second_bytes + third_bytes) return FORTAI_CUDA_INVALID;
+    const HostRequest requests[] = {
+        {first_weights, host_output, first_bytes},
+        {second_weights, host_output + first_weights->rows, second_bytes},
+        {third_weights, host_output + first_weights->rows + second_weights->rows, third_bytes}};
+    return matvec_host_many(context, requests, 3, host_activation, activation_bytes, elapsed_ms,
+        host_output);
+}
+
+extern "C" int fortai_cuda_q8_ffn_host(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *host_activation,
+    size_t activation_bytes, float *host_output, size_t output_bytes, float *elapsed_ms) {
+    if (!context || !gate_weights || !up_weights || !down_weights || !host_activation ||
+        !host_output || !elapsed_ms) return FORTAI_CUDA_INVALID;
+    if (!ffn_shapes_ok(context, gate_weights, up_weights, down_weights))
+        return FORTAI_CUDA_INVALID;
+    const size_t expected_activation = static_cast<size_t>(gate_weights->blocks) * kBlockBytes;
+    const size_t down_activation = static_cast<size_t>(down_weights->blocks) * kBlockBytes;
+    const size_t inner_bytes = static_cast<size_t>(gate_weights->rows) * sizeof(float);
+    const size_t expected_output = static_cast<size_t>(down_weights->rows) * sizeof(float);
+    if (activation_bytes < expected_activation || output_bytes < expected_output)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    // activation scratch: x's blocks, later overwritten by h's; output scratch:
+    // h (inner floats) followed by the result (hidden floats)
+    cudaError_t error = ensure_scratch(context, std::max(expected_activation, down_activation),
+        inner_bytes + expected_output);
+    if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(context->scratch_activation, host_activation,
+            expected_activation, cudaMemcpyHostToDevice, context->stream);
+    float *result = context->scratch_output + gate_weights->rows;
+    if (error == cudaSuccess)
+        error = enqueue_ffn(context, gate_weights, up_weights, down_weights,
+            context->scratch_activation, kActQ8, result);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(host_output, result, expected_output, cudaMemcpyDeviceToHost,
+            context->stream);
+    if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
+    if (error == cudaSuccess)
+        error = cudaEventElapsedTime(elapsed_ms, context->start, context->stop);
+    return finish(context, "Qwen FFN host", error);
+}
+
+extern "C" int fortai_cuda_q8_ffn_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation,
+    size_t activation_elements, void *device_output, size_t output_elements) {
+    if (!context || !gate_weights || !up_weights || !down_weights || !device_activation ||
+        !device_output) return FORTAI_CUDA_INVALID;
+    if (!ffn_shapes_ok(context, gate_weights, up_weights, down_weights) ||
+        activation_elements != static_cast<size_t>(gate_weights->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(down_weights->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error = ensure_scratch(context,
+        static_cast<size_t>(down_weights->blocks) * kBlockBytes,
+        static_cast<size_t>(gate_weights->rows) * sizeof(float));
+    if (error == cudaSuccess)
+        error = enqueue_ffn(context, gate_weights, up_weights, down_weights, device_activation,
+            kActF32, static_cast<float *>(device_output));
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "Qwen FFN device", error);
+}
+
+// --- gated-delta-net and attention layers: outside the Q8_0 matvec path -------
+extern "C" int fortai_cuda_qwen35_recurrent_create(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *,
+    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *,
+    const fortai_cuda_q8_weights *, const void *, size_t, int, int, const void *, size_t,
+    const void *, size_t, const void *, size_t, int, int, int, int, int, float,
+    fortai_cuda_qwen35_recurrent **layer) {
+    if (layer) *layer = nullptr;
+    if (!context || !layer) return FORTAI_CUDA_INVALID;
+    return not_built(context, "the Qwen3.5 recurrent layer");
+}
+extern "C" int fortai_cuda_qwen35_recurrent_destroy(fortai_cuda_qwen35_recurrent *layer) {
+    delete layer;
+    return FORTAI_CUDA_OK;
+}
+extern "C" int fortai_cuda_qwen35_recurrent_reset(fortai_cuda_qwen35_recurrent *layer) {
+    return layer ? not_built(layer->context, "the Qwen3.5 recurrent layer") : FORTAI_CUDA_INVALID;
+}
+extern "C" int fortai_cuda_qwen35_recurrent_run(fortai_cuda_qwen35_recurrent *layer, const void *,
+    size_t, float *, size_t, float *elapsed_ms) {
+    if (elapsed_ms) *elapsed_ms = 0.0f;
+    return layer ? not_built(layer->context, "the Qwen3.5 recurrent layer") : FORTAI_CUDA_INVALID;
+}
+extern "C" int fortai_cuda_qwen35_recurrent_run_device(fortai_cuda_qwen35_recurrent *layer,
+    const void *, size_t, void *, size_t) {
+    return layer ? not_built(layer->context, "the Qwen3.5 recurrent layer") : FORTAI_CUDA_INVALID;
+}
+extern "C" int fortai_cuda_qwen35_attention_create(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *,
+    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *, const void *, size_t,
+    const void *, size_t, int, int, int, int, int, int, float, float,
+    fortai_cuda_qwen35_attention **layer) {
+    if (layer) *layer = nullptr;
+    if (!context || !layer) return FORTAI_CUDA_INVALID;
+    return not_built(context, "the Qwen3.5 attention layer");
+}
+extern "C" int fortai_cuda_qwen35_attention_destroy(fortai_cuda_qwen35_attention *layer) {
+    delete layer;
+    return FORTAI_CUDA_OK;
+}
+extern "C" int fortai_cuda_qwen35_attention_reset(fortai_cuda_qwen35_attention *layer) {
+    return layer ? not_built(layer->context, "the Qwen3.5 attention layer") : FORTAI_CUDA_INVALID;
+}
+extern "C" int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attention *layer,
+    const void *, size_t, int, void *, size_t) {
+    return layer ? not_built(layer->context, "the Qwen3.5 attention layer") : FORTAI_CUDA_INVALID;
+}
+
+extern "C" const char *fortai_cuda_q8_last_error(const fortai_cuda_q8_context *context) {
+    return context ? context->error : "invalid CUDA Q8 context";
+}
+
+// ===========================================================================
+// Part 2: extensions
+// ===========================================================================
+extern "C" void *fortai_cuda_q8_context_stream(const fortai_cuda_q8_context *context) {
+    return context ? static_cast<void *>(context->stream) : nullptr;
+}
+
+extern "C" uint64_t fortai_cuda_q8_context_launch_count(const fortai_cuda_q8_context *context) {
+    return context ? context->launches : 0;
+}
+
+extern "C" int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context) {
+    if (!context) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    return finish(context, "synchronize", cudaStreamSynchronize(context->stream));
+}
+
+extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context,
+    const char *name, int value) {
+    if (!context || !name || value < 0) return FORTAI_CUDA_INVALID;
+    if (!std::strcmp(name, "gemv_variant") && value <= 2) context->gemv_variant = value;
+    else if (!std::strcmp(name, "gemv_ctas_per_sm") && value <= 32)
+        context->gemv_ctas_per_sm = value;
+    else if (!std::strcmp(name, "gemv_rows_per_warp") && value <= 2)
+        context->gemv_rows_per_warp = value;
+    else if (!std::strcmp(name, "ring_stages") && value <= kRingMaxStages)
+        context->ring_stages = value;
+    else if (!std::strcmp(name, "ring_rows") && value <= 256) context->ring_rows = value;
+    else if (!std::strcmp(name, "mmq_min_tokens")) context->mmq_min_tokens = value;
+    else return FORTAI_CUDA_INVALID;
+    return FORTAI_CUDA_OK;
+}
+
+extern "C" int fortai_cuda_q8_quantize_device(fortai_cuda_q8_context *context,
+    const void *device_input, size_t elements, void *device_output, size_t output_bytes) {
+    if (!context || !device_input || !device_output || elements == 0 ||
+        elements % kBlockElems != 0 || output_bytes < elements / kBlockElems * kBlockBytes)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const cudaError_t error = launch_quantize(context, static_cast<const float *>(device_input),
+        static_cast<uint8_t *>(device_output), elements / kBlockElems);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device Q8 quantize", error);
+}
+
+extern "C" int fortai_cuda_q8_block_dots_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
+    size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !device_output ||
+        output_elements < static_cast<size_t>(weights->rows) * weights->blocks)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const GemvParams p = single_params(context, weights, device_activation,
+        static_cast<float *>(device_output));
+    const cudaError_t error = launch_gemv(context, p, kActQ8, kEpiBlockDots);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "block dots", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const float *host_activation,
+    size_t activation_elements, float *host_output, size_t output_bytes, float *elapsed_ms) {
+    if (!owned(context, weights) || !host_activation || !host_output || !elapsed_ms ||
+        activation_elements != static_cast<size_t>(weights->blocks) * kBlockElems ||
+        output_bytes < static_cast<size_t>(weights->rows) * sizeof(float))
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const size_t in_bytes = activation_elements * sizeof(float);
+    const size_t out_bytes = static_cast<size_t>(weights->rows) * sizeof(float);
+    // the fp32 activation is parked in the activation scratch (4 bytes per element)
+    cudaError_t error = ensure_scratch(context, in_bytes, out_bytes);
+    if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(context->scratch_activation, host_activation, in_bytes,
+            cudaMemcpyHostToDevice, context->stream);
+    if (error == cudaSuccess) {
+        const GemvParams p = single_params(context, weights, context->scratch_activation,
+            context->scratch_output);
+        error = launch_gemv(context, p, kActF32, kEpiPlain);
+    }
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(host_output, context->scratch_output, out_bytes,
+            cudaMemcpyDeviceToHost, context->stream);
+    if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
+    if (error == cudaSuccess)
+        error = cudaEventElapsedTime(elapsed_ms, context->start, context->stop);
+    return finish(context, "host F32 matvec", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_outputs, int peer_count, size_t first_row,
+    size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !peer_outputs || peer_count <= 0 ||
+        peer_count > kMaxPeers ||
+        activation_elements != static_cast<size_t>(weights->blocks) * kBlockElems ||
+        first_row + static_cast<size_t>(weights->rows) > output_elements ||
+        output_elements > static_cast<size_t>(INT32_MAX)) return FORTAI_CUDA_INVALID;
+    for (int i = 0; i < peer_count; ++i)
+        if (!peer_outputs[i]) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    GemvParams p = single_params(context, weights, device_activation, nullptr);
+    for (int i = 0; i < peer_count; ++i) p.peer_outputs[i] = static_cast<float *>(peer_outputs[i]);
+    p.peers = peer_count;
+    p.first_row = static_cast<int>(first_row);
+    const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "peer-output matvec", error);
+}
+
+// ---------------------------------------------------------------------------
+// batched (prefill) product
+// ---------------------------------------------------------------------------
+namespace {
+
+// Small batches stay on the streaming kernel, one launch per token: the weights
+// of any projection short of the lm_head stay L2-resident between launches.
+cudaError_t enqueue_matmul_streaming(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
+    const void *activation, int act, int tokens, float *output) {
+    cudaError_t error = cudaSuccess;
+    const size_t act_stride = act == kActF32 ? static_cast<size_t>(w->width) * sizeof(float)
+                                             : static_cast<size_t>(w->blocks) * kBlockBytes;
+    for (int t = 0; t < tokens && error == cudaSuccess; ++t) {
+        const GemvParams p = single_params(c, w,
+            static_cast<const uint8_t *>(activation) + t * act_stride,
+            output + static_cast<size_t>(t) * w->rows);
+        error = launch_gemv(c, p, act, kEpiPlain);
+    }
+    return error;
+}
+
+}  // namespace
+
+extern "C" int fortai_cuda_q8_matmul_device_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !device_output || tokens <= 0 ||
+        output_elements < static_cast<size_t>(tokens) * weights->rows)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error;
+    if (mmq_supported(weights->rows, weights->width, tokens, context->mmq_min_tokens)) {
+        error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
+            &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data, weights->rows,
+            weights->width, weights->row_stride, device_activation, kActF32, tokens,
+            static_cast<float *>(device_output), nullptr,
+            reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
+            &context->launches);
+    } else {
+        error = enqueue_matmul_streaming(context, weights, device_activation, kActF32, tokens,
+            static_cast<float *>(device_output));
+    }
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device F32 matmul", error);
+}
+
+extern "C" int fortai_cuda_q8_matmul_resident(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, float *kernel_ms) {
+    if (!owned(context, weights) || !device_activation || !device_output || tokens <= 0 ||
+        !kernel_ms) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error = cudaSuccess;
+    const bool tensor = mmq_supported(weights->rows, weights->width, tokens,
+        context->mmq_min_tokens);
+    if (tensor)   // grow scratch before the timed region
+        error = mmq_reserve(reinterpret_cast<void **>(&context->scratch_aux),
+            &context->scratch_aux_bytes, weights->rows, weights->width, tokens);
+    if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
+    if (error == cudaSuccess) {
+        if (tensor)
+            error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
+                &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data,
+                weights->rows, weights->width, weights->row_stride, device_activation, kActQ8,
+                tokens, static_cast<float *>(device_output), nullptr,
+                reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
+                &context->launches);
+        else
+            error = enqueue_matmul_streaming(context, weights, device_activation, kActQ8, tokens,
+                static_cast<float *>(device_output));
+    }
+    if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
+    if (error == cudaSuccess)
+        error = cudaEventElapsedTime(kernel_ms, context->start, context->stop);
+    return finish(context, "resident matmul", error);
+}
+
+extern "C" int fortai_cuda_q8_matmul_host_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const float *host_activation, int tokens,
+    float *host_output, size_t output_bytes, float *elapsed_ms) {
+    if (!owned(context, weights) || !host_activation || !host_output || tokens <= 0 ||
+        !elapsed_ms ||
+        output_bytes < static_cast<size_t>(tokens) * weights->rows * sizeof(float))
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const size_t in_bytes = static_cast<size_t>(tokens) * weights->width * sizeof(float);
+    const size_t out_bytes = static_cast<size_t>(tokens) * weights->rows * sizeof(float);
+    const bool tensor = mmq_supported(weights->rows, weights->width, tokens,
+        context->mmq_min_tokens);
+    cudaError_t error = ensure_scratch(context, in_bytes, out_bytes);
+    if (error == cudaSuccess && tensor)
+        error = mmq_reserve(reinterpret_cast<void **>(&context->scratch_aux),
+            &context->scratch_aux_bytes, weights->rows, weights->width, tokens);
+    if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(context->scratch_activation, host_activation, in_bytes,
+            cudaMemcpyHostToDevice, context->stream);
+    if (error == cudaSuccess) {
+        if (tensor)
+            error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
+                &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data,
+                weights->rows, weights->width, weights->row_stride, context->scratch_activation,
+                kActF32, tokens, context->scratch_output, nullptr,
+                reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
+                &context->launches);
+        else
+            error = enqueue_matmul_streaming(context, weights, context->scratch_activation,
+                kActF32, tokens, context->scratch_output);
+    }
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(host_output, context->scratch_output, out_bytes,
+            cudaMemcpyDeviceToHost, context->stream);
+    if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
+    if (error == cudaSuccess)
+        error = cudaEventElapsedTime(elapsed_ms, context->start, context->stop);
+    return finish(context, "host F32 matmul", error);
+}
+
+extern "C" int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !device_output || tokens <= 0 ||
+        output_elements < static_cast<size_t>(tokens) * weights->rows * weights->blocks)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaError_t error;
+    if (mmq_supported(weights->rows, weights->width, tokens, context->mmq_min_tokens)) {
+        error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
+            &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data, weights->rows,
+            weights->width, weights->row_stride, device_activation, kActQ8, tokens, nullptr,
+            static_cast<int32_t *>(device_output),
+            reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
+            &context->launches);
+    } else {
+        error = cudaSuccess;
+        for (int t = 0; t < tokens && error == cudaSuccess; ++t) {
+            const GemvParams p = single_params(context, weights,
+                static_cast<const uint8_t *>(device_activation) +
+                    static_cast<size_t>(t) * weights->blocks * kBlockBytes,
+                reinterpret_cast<float *>(static_cast<int32_t *>(device_output) +
+                    static_cast<size_t>(t) * weights->rows * weights->blocks));
+            error = launch_gemv(context, p, kActQ8, kEpiBlockDots);
+        }
+    }
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "matmul block dots", error);
+}

@@ -1,0 +1,159 @@
+// Shared device helpers and the device-side weight layout of the Q8_0 backend.
+//
+// Host (GGUF) layout, as uploaded: rows x B blocks of 34 bytes, each block a
+// binary16 scale followed by 32 int8 quants (reference:
+// src/fortai_gguf_runtime.f90:312-318, 751-757).  Blocks are only 2-byte
+// aligned, which is why the reference kernels fetch weights with 2-byte loads
+// (backend/cuda/fortai_cuda_backend.cu:54-57).
+//
+// Device layout used here ("row-planar"): row r lives at r * row_stride bytes,
+//     [ K int8 quants | B binary16 scales | pad to a multiple of 16 ]
+// with row_stride = round_up(34 * B, 16).  The bytes per block are unchanged
+// (34), every row starts on a 16-byte boundary, quants can be fetched with
+// 16-byte vector loads or 1-D bulk copies, a row stays one contiguous burst for
+// the memory system, and both planes are addressable as 2-D tensor maps
+// (pitch = row_stride) by the tensor-core prefill kernel.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fortai_b200 {
+
+constexpr int kBlockElems = 32;
+constexpr int kBlockBytes = 34;
+constexpr int kSmCountB200 = 148;
+
+// Codes written to the context's device status word by kernels whose bounded
+// waits ran out.  Zero means no kernel gave up.
+enum DeviceStatus : int {
+    kStatusOk = 0,
+    kStatusRingProducerTimeout = 1,
+    kStatusRingConsumerTimeout = 2,
+    kStatusMmqLoadTimeout = 3,
+    kStatusMmqMmaTimeout = 4,
+    kStatusMmqDrainTimeout = 5,
+    kStatusPeerFlagTimeout = 6
+};
+
+__host__ __device__ inline size_t row_stride_bytes(int blocks) {
+    return (static_cast<size_t>(blocks) * kBlockBytes + 15) & ~static_cast<size_t>(15);
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint16_t bits) {
+    return __half2float(__ushort_as_half(bits));
+}
+
+// 16-byte streaming load: read-only path, no L1 allocation (each weight byte is
+// used exactly once per GEMV).
+__device__ __forceinline__ int4 ldg_stream_16(const void *address) {
+    int4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.s32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(address));
+    return v;
+}
+
+__device__ __forceinline__ uint16_t ldg_stream_u16(const void *address) {
+    uint16_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(address));
+    return v;
+}
+
+__device__ __forceinline__ int dot16(const int4 &w, const int4 &a) {
+    int d = __dp4a(w.x, a.x, 0);
+    d = __dp4a(w.y, a.y, d);
+    d = __dp4a(w.z, a.z, d);
+    return __dp4a(w.w, a.w, d);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+
+// silu(g) * u with the IEEE exponential and division (the reference CPU path
+// approximates expf to ~2e-7 relative; its own test tolerance is 2e-5,
+// test/test_fortai_smoke.f90:284-299).
+__device__ __forceinline__ float silu_mul(float gate, float up) {
+    return __fdiv_rn(gate, 1.0f + expf(-gate)) * up;
+}
+
+// ---- Q8_0 quantization of 32 floats held one per lane ----------------------
+// Bit-for-bit the arithmetic of the reference's AVX2 quantizer
+// (src/backend/cpu/fortai_q8_dot.c:153-198): amax over the block, scale =
+// amax / 127 (IEEE division) rounded to binary16 nearest-even, inverse =
+// 127 / amax (0 for an all-zero block), quant = round-half-even(x * inverse)
+// saturated to int8.  Returns the quant; *scale_bits gets the stored scale.
+__device__ __forceinline__ int quantize_lane(float x, uint16_t *scale_bits) {
+    float amax = fabsf(x);
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1)
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, offset));
+    const float scale = __fdiv_rn(amax, 127.0f);
+    const float inverse = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+    *scale_bits = __half_as_ushort(__float2half_rn(scale));
+    int q = __float2int_rn(__fmul_rn(x, inverse));
+    return max(-128, min(127, q));
+}
+
+// ---- mbarrier / bulk-copy primitives (sm_90+; used without clusters) -------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Wait for the phase of the given parity to complete, giving up after `limit`
+// probes (each probe itself blocks for a hardware-defined slice).  Returns false
+// on give-up so that the caller can record a status and leave; no wait in this
+// library spins without a bound.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity,
+    uint32_t limit = 1u << 22) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// 1-D bulk asynchronous copy global -> shared, completion counted in bytes on an
+// mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.  Always the
+// plain one-destination form: the copy lands in the issuing CTA's own shared memory.
+__device__ __forceinline__ void bulk_copy_g2s(void *smem_dst, const void *gmem_src,
+    uint32_t bytes, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+
+}  // namespace fortai_b200

@@ -1,0 +1,443 @@
+// Batch-1 Q8_0 x Q8_0 matrix-vector kernels for sm_100a.
+//
+// What they replace in the reference (backend/cuda/fortai_cuda_backend.cu):
+//   q8_gemv_one_warp :64-86, q8_gemv_four_warp :88-126, launch_q8 :139-147,
+//   q8_gemv_fused4 :149-190, q8_gemv_silu_product + qwen_silu_product :331-384,
+//   qwen_quantize_q8 :483-498 (folded into the GEMV prologue for fp32 input).
+//
+// Arithmetic (identical per block to the reference GPU kernels):
+//   dot_b  = sum_{i<32} qw[b][i] * qa[b][i]            exact int32 (dp4a)
+//   out    = sum_b fmaf(half(dw[b]) * half(da[b]), float(dot_b), acc)
+// Each lane owns 16-byte half-blocks; the two halves of a block sit in adjacent
+// lanes and are joined with one shuffle before the scale is applied, so the
+// value that gets scaled is the exact int32 block dot.  Lane partial sums are
+// combined with a butterfly; only the fp32 summation order differs from the CPU
+// path.
+//
+// This is HBM-streaming integer/byte work (about 1.9 int-ops per weight byte),
+// so no tensor cores: the design goal is bytes in flight.  Two variants:
+//   direct  persistent warps, each lane issues U 16-byte no-allocate loads per
+//           row before consuming any of them;
+//   ring    one producer thread per CTA feeds a shared-memory ring of row tiles
+//           with 1-D bulk asynchronous copies (the TMA engine) completed on
+//           mbarriers; eight consumer warps dequant-and-dot out of shared
+//           memory.  Every barrier wait is bounded and reports a status word.
+#pragma once
+
+#include "q8_common.cuh"
+
+namespace fortai_b200 {
+
+constexpr int kMaxSegments = 4;
+constexpr int kMaxPeers = 8;
+constexpr int kGemvWarps = 8;
+constexpr int kGemvThreads = kGemvWarps * 32;
+
+enum GemvEpilogue : int {
+    kEpiPlain = 0,      // out[row] = dot
+    kEpiSiluPair = 1,   // segments: 0 = gate, 1 = up; out[row] = silu(gate.x) * (up.x)
+    kEpiBlockDots = 2,  // int32 out[row * blocks + b] = exact block dot
+    kEpiPeers = 3       // plain, stored into every peer's output vector
+};
+
+enum ActivationKind : int {
+    kActQ8 = 0,   // width/32 blocks of 34 bytes (GGUF Q8_0)
+    kActF32 = 1   // width floats, quantized in the prologue
+};
+
+struct GemvParams {
+    const uint8_t *weights[kMaxSegments];
+    float *outputs[kMaxSegments];
+    int rows[kMaxSegments];
+    int segments;
+    int total_rows;
+    int width;
+    int blocks;
+    int row_stride;
+    const void *activation;
+    int *status;
+    float *peer_outputs[kMaxPeers];
+    int peers;
+    int first_row;  // element offset of this shard inside the peers' vectors
+};
+
+// Shared-memory image of the activation: `width` int8 quants, then `blocks`
+// floats holding half(da[b]).
+__host__ __device__ inline size_t activation_smem_bytes(int width, int blocks) {
+    return (static_cast<size_t>(width) + static_cast<size_t>(blocks) * 4 + 15) & ~size_t(15);
+}
+
+template <int ACT>
+__device__ __forceinline__ void stage_activation(const void *activation, int width, int blocks,
+    uint8_t *smem, int tid, int threads) {
+    int8_t *act_q = reinterpret_cast<int8_t *>(smem);
+    float *act_s = reinterpret_cast<float *>(smem + width);
+    if (ACT == kActQ8) {
+        // 17 two-byte words per block: word 0 is the scale, words 1..16 the quants.
+        const uint16_t *raw = static_cast<const uint16_t *>(activation);
+        uint16_t *act_q16 = reinterpret_cast<uint16_t *>(act_q);
+        const int words = blocks * 17;
+        for (int i = tid; i < words; i += threads) {
+            const int b = i / 17;
+            const int j = i - b * 17;
+            const uint16_t v = raw[i];
+            if (j == 0) act_s[b] = half_bits_to_float(v);
+            else act_q16[b * 16 + (j - 1)] = v;
+        }
+    } else {
+        const float *x = static_cast<const float *>(activation);
+        const int lane = tid & 31;
+        for (int b = tid >> 5; b < blocks; b += threads >> 5) {
+            uint16_t bits;
+            const int q = quantize_lane(x[b * kBlockElems + lane], &bits);
+            act_q[b * kBlockElems + lane] = static_cast<int8_t>(q);
+            if (lane == 0) act_s[b] = half_bits_to_float(bits);
+        }
+    }
+}
+
+// NR rows at once from global memory.  All 16-byte loads of a pass are issued
+// before the first one is consumed.
+template <int NR, int U, bool BLOCKDOTS>
+__device__ __forceinline__ void rows_dot_global(const uint8_t *const (&base)[NR],
+    const int4 *__restrict__ act_q, const float *__restrict__ act_s, int width, int nchunks,
+    int lane, float (&acc)[NR], int32_t *const (&dots)[NR]) {
+#pragma unroll
+    for (int r = 0; r < NR; ++r) acc[r] = 0.0f;
+    for (int c0 = 0; c0 < nchunks; c0 += 32 * U) {
+        int4 w[NR][U];
+        uint16_t d[NR][U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = c0 + u * 32 + lane;
+            const bool ok = idx < nchunks;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                if (ok) {
+                    w[r][u] = ldg_stream_16(base[r] + static_cast<size_t>(idx) * 16);
+                    d[r][u] = ldg_stream_u16(base[r] + width + (idx >> 1) * 2);
+                } else {
+                    w[r][u] = make_int4(0, 0, 0, 0);
+                    d[r][u] = 0;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int idx = c0 + u * 32 + lane;
+            const bool ok = idx < nchunks;
+            const int4 a = ok ? act_q[idx] : make_int4(0, 0, 0, 0);
+            const float sa = (ok && !(lane & 1)) ? act_s[idx >> 1] : 0.0f;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                int dot = dot16(w[r][u], a);
+                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+                acc[r] = fmaf(half_bits_to_float(d[r][u]) * sa, static_cast<float>(dot), acc[r]);
+                if (BLOCKDOTS && ok && !(lane & 1)) dots[r][idx >> 1] = dot;
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
+// direct variant
+// --------------------------------------------------------------------------
+template <int U, int NR, int ACT, int EPI>
+__global__ void __launch_bounds__(kGemvThreads)
+q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(16) uint8_t gemv_smem[];
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
+    __syncthreads();
+    const int4 *act_q = reinterpret_cast<const int4 *>(gemv_smem);
+    const float *act_s = reinterpret_cast<const float *>(gemv_smem + p.width);
+    const int lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
+    const int warps = gridDim.x * kGemvWarps;
+    const int nchunks = p.width >> 4;
+    const size_t stride = static_cast<size_t>(p.row_stride);
+
+    if (EPI == kEpiSiluPair) {
+        // NR is 2 here: the gate row and the up row of the same index.
+        for (int row = warp; row < p.total_rows; row += warps) {
+            const uint8_t *base[2] = {p.weights[0] + row * stride, p.weights[1] + row * stride};
+            int32_t *none[2] = {nullptr, nullptr};
+            float acc[2];
+            rows_dot_global<2, U, false>(base, act_q, act_s, p.width, nchunks, lane, acc, none);
+            const float gate = warp_sum(acc[0]);
+            const float up = warp_sum(acc[1]);
+            if (lane == 0) p.outputs[0][row] = silu_mul(gate, up);
+        }
+        return;
+    }
+
+    for (int first = warp * NR; first < p.total_rows; first += warps * NR) {
+        const uint8_t *base[NR];
+        float *out[NR];
+        int32_t *dots[NR];
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            int row = first + r;
+            if (row >= p.total_rows) row = first;  // duplicate work, no store
+            int seg = 0;
+            int local = row;
+            if (EPI == kEpiPlain) {
+#pragma unroll
+                for (int s = 0; s < kMaxSegments - 1; ++s)
+                    if (seg == s && s + 1 < p.segments && local >= p.rows[s]) {
+                        local -= p.rows[s];
+                        seg = s + 1;
+                    }
+            }
+            base[r] = p.weights[seg] + local * stride;
+            out[r] = p.outputs[seg] + local;
+            dots[r] = EPI == kEpiBlockDots
+                ? reinterpret_cast<int32_t *>(p.outputs[0]) + static_cast<size_t>(local) * p.blocks
+                : nullptr;
+        }
+        float acc[NR];
+        rows_dot_global<NR, U, EPI == kEpiBlockDots>(base, act_q, act_s, p.width, nchunks, lane,
+            acc, dots);
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const float total = warp_sum(acc[r]);
+            const int row = first + r;
+            if (lane == 0 && row < p.total_rows) {
+                if (EPI == kEpiPlain) {
+                    *out[r] = total;
+                } else if (EPI == kEpiPeers) {
+                    for (int peer = 0; peer < p.peers; ++peer)
+                        p.peer_outputs[peer][p.first_row + row] = total;
+                }
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
+// ring variant
+// --------------------------------------------------------------------------
+constexpr int kRingConsumerWarps = 8;
+constexpr int kRingThreads = (kRingConsumerWarps + 1) * 32;
+constexpr int kRingMaxStages = 16;
+
+struct RingConfig {
+    int stages;         // 2..kRingMaxStages
+    int rows_per_tile;  // rows of one matrix per stage
+    int stage_bytes;    // rows_per_tile * row_stride * (2 for the SiLU pair)
+    int tiles;          // ceil(total_rows / rows_per_tile)
+};
+
+__host__ __device__ inline size_t ring_smem_bytes(int width, int blocks, const RingConfig &cfg) {
+    size_t bytes = activation_smem_bytes(width, blocks);
+    bytes += 2 * kRingMaxStages * sizeof(uint64_t);
+    bytes = (bytes + 127) & ~size_t(127);
+    return bytes + static_cast<size_t>(cfg.stages) * cfg.stage_bytes;
+}
+
+__device__ __forceinline__ float row_dot_shared(const uint8_t *row, const int4 *act_q,
+    const float *act_s, int width, int nchunks, int lane) {
+    float acc = 0.0f;
+    const int passes = (nchunks + 31) >> 5;
+#pragma unroll 4
+    for (int pass = 0; pass < passes; ++pass) {
+        const int idx = pass * 32 + lane;
+        const bool ok = idx < nchunks;
+        const int safe = ok ? idx : 0;
+        const int4 w = *reinterpret_cast<const int4 *>(row + safe * 16);
+        const uint16_t d = *reinterpret_cast<const uint16_t *>(row + width + (safe >> 1) * 2);
+        const int4 a = act_q[safe];
+        const float sa = (ok && !(lane & 1)) ? act_s[safe >> 1] : 0.0f;
+        int dot = ok ? dot16(w, a) : 0;
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        acc = fmaf(half_bits_to_float(d) * sa, static_cast<float>(dot), acc);
+    }
+    return acc;
+}
+
+template <int ACT, int EPI>
+__global__ void __launch_bounds__(kRingThreads, 1)
+q8_gemv_ring_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ RingConfig cfg) {
+    extern __shared__ __align__(128) uint8_t ring_smem[];
+    const size_t act_bytes = activation_smem_bytes(p.width, p.blocks);
+    uint64_t *full = reinterpret_cast<uint64_t *>(ring_smem + act_bytes);
+    uint64_t *empty = full + kRingMaxStages;
+    uint8_t *stages = ring_smem +
+        ((act_bytes + 2 * kRingMaxStages * sizeof(uint64_t) + 127) & ~size_t(127));
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const size_t stride = static_cast<size_t>(p.row_stride);
+    const int copies = EPI == kEpiSiluPair ? 2 : 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < cfg.stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kRingConsumerWarps);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    // ---------------- producer: one thread drives the copy engine --------------
+    // It first arms every stage once (no waits are needed for the first lap), so
+    // weight tiles are in flight while the whole CTA stages the activation; only
+    // after the CTA-wide barrier does it enter the steady state, where each refill
+    // waits for the consumers to release the stage.
+    const bool producer = warp == kRingConsumerWarps && lane == 0;
+    int issued = 0;
+    int next_tile = blockIdx.x;
+    auto issue = [&](int tile, int s) {
+        const int first_row = tile * cfg.rows_per_tile;
+        const int rows = min(cfg.rows_per_tile, p.total_rows - first_row);
+        const uint32_t bytes = static_cast<uint32_t>(rows * stride);
+        uint8_t *dst = stages + static_cast<size_t>(s) * cfg.stage_bytes;
+        mbar_arrive_expect_tx(&full[s], bytes * copies);
+        bulk_copy_g2s(dst, p.weights[0] + first_row * stride, bytes, &full[s]);
+        if (copies == 2)
+            bulk_copy_g2s(dst + cfg.rows_per_tile * stride, p.weights[1] + first_row * stride,
+                bytes, &full[s]);
+    };
+    if (producer) {
+        for (; next_tile < cfg.tiles && issued < cfg.stages; next_tile += gridDim.x, ++issued)
+            issue(next_tile, issued);
+    }
+
+    stage_activation<ACT>(p.activation, p.width, p.blocks, ring_smem, threadIdx.x, kRingThreads);
+    __syncthreads();
+
+    if (producer) {
+        bool gave_up = false;
+        for (; next_tile < cfg.tiles; next_tile += gridDim.x, ++issued) {
+            const int s = issued % cfg.stages;
+            const int use = issued / cfg.stages;
+            if (!mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
+                atomicExch(p.status, kStatusRingProducerTimeout);
+                atomicExch(&abort_flag, 1);
+                gave_up = true;
+                break;
+            }
+            if (*reinterpret_cast<volatile int *>(&abort_flag)) {
+                gave_up = true;
+                break;
+            }
+            issue(next_tile, s);
+        }
+        if (gave_up) {
+            // Let copies that are still in flight land before the CTA's shared
+            // memory is released: wait (bounded) on the full barrier of every
+            // stage that was armed in the last lap.
+            const int lap = issued < cfg.stages ? issued : cfg.stages;
+            for (int k = 0; k < lap; ++k) {
+                const int n = issued - 1 - k;
+                mbar_wait_bounded(&full[n % cfg.stages], (n / cfg.stages) & 1, 1u << 16);
+            }
+        }
+    }
+
+    if (warp < kRingConsumerWarps) {
+        const int4 *act_q = reinterpret_cast<const int4 *>(ring_smem);
+        const float *act_s = reinterpret_cast<const float *>(ring_smem + p.width);
+        const int nchunks = p.width >> 4;
+        int consumed = 0;
+        for (int tile = blockIdx.x; tile < cfg.tiles; tile += gridDim.x, ++consumed) {
+            const int s = consumed % cfg.stages;
+            const int use = consumed / cfg.stages;
+            bool ready = true;
+            if (lane == 0) {
+                ready = mbar_wait_bounded(&full[s], use & 1);
+                if (!ready) {
+                    atomicExch(p.status, kStatusRingConsumerTimeout);
+                    atomicExch(&abort_flag, 1);
+                }
+            }
+            ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+            if (!ready || *reinterpret_cast<volatile int *>(&abort_flag)) break;
+            // lane 0 observed the phase; the others re-check once, which returns
+            // at once and gives each lane its own acquire of the copied bytes
+            mbar_wait_bounded(&full[s], use & 1, 1u << 10);
+            const uint8_t *tile_base = stages + static_cast<size_t>(s) * cfg.stage_bytes;
+            const int first_row = tile * cfg.rows_per_tile;
+            const int rows = min(cfg.rows_per_tile, p.total_rows - first_row);
+            for (int r = warp; r < rows; r += kRingConsumerWarps) {
+                const float a0 = warp_sum(row_dot_shared(tile_base + r * stride, act_q, act_s,
+                    p.width, nchunks, lane));
+                if (EPI == kEpiSiluPair) {
+                    const float a1 = warp_sum(row_dot_shared(
+                        tile_base + (cfg.rows_per_tile + r) * stride, act_q, act_s, p.width,
+                        nchunks, lane));
+                    if (lane == 0) p.outputs[0][first_row + r] = silu_mul(a0, a1);
+                } else if (EPI == kEpiPeers) {
+                    if (lane == 0)
+                        for (int peer = 0; peer < p.peers; ++peer)
+                            p.peer_outputs[peer][p.first_row + first_row + r] = a0;
+                } else {
+                    if (lane == 0) p.outputs[0][first_row + r] = a0;
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
+// standalone quantizer: one warp per block of 32 floats
+// --------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+q8_quantize_kernel(const float *__restrict__ input, uint8_t *__restrict__ output, long long blocks) {
+    const int lane = threadIdx.x & 31;
+    const long long warp = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    const long long warps = static_cast<long long>(gridDim.x) * 8;
+    for (long long b = warp; b < blocks; b += warps) {
+        uint16_t bits;
+        const int q = quantize_lane(input[b * kBlockElems + lane], &bits);
+        uint8_t *dst = output + b * kBlockBytes;
+        dst[2 + lane] = static_cast<uint8_t>(q);
+        if (lane == 0) *reinterpret_cast<uint16_t *>(dst) = bits;
+    }
+}
+
+// --------------------------------------------------------------------------
+// upload-time re-layout: GGUF blocks -> row-planar device rows
+// --------------------------------------------------------------------------
+// One thread per (row, block) of the destination.  src_blocks is the block count
+// of a full source row; [first_block, first_block + blocks) is the slice kept.
+__global__ void __launch_bounds__(256)
+q8_repack_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, int rows,
+    int src_blocks, int first_block, int blocks, int row_stride) {
+    const long long total = static_cast<long long>(rows) * blocks;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int row = static_cast<int>(i / blocks);
+        const int b = static_cast<int>(i - static_cast<long long>(row) * blocks);
+        const uint16_t *in = reinterpret_cast<const uint16_t *>(
+            src + (static_cast<size_t>(row) * src_blocks + first_block + b) * kBlockBytes);
+        uint8_t *out_row = dst + static_cast<size_t>(row) * row_stride;
+        uint32_t q[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            q[k] = static_cast<uint32_t>(in[1 + 2 * k]) |
+                (static_cast<uint32_t>(in[2 + 2 * k]) << 16);
+        uint4 *out_q = reinterpret_cast<uint4 *>(out_row + b * kBlockElems);
+        out_q[0] = make_uint4(q[0], q[1], q[2], q[3]);
+        out_q[1] = make_uint4(q[4], q[5], q[6], q[7]);
+        reinterpret_cast<uint16_t *>(out_row + blocks * kBlockElems)[b] = in[0];
+    }
+}
+
+// Dequantize one row of a row-planar matrix (embedding lookup; reference
+// qwen_embedding_lookup_q8, backend.cu:500-510).
+__global__ void __launch_bounds__(256)
+q8_dequantize_row_kernel(const uint8_t *__restrict__ weights, long long row, int width,
+    int row_stride, float *__restrict__ output) {
+    const int index = blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= width) return;
+    const uint8_t *base = weights + static_cast<size_t>(row) * row_stride;
+    const float scale = half_bits_to_float(
+        reinterpret_cast<const uint16_t *>(base + width)[index >> 5]);
+    output[index] = scale * static_cast<float>(static_cast<int8_t>(base[index]));
+}
+
+}  // namespace fortai_b200

@@ -1,0 +1,267 @@
+/* C ABI of the B200 (sm_100a) Q8_0 backend.
+ *
+ * Part 1 declares, symbol for symbol, the interface that the reference's
+ * Fortran wrapper binds with ISO_C_BINDING (reference:
+ * backend/cuda/fortai_cuda_backend.h:22-152, bound at
+ * src/backend/cuda/fortai_backend_cuda.f90:67-414).  A program that links the
+ * reference backend object links this library instead without source changes.
+ *
+ * Part 2 declares entry points that the reference does not have (batched
+ * prefill, fp32 host convenience calls, shard uploads, peer-output GEMV,
+ * parity probes).  They follow the same conventions.
+ *
+ * Conventions (reference: backend/cuda/fortai_cuda_backend.cu:42-52, 805-850):
+ *  - every function returns FORTAI_CUDA_OK, FORTAI_CUDA_INVALID (bad argument or
+ *    shape; nothing was enqueued) or FORTAI_CUDA_RUNTIME_ERROR (a CUDA call or a
+ *    device-side wait failed; fortai_cuda_q8_last_error gives the text);
+ *  - a context owns one device, one stream, its events and its scratch; it is
+ *    not thread-safe; weights and layer handles belong to the context that made
+ *    them and must be destroyed before it;
+ *  - "host" calls block until the result is in host memory; "device" calls only
+ *    enqueue on the context's stream;
+ *  - a Q8_0 block is 34 bytes: little-endian binary16 scale, then 32 int8.
+ *    Weight matrices arrive as rows x (width/32) blocks, row-major.  The device
+ *    copy is re-laid-out at upload (the handle is opaque), so a weights handle
+ *    cannot be reinterpreted as raw GGUF bytes on the device.
+ */
+#ifndef FORTAI_CUDA_BACKEND_B200_H
+#define FORTAI_CUDA_BACKEND_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fortai_cuda_q8_context fortai_cuda_q8_context;
+typedef struct fortai_cuda_q8_weights fortai_cuda_q8_weights;
+typedef struct fortai_cuda_qwen35_recurrent fortai_cuda_qwen35_recurrent;
+typedef struct fortai_cuda_qwen35_attention fortai_cuda_qwen35_attention;
+
+#ifndef FORTAI_CUDA_BACKEND_H   /* the reference header defines the same values */
+enum {
+    FORTAI_CUDA_OK = 0,
+    FORTAI_CUDA_INVALID = 1,
+    FORTAI_CUDA_RUNTIME_ERROR = 2
+};
+#endif
+
+/* ======================================================================= *
+ * Part 1 - the reference interface                                          *
+ * ======================================================================= */
+
+/* reference header :22-23, implementation backend.cu:805-850 */
+int fortai_cuda_q8_context_create(int device, fortai_cuda_q8_context **context);
+int fortai_cuda_q8_context_destroy(fortai_cuda_q8_context *context);
+
+/* reference header :24-27, backend.cu:852-893 (device-side position word and
+ * CUDA-graph capture of the context's stream) */
+int fortai_cuda_q8_context_set_position(fortai_cuda_q8_context *context, int position);
+int fortai_cuda_q8_context_capture_begin(fortai_cuda_q8_context *context);
+int fortai_cuda_q8_context_capture_end(fortai_cuda_q8_context *context);
+int fortai_cuda_q8_context_graph_launch(fortai_cuda_q8_context *context);
+
+/* reference header :29-32, backend.cu:895-931.  host_weights holds at least
+ * rows * (width/32) * 34 bytes in GGUF Q8_0 order; width % 32 == 0. */
+int fortai_cuda_q8_weights_upload(fortai_cuda_q8_context *context, const void *host_weights,
+    size_t weight_bytes, int rows, int width, fortai_cuda_q8_weights **weights);
+int fortai_cuda_q8_weights_destroy(fortai_cuda_q8_weights *weights);
+
+/* reference header :36-45, backend.cu:933-990.  upload and download block;
+ * upload_ptr only enqueues the copy. */
+int fortai_cuda_q8_device_buffer_create(fortai_cuda_q8_context *context, size_t bytes,
+    void **device_buffer);
+int fortai_cuda_q8_device_buffer_destroy(fortai_cuda_q8_context *context, void *device_buffer);
+int fortai_cuda_q8_device_buffer_upload(fortai_cuda_q8_context *context, void *device_buffer,
+    const void *host_data, size_t bytes);
+int fortai_cuda_q8_device_buffer_upload_ptr(fortai_cuda_q8_context *context, void *device_buffer,
+    const void *host_data, size_t bytes);
+int fortai_cuda_q8_device_buffer_download(fortai_cuda_q8_context *context, void *host_data,
+    const void *device_buffer, size_t bytes);
+
+/* reference header :49-51, backend.cu:992-1011.  device_activation is a Q8_0
+ * vector (width/32 blocks of 34 bytes) in device memory; device_output receives
+ * `rows` floats; blocks until done; kernel_ms is the kernel alone. */
+int fortai_cuda_q8_matvec_resident(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
+    float *kernel_ms);
+
+/* reference header :52-54, backend.cu:1013-1039.  fp32 activation in device
+ * memory; quantization to Q8_0 happens on the device; enqueue only. */
+int fortai_cuda_q8_matvec_device_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *device_output, size_t output_elements);
+
+/* reference header :55-57, backend.cu:1041-1055: dequantize one weight row. */
+int fortai_cuda_qwen35_embedding_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, int64_t token_id, void *device_output,
+    size_t output_elements);
+
+/* reference header :59-67, backend.cu:1057-1095 */
+int fortai_cuda_qwen35_copy_device(fortai_cuda_q8_context *context, const void *device_input,
+    void *device_output, size_t bytes);
+int fortai_cuda_qwen35_add_device(fortai_cuda_q8_context *context, const void *device_left,
+    const void *device_right, void *device_output, size_t elements);
+int fortai_cuda_qwen35_rms_norm_device(fortai_cuda_q8_context *context, const void *device_input,
+    const void *device_weights, void *device_output, size_t elements, float epsilon);
+
+/* reference header :72-75, backend.cu:1097-1129.  Q8_0 activation and fp32
+ * output live in host memory; elapsed_ms includes both transfers. */
+int fortai_cuda_q8_matvec_host(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *host_activation, size_t activation_bytes,
+    float *host_output, size_t output_bytes, float *elapsed_ms);
+
+/* reference header :79-100, backend.cu:249-315, 1131-1187.  One activation
+ * upload, several matrices with the same width.  The contiguous form returns
+ * the three outputs back to back and is accepted only for width < 4096, the
+ * condition under which the reference fuses them (backend.cu:257-258). */
+int fortai_cuda_q8_matvec_host_pair(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *first_weights, const fortai_cuda_q8_weights *second_weights,
+    const void *host_activation, size_t activation_bytes, float *first_output,
+    size_t first_output_bytes, float *second_output, size_t second_output_bytes,
+    float *elapsed_ms);
+int fortai_cuda_q8_matvec_host_triplet(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *first_weights, const fortai_cuda_q8_weights *second_weights,
+    const fortai_cuda_q8_weights *third_weights, const void *host_activation,
+    size_t activation_bytes, float *first_output, size_t first_output_bytes,
+    float *second_output, size_t second_output_bytes, float *third_output,
+    size_t third_output_bytes, float *elapsed_ms);
+int fortai_cuda_q8_matvec_host_triplet_contiguous(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *first_weights, const fortai_cuda_q8_weights *second_weights,
+    const fortai_cuda_q8_weights *third_weights, const void *host_activation,
+    size_t activation_bytes, float *host_output, size_t host_output_bytes, float *elapsed_ms);
+
+/* reference header :102-114, backend.cu:1189-1296.  out = down * Q8(silu(gate*x) .* (up*x));
+ * gate and up are inner x hidden, down is hidden_out x inner. */
+int fortai_cuda_q8_ffn_host(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *host_activation,
+    size_t activation_bytes, float *host_output, size_t output_bytes, float *elapsed_ms);
+int fortai_cuda_q8_ffn_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation,
+    size_t activation_elements, void *device_output, size_t output_elements);
+
+/* reference header :120-139, backend.cu:1298-1567 (gated-delta-net layer) */
+int fortai_cuda_qwen35_recurrent_create(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *qkv_weights, const fortai_cuda_q8_weights *gate_weights,
+    const fortai_cuda_q8_weights *alpha_weights, const fortai_cuda_q8_weights *beta_weights,
+    const fortai_cuda_q8_weights *output_weights, const void *conv_weights,
+    size_t conv_weight_bytes, int conv_size, int conv_kernel, const void *ssm_a,
+    size_t ssm_a_bytes, const void *ssm_dt, size_t ssm_dt_bytes, const void *ssm_norm,
+    size_t ssm_norm_bytes, int state_size, int key_heads, int value_heads, int head_size,
+    int inner_size, float norm_epsilon, fortai_cuda_qwen35_recurrent **layer);
+int fortai_cuda_qwen35_recurrent_destroy(fortai_cuda_qwen35_recurrent *layer);
+int fortai_cuda_qwen35_recurrent_reset(fortai_cuda_qwen35_recurrent *layer);
+int fortai_cuda_qwen35_recurrent_run(fortai_cuda_qwen35_recurrent *layer,
+    const void *host_activation, size_t activation_bytes, float *host_output,
+    size_t output_bytes, float *elapsed_ms);
+int fortai_cuda_qwen35_recurrent_run_device(fortai_cuda_qwen35_recurrent *layer,
+    const void *device_activation, size_t activation_elements, void *device_output,
+    size_t output_elements);
+
+/* reference header :141-154, backend.cu:1569-1731 (single-query attention layer) */
+int fortai_cuda_qwen35_attention_create(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *query_weights, const fortai_cuda_q8_weights *key_weights,
+    const fortai_cuda_q8_weights *value_weights, const fortai_cuda_q8_weights *output_weights,
+    const void *query_norm, size_t query_norm_bytes, const void *key_norm,
+    size_t key_norm_bytes, int heads, int key_value_heads, int head_size, int value_size,
+    int max_context, int rope_dimension, float rope_base, float norm_epsilon,
+    fortai_cuda_qwen35_attention **layer);
+int fortai_cuda_qwen35_attention_destroy(fortai_cuda_qwen35_attention *layer);
+int fortai_cuda_qwen35_attention_reset(fortai_cuda_qwen35_attention *layer);
+int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attention *layer,
+    const void *device_activation, size_t activation_elements, int position,
+    void *device_output, size_t output_elements);
+
+/* reference header :156, backend.cu:1733-1736 */
+const char *fortai_cuda_q8_last_error(const fortai_cuda_q8_context *context);
+
+/* ======================================================================= *
+ * Part 2 - entry points without a counterpart in the reference              *
+ * ======================================================================= */
+
+/* Context on a stream the caller owns (cudaStream_t passed as void*; NULL is
+ * the legacy default stream).  Lets a host that already has a stream - for
+ * example one that also carries NCCL collectives - order this backend's work
+ * on it.  The stream is borrowed, never destroyed here. */
+int fortai_cuda_q8_context_create_on_stream(int device, void *stream,
+    fortai_cuda_q8_context **context);
+/* The context's stream as a cudaStream_t. */
+void *fortai_cuda_q8_context_stream(const fortai_cuda_q8_context *context);
+/* Kernels launched through this context since it was created. */
+uint64_t fortai_cuda_q8_context_launch_count(const fortai_cuda_q8_context *context);
+/* Blocks until the stream is idle, then reports any device-side wait that gave
+ * up (bounded mbarrier waits in the staged kernels) as RUNTIME_ERROR. */
+int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context);
+/* Tuning knobs, by name: "gemv_variant" (0 = automatic, 1 = direct vector loads,
+ * 2 = bulk-copy ring), "gemv_ctas_per_sm", "ring_stages", "ring_rows",
+ * "mmq_min_tokens".  Unknown names return INVALID. */
+int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context, const char *name,
+    int value);
+
+/* Shape of a weights handle. */
+int fortai_cuda_q8_weights_shape(const fortai_cuda_q8_weights *weights, int *rows, int *width);
+
+/* Upload only blocks [first_block, first_block + block_count) of every row of a
+ * rows x width host matrix: the K-slice that one rank of a column-sharded
+ * (reduce-after) projection owns.  The handle reports width = 32 * block_count. */
+int fortai_cuda_q8_weights_upload_columns(fortai_cuda_q8_context *context,
+    const void *host_weights, size_t weight_bytes, int rows, int width, int first_block,
+    int block_count, fortai_cuda_q8_weights **weights);
+
+/* fp32 -> Q8_0 on the device: `elements` floats (a multiple of 32) become
+ * elements/32 blocks of 34 bytes, byte-identical to the reference CPU quantizer
+ * (src/backend/cpu/fortai_q8_dot.c:153-198).  Enqueue only. */
+int fortai_cuda_q8_quantize_device(fortai_cuda_q8_context *context, const void *device_input,
+    size_t elements, void *device_output, size_t output_bytes);
+
+/* Parity probe: the exact int32 dot of every (row, block) pair, rows x (width/32)
+ * values, produced by the same inner loop as the GEMV.  Enqueue only. */
+int fortai_cuda_q8_block_dots_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
+    size_t output_elements);
+
+/* Host fp32 in, host fp32 out: H2D of `activation_elements` floats, quantize and
+ * GEMV in one kernel, D2H of `rows` floats; blocks; elapsed_ms covers all of it. */
+int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const float *host_activation,
+    size_t activation_elements, float *host_output, size_t output_bytes, float *elapsed_ms);
+
+/* Batched product for multi-token prefill: `tokens` rows of `width` floats in,
+ * tokens x rows floats out (token-major: out[t * rows + r]).  Each token row is
+ * quantized to Q8_0 exactly as a single activation would be.  Enqueue only. */
+int fortai_cuda_q8_matmul_device_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, size_t output_elements);
+/* Same with a pre-quantized activation (tokens x width/32 blocks of 34 bytes);
+ * blocks; kernel_ms is the product kernel alone. */
+int fortai_cuda_q8_matmul_resident(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, float *kernel_ms);
+/* Host fp32 in/out form of the batched product; blocks. */
+int fortai_cuda_q8_matmul_host_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const float *host_activation, int tokens,
+    float *host_output, size_t output_bytes, float *elapsed_ms);
+/* Parity probe for the batched path: int32 dot of every (token, row, block),
+ * out[(t * rows + r) * blocks + b], taken from the tensor-core accumulators. */
+int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, size_t output_elements);
+
+/* Row-sharded GEMV whose epilogue stores this rank's slice into every rank's
+ * output vector: peer_outputs[p] is rank p's full-length output buffer (device
+ * pointers valid on this device, e.g. from symmetric memory); the slice is
+ * written at element offset `first_row`.  Enqueue only; the caller provides the
+ * cross-rank barrier before the outputs are read. */
+int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_outputs, int peer_count, size_t first_row,
+    size_t output_elements);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif
