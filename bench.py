@@ -42,6 +42,12 @@ FALLBACK_HBM_GBS = 6650.0
 GEMV_DRAM_TRAFFIC_BYTES = None
 
 
+def set_rows(rows: int) -> None:
+    global ROWS, WEIGHT_BYTES
+    ROWS = int(rows)
+    WEIGHT_BYTES = ROWS * BLOCKS * 34
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -320,6 +326,15 @@ def run_gpu_arm(args):
     torch.cuda.synchronize()
     kernel_ms = start.elapsed_time(stop) / k_iters
 
+    if args.kernel_only:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"kernel_only": True, "rows": ROWS, "kernel_ms": kernel_ms,
+                              "weight_gbs": my_rows * BLOCKS * 34 / kernel_ms / 1e6,
+                              "ms_per_step": elapsed_ms / args.steps}), flush=True)
+        ctx_cleanup(weights, ctx, dist)
+        return 0
+
     # ---- end to end through the host-buffer entry point, pinned buffers
     host_x = torch.empty(WIDTH, dtype=torch.float32).pin_memory()
     host_x.copy_(x.cpu())
@@ -444,7 +459,12 @@ def main():
     parser.add_argument("--steps", type=int, default=20000)
     parser.add_argument("--warmup", type=int, default=200)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--rows", type=int, default=ROWS,
+                        help="row count of the GEMV (smaller cases are for profiler captures)")
+    parser.add_argument("--kernel-only", action="store_true",
+                        help="skip the e2e, prefill and CPU legs (profiler captures)")
     args = parser.parse_args()
+    set_rows(args.rows)
     if args.impl == "reference":
         return run_reference_arm(args)
     return run_gpu_arm(args)

@@ -185,6 +185,52 @@ cudaError_t launch_direct(fortai_cuda_q8_context *c, const GemvParams &p) {
                               : launch_direct_instance<8, 1, ACT, EPI>(c, p);
 }
 
+template <int P, int NR, int ACT, int EPI>
+cudaError_t launch_block_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
+    auto kernel = q8_gemv_block_kernel<P, NR, ACT, EPI>;
+    const size_t smem = activation_smem_bytes(p.width, p.blocks);
+    cudaError_t error = cudaSuccess;
+    if (smem > 48 * 1024) {
+        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            static_cast<int>(smem));
+        if (error != cudaSuccess) return error;
+    }
+    int per_sm = c->gemv_ctas_per_sm;
+    if (per_sm <= 0) {
+        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem);
+        if (error != cudaSuccess) return error;
+        if (per_sm < 1) per_sm = 1;
+    }
+    const int rows_per_cta = kGemvWarps * (EPI == kEpiSiluPair ? 1 : NR);
+    const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
+    const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
+    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+template <int NR, int ACT, int EPI>
+cudaError_t launch_block_passes(fortai_cuda_q8_context *c, const GemvParams &p) {
+    switch ((p.blocks + 31) / 32) {
+    case 1: return launch_block_instance<1, NR, ACT, EPI>(c, p);
+    case 2: return launch_block_instance<2, NR, ACT, EPI>(c, p);
+    case 3: return launch_block_instance<3, NR, ACT, EPI>(c, p);
+    case 4: return launch_block_instance<4, NR, ACT, EPI>(c, p);
+    default: return launch_block_instance<0, NR, ACT, EPI>(c, p);
+    }
+}
+
+template <int ACT, int EPI>
+cudaError_t launch_block(fortai_cuda_q8_context *c, const GemvParams &p) {
+    if (EPI == kEpiSiluPair || EPI == kEpiBlockDots || EPI == kEpiPeers)
+        return launch_block_passes<1, ACT, EPI>(c, p);
+    const int passes = (p.blocks + 31) / 32;
+    int rows_per_warp = c->gemv_rows_per_warp;
+    if (rows_per_warp <= 0) rows_per_warp = passes <= 2 ? 2 : 1;
+    return rows_per_warp == 2 ? launch_block_passes<2, ACT, kEpiPlain>(c, p)
+                              : launch_block_passes<1, ACT, kEpiPlain>(c, p);
+}
+
 bool ring_plan(const fortai_cuda_q8_context *c, const GemvParams &p, int epi, RingConfig *cfg) {
     const int copies = epi == kEpiSiluPair ? 2 : 1;
     const size_t stride = static_cast<size_t>(p.row_stride);
@@ -225,25 +271,28 @@ cudaError_t launch_ring(fortai_cuda_q8_context *c, const GemvParams &p, const Ri
 bool want_ring(const fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
     if (epi == kEpiBlockDots) return false;
     if (epi == kEpiPlain && p.segments != 1) return false;
-    if (c->gemv_variant == 1) return false;
-    if (c->gemv_variant == 2) return true;
-    return false;
+    return c->gemv_variant == 2;
 }
 
 template <int ACT>
 cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
     RingConfig cfg;
     const bool ring = want_ring(c, p, epi) && ring_plan(c, p, epi, &cfg);
+    const bool half_block = c->gemv_variant == 1;   // the 16-byte-per-lane kernel
     switch (epi) {
     case kEpiPlain:
-        return ring ? launch_ring<ACT, kEpiPlain>(c, p, cfg) : launch_direct<ACT, kEpiPlain>(c, p);
+        if (ring) return launch_ring<ACT, kEpiPlain>(c, p, cfg);
+        return half_block ? launch_direct<ACT, kEpiPlain>(c, p) : launch_block<ACT, kEpiPlain>(c, p);
     case kEpiSiluPair:
-        return ring ? launch_ring<ACT, kEpiSiluPair>(c, p, cfg)
-                    : launch_direct<ACT, kEpiSiluPair>(c, p);
+        if (ring) return launch_ring<ACT, kEpiSiluPair>(c, p, cfg);
+        return half_block ? launch_direct<ACT, kEpiSiluPair>(c, p)
+                          : launch_block<ACT, kEpiSiluPair>(c, p);
     case kEpiPeers:
-        return ring ? launch_ring<ACT, kEpiPeers>(c, p, cfg) : launch_direct<ACT, kEpiPeers>(c, p);
+        if (ring) return launch_ring<ACT, kEpiPeers>(c, p, cfg);
+        return half_block ? launch_direct<ACT, kEpiPeers>(c, p) : launch_block<ACT, kEpiPeers>(c, p);
     default:
-        return launch_direct<kActQ8, kEpiBlockDots>(c, p);
+        return half_block ? launch_direct<kActQ8, kEpiBlockDots>(c, p)
+                          : launch_block<kActQ8, kEpiBlockDots>(c, p);
     }
 }
 
@@ -923,7 +972,7 @@ extern "C" int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *contex
 extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context,
     const char *name, int value) {
     if (!context || !name || value < 0) return FORTAI_CUDA_INVALID;
-    if (!std::strcmp(name, "gemv_variant") && value <= 2) context->gemv_variant = value;
+    if (!std::strcmp(name, "gemv_variant") && value <= 3) context->gemv_variant = value;
     else if (!std::strcmp(name, "gemv_ctas_per_sm") && value <= 32)
         context->gemv_ctas_per_sm = value;
     else if (!std::strcmp(name, "gemv_rows_per_warp") && value <= 2)

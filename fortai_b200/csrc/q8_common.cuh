@@ -7,10 +7,10 @@
 // (backend/cuda/fortai_cuda_backend.cu:54-57).
 //
 // Device layout used here ("row-planar"): row r lives at r * row_stride bytes,
-//     [ K int8 quants | B binary16 scales | pad to a multiple of 16 ]
-// with row_stride = round_up(34 * B, 16).  The bytes per block are unchanged
-// (34), every row starts on a 16-byte boundary, quants can be fetched with
-// 16-byte vector loads or 1-D bulk copies, a row stays one contiguous burst for
+//     [ K int8 quants | B binary16 scales | pad to a multiple of 32 ]
+// with row_stride = round_up(34 * B, 32).  The bytes per block are unchanged
+// (34), every row and every block starts on a 32-byte boundary, quants can be fetched with
+// 16- or 32-byte vector loads or 1-D bulk copies, a row stays one contiguous burst for
 // the memory system, and both planes are addressable as 2-D tensor maps
 // (pitch = row_stride) by the tensor-core prefill kernel.
 #pragma once
@@ -38,7 +38,7 @@ enum DeviceStatus : int {
 };
 
 __host__ __device__ inline size_t row_stride_bytes(int blocks) {
-    return (static_cast<size_t>(blocks) * kBlockBytes + 15) & ~static_cast<size_t>(15);
+    return (static_cast<size_t>(blocks) * kBlockBytes + 31) & ~static_cast<size_t>(31);
 }
 
 __device__ __forceinline__ float half_bits_to_float(uint16_t bits) {

@@ -214,6 +214,187 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
 }
 
 // --------------------------------------------------------------------------
+// block-per-lane variant: one 32-byte load fetches a whole Q8_0 block
+// --------------------------------------------------------------------------
+// Lane l owns blocks l, l + 32, ... of a row, so every int32 block dot is formed
+// inside one lane (eight dp4a) and no shuffle is needed before scaling.  With
+// P > 0 the row has at most 32 * P blocks and the lane's share of the quantized
+// activation (P blocks, 9 registers each) stays in registers for the whole
+// kernel; with P == 0 the activation is read from shared memory.  Compared with
+// the half-block kernel above this issues about a quarter of the instructions
+// per weight byte, which is what keeps the SM clock up under the power cap.
+struct Block32 {
+    int4 lo, hi;
+};
+
+__device__ __forceinline__ Block32 ldg_stream_32(const void *address) {
+    Block32 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v8.s32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x),
+                   "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
+                 : "l"(address));
+    return v;
+}
+
+__device__ __forceinline__ int dot32(const Block32 &w, const Block32 &a) {
+    return dot16(w.hi, a.hi) + dot16(w.lo, a.lo);
+}
+
+template <int P, int NR, int ACT, int EPI>
+__global__ void __launch_bounds__(kGemvThreads)
+q8_gemv_block_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(16) uint8_t gemv_smem[];
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
+    __syncthreads();
+    const int4 *act_q = reinterpret_cast<const int4 *>(gemv_smem);
+    const float *act_s = reinterpret_cast<const float *>(gemv_smem + p.width);
+    const int lane = threadIdx.x & 31;
+    const int warp = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
+    const int warps = gridDim.x * kGemvWarps;
+    const int blocks = p.blocks;
+    const size_t stride = static_cast<size_t>(p.row_stride);
+    constexpr int PR = P > 0 ? P : 1;
+    constexpr int ROWS_AT_ONCE = EPI == kEpiSiluPair ? 2 : NR;
+
+    // register image of this lane's activation blocks (P > 0 only)
+    Block32 a_reg[PR];
+    float sa_reg[PR];
+    if (P > 0) {
+#pragma unroll
+        for (int u = 0; u < PR; ++u) {
+            const int b = u * 32 + lane;
+            const bool ok = b < blocks;
+            a_reg[u].lo = ok ? act_q[2 * b] : make_int4(0, 0, 0, 0);
+            a_reg[u].hi = ok ? act_q[2 * b + 1] : make_int4(0, 0, 0, 0);
+            sa_reg[u] = ok ? act_s[b] : 0.0f;
+        }
+    }
+    const int lane_q = lane * 32;   // byte offset of the lane's first block in a row
+    const int lane_s = p.width + lane * 2;
+
+    for (int first = warp * NR; first < p.total_rows; first += warps * NR) {
+        const uint8_t *base[ROWS_AT_ONCE];
+        int local_row[ROWS_AT_ONCE];
+        int seg_of[ROWS_AT_ONCE];
+#pragma unroll
+        for (int r = 0; r < ROWS_AT_ONCE; ++r) {
+            if (EPI == kEpiSiluPair) {
+                local_row[r] = first;
+                seg_of[r] = r;
+            } else {
+                int row = first + r;
+                if (row >= p.total_rows) row = first;
+                int seg = 0;
+                if (EPI == kEpiPlain && p.segments > 1) {
+#pragma unroll
+                    for (int s = 0; s < kMaxSegments - 1; ++s)
+                        if (seg == s && s + 1 < p.segments && row >= p.rows[s]) {
+                            row -= p.rows[s];
+                            seg = s + 1;
+                        }
+                }
+                local_row[r] = row;
+                seg_of[r] = seg;
+            }
+            base[r] = p.weights[seg_of[r]] + local_row[r] * stride;
+        }
+        float acc[ROWS_AT_ONCE];
+#pragma unroll
+        for (int r = 0; r < ROWS_AT_ONCE; ++r) acc[r] = 0.0f;
+
+        if (P > 0) {
+            Block32 w[ROWS_AT_ONCE][PR];
+            uint16_t d[ROWS_AT_ONCE][PR];
+#pragma unroll
+            for (int u = 0; u < PR; ++u) {
+                // only the last pass can be ragged
+                const bool ok = (u + 1 < PR) || (u * 32 + lane < blocks);
+#pragma unroll
+                for (int r = 0; r < ROWS_AT_ONCE; ++r) {
+                    if (ok) {
+                        w[r][u] = ldg_stream_32(base[r] + lane_q + u * 1024);
+                        d[r][u] = ldg_stream_u16(base[r] + lane_s + u * 64);
+                    } else {
+                        w[r][u].lo = w[r][u].hi = make_int4(0, 0, 0, 0);
+                        d[r][u] = 0;
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < PR; ++u) {
+#pragma unroll
+                for (int r = 0; r < ROWS_AT_ONCE; ++r) {
+                    const int dot = dot32(w[r][u], a_reg[u]);
+                    acc[r] = fmaf(half_bits_to_float(d[r][u]) * sa_reg[u],
+                        static_cast<float>(dot), acc[r]);
+                    if (EPI == kEpiBlockDots && u * 32 + lane < blocks)
+                        reinterpret_cast<int32_t *>(p.outputs[0])[
+                            static_cast<size_t>(local_row[r]) * blocks + u * 32 + lane] = dot;
+                }
+            }
+        } else {
+            constexpr int U = 4;
+            for (int b0 = 0; b0 < blocks; b0 += 32 * U) {
+                Block32 w[ROWS_AT_ONCE][U];
+                uint16_t d[ROWS_AT_ONCE][U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int b = b0 + u * 32 + lane;
+                    const bool ok = b < blocks;
+#pragma unroll
+                    for (int r = 0; r < ROWS_AT_ONCE; ++r) {
+                        if (ok) {
+                            w[r][u] = ldg_stream_32(base[r] + static_cast<size_t>(b) * 32);
+                            d[r][u] = ldg_stream_u16(base[r] + p.width + b * 2);
+                        } else {
+                            w[r][u].lo = w[r][u].hi = make_int4(0, 0, 0, 0);
+                            d[r][u] = 0;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int b = b0 + u * 32 + lane;
+                    const bool ok = b < blocks;
+                    Block32 a;
+                    a.lo = ok ? act_q[2 * b] : make_int4(0, 0, 0, 0);
+                    a.hi = ok ? act_q[2 * b + 1] : make_int4(0, 0, 0, 0);
+                    const float sa = ok ? act_s[b] : 0.0f;
+#pragma unroll
+                    for (int r = 0; r < ROWS_AT_ONCE; ++r) {
+                        const int dot = dot32(w[r][u], a);
+                        acc[r] = fmaf(half_bits_to_float(d[r][u]) * sa, static_cast<float>(dot),
+                            acc[r]);
+                        if (EPI == kEpiBlockDots && ok)
+                            reinterpret_cast<int32_t *>(p.outputs[0])[
+                                static_cast<size_t>(local_row[r]) * blocks + b] = dot;
+                    }
+                }
+            }
+        }
+
+        if (EPI == kEpiSiluPair) {
+            const float gate = warp_sum(acc[0]);
+            const float up = warp_sum(acc[ROWS_AT_ONCE - 1]);
+            if (lane == 0) p.outputs[0][first] = silu_mul(gate, up);
+        } else {
+#pragma unroll
+            for (int r = 0; r < ROWS_AT_ONCE; ++r) {
+                const float total = warp_sum(acc[r]);
+                if (lane == 0 && first + r < p.total_rows) {
+                    if (EPI == kEpiPlain) {
+                        p.outputs[seg_of[r]][local_row[r]] = total;
+                    } else if (EPI == kEpiPeers) {
+                        for (int peer = 0; peer < p.peers; ++peer)
+                            p.peer_outputs[peer][p.first_row + local_row[r]] = total;
+                    }
+                }
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
 // ring variant
 // --------------------------------------------------------------------------
 constexpr int kRingConsumerWarps = 8;

@@ -1,12 +1,514 @@
-// placeholder replaced below
+// Batched Q8_0 x Q8_0 product for multi-token prefill on the sm_100a tensor cores.
+//
+// out[t][r] = sum_b half(dw[r][b]) * half(da[t][b]) * (sum_i qw[r][b][i] * qa[t][b][i])
+//
+// The reference has no batched call (one token per forward,
+// src/models/qwen35/fortai_qwen35_cpu.f90:591); parity is defined as `tokens`
+// independent reference matvecs (src/fortai_gguf_runtime.f90:424-465), and the
+// per-(token, row, block) int32 dots are the loop of
+// src/backend/cpu/fortai_q8_dot.c:277-279.
+//
+// Mapping.  One `tcgen05.mma.kind::i8` has K = 32, exactly one Q8_0 block, so
+// each MMA yields the exact int32 block dots of a 128 (weight rows) x 128
+// (tokens) tile, written to a fresh TMEM accumulator (no accumulation across
+// blocks, because every block has its own pair of scales).  Epilogue warps pull
+// the accumulator out with tcgen05.ld, convert, scale by dw * da and add into
+// fp32 registers, while the next blocks' MMAs run into the other TMEM buffers.
+//
+//   warp 0        TMA producer: 2-D tiled loads (128B swizzle) of 128 rows x 128
+//                 K-bytes of weights and of activations per stage (= 4 blocks)
+//   warp 1        TMEM allocation, MMA issue (one elected thread), commits
+//   warps 2..9    epilogue: warp w owns TMEM lanes 32*(w%4).. and 64 of the 128
+//                 token columns; 64 fp32 accumulators per thread
+//
+// TMEM: 512 columns = 4 accumulator buffers of 128 int32 columns.  All waits on
+// mbarriers are bounded; a wait that gives up records a status word, raises the
+// CTA's abort flag, and every role falls through to the common exit, where the
+// TMEM allocation is released.
 #pragma once
+
+#include <cuda.h>
+
 #include "q8_common.cuh"
+
 namespace fortai_b200 {
-struct MmqWeightsPlan { bool ready = false; };
-inline bool mmq_supported(int, int, int, int) { return false; }
-inline cudaError_t mmq_reserve(void **, size_t *, int, int, int) { return cudaSuccess; }
-inline cudaError_t mmq_enqueue(cudaStream_t, int, int *, MmqWeightsPlan *, const uint8_t *, int, int,
-    int, const void *, int, int, float *, int32_t *, void **, size_t *, uint64_t *) {
-    return cudaErrorNotSupported;
+
+constexpr int kMmqTileRows = 128;     // weight rows per CTA (MMA M)
+constexpr int kMmqTileTokens = 128;   // tokens per CTA (MMA N)
+constexpr int kMmqStageBlocks = 4;    // Q8_0 blocks per pipeline stage (128 K-bytes)
+constexpr int kMmqStages = 4;
+constexpr int kMmqTmemBuffers = 4;
+constexpr int kMmqEpilogueWarps = 8;
+constexpr int kMmqThreads = (2 + kMmqEpilogueWarps) * 32;
+constexpr int kMmqStageBytes = (kMmqTileRows + kMmqTileTokens) * 128;
+
+struct MmqWeightsPlan {
+    bool ready = false;
+    CUtensorMap weights_map;
+};
+
+// ---- planar activation image in scratch -------------------------------------
+//   [ tokens_padded x width int8 quants ][ blocks x tokens_padded float scales ]
+// The scale plane is block-major so that a tile's 128 scales of one block are
+// contiguous.
+inline int mmq_padded_tokens(int tokens) {
+    return (tokens + kMmqTileTokens - 1) / kMmqTileTokens * kMmqTileTokens;
 }
+
+inline size_t mmq_scratch_bytes(int width, int tokens) {
+    const size_t padded = static_cast<size_t>(mmq_padded_tokens(tokens));
+    return padded * width + padded * (width / kBlockElems) * sizeof(float);
 }
+
+inline bool mmq_supported(int rows, int width, int tokens, int min_tokens) {
+    const int threshold = min_tokens > 0 ? min_tokens : 32;
+    return tokens >= threshold && width % (kMmqStageBlocks * kBlockElems) == 0 && rows >= 1;
+}
+
+// One warp per Q8_0 block of the activation: fp32 -> (quants, scale) or
+// GGUF block -> (quants, scale), into the planar image.
+template <int ACT>
+__global__ void __launch_bounds__(256)
+mmq_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_tokens, int width,
+    int8_t *__restrict__ quants, float *__restrict__ scales) {
+    const int blocks = width / kBlockElems;
+    const int lane = threadIdx.x & 31;
+    const long long total = static_cast<long long>(padded_tokens) * blocks;
+    for (long long i = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); i < total;
+         i += static_cast<long long>(gridDim.x) * 8) {
+        const int t = static_cast<int>(i / blocks);
+        const int b = static_cast<int>(i - static_cast<long long>(t) * blocks);
+        int q = 0;
+        float scale = 0.0f;
+        if (t < tokens) {
+            if (ACT == 1) {
+                const float *x = static_cast<const float *>(activation);
+                uint16_t bits;
+                q = quantize_lane(x[static_cast<size_t>(t) * width + b * kBlockElems + lane], &bits);
+                scale = half_bits_to_float(bits);
+            } else {
+                const uint8_t *block = static_cast<const uint8_t *>(activation) +
+                    (static_cast<size_t>(t) * blocks + b) * kBlockBytes;
+                q = static_cast<int8_t>(block[2 + lane]);
+                scale = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
+            }
+        }
+        quants[static_cast<size_t>(t) * width + b * kBlockElems + lane] = static_cast<int8_t>(q);
+        if (lane == 0) scales[static_cast<size_t>(b) * padded_tokens + t] = scale;
+    }
+}
+
+// ---- tcgen05 / TMA wrappers ---------------------------------------------------
+__device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y,
+    uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)),
+        "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t base, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// D(tmem) = A(smem) * B(smem)^T, int8 x int8 -> int32, fresh accumulator.
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+    uint32_t idesc) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(0u)
+        : "memory");
+}
+
+// Arrive on an mbarrier once every MMA issued so far by this thread has finished.
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+          "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+          "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]),
+          "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]),
+          "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_wait() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are
+// 128 bytes apart, groups of 8 rows 1024 bytes apart (the stride byte offset);
+// the leading byte offset is not used by swizzled K-major layouts.
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(const void *tile) {
+    uint64_t desc = (smem_u32(tile) >> 4) & 0x3fffu;
+    desc |= static_cast<uint64_t>(1024 >> 4) << 32;   // stride byte offset
+    desc |= 1ull << 46;                               // descriptor version for tcgen05
+    desc |= 2ull << 61;                               // SWIZZLE_128B
+    return desc;
+}
+
+// Instruction descriptor of kind::i8: D = s32, A = B = s8, both K-major.
+__host__ __device__ constexpr uint32_t mmq_instr_desc(int m, int n) {
+    return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+        (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+struct MmqParams {
+    const uint8_t *weights;     // row-planar weight rows (for the fp16 scale plane)
+    int rows;
+    int width;
+    int blocks;
+    int row_stride;
+    int tokens;
+    int padded_tokens;
+    const float *act_scales;    // [blocks][padded_tokens]
+    float *output;              // [tokens][rows]
+    int32_t *block_dots;        // optional [tokens][rows][blocks]
+    int *status;
+};
+
+struct MmqShared {
+    uint64_t smem_full[kMmqStages];
+    uint64_t smem_empty[kMmqStages];
+    uint64_t tmem_full[kMmqTmemBuffers];
+    uint64_t tmem_empty[kMmqTmemBuffers];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <bool DOTS>
+__global__ void __launch_bounds__(kMmqThreads, 1)
+q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
+    const __grid_constant__ CUtensorMap act_map, const __grid_constant__ MmqParams p) {
+    extern __shared__ uint8_t mmq_smem_raw[];
+    // [stages x (A 16 KB | B 16 KB)] [activation scales: blocks x 128 floats] [barriers]
+    // Swizzled tiles must start on a 1024-byte boundary: round the base up (the
+    // launch reserves the slack).
+    uint8_t *mmq_smem = mmq_smem_raw + ((1024u - (smem_u32(mmq_smem_raw) & 1023u)) & 1023u);
+    uint8_t *stage_base = mmq_smem;
+    float *da_s = reinterpret_cast<float *>(mmq_smem + kMmqStages * kMmqStageBytes);
+    MmqShared *sh = reinterpret_cast<MmqShared *>(
+        reinterpret_cast<uint8_t *>(da_s) + static_cast<size_t>(p.blocks) * kMmqTileTokens * 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kMmqTileRows;
+    const int token0 = blockIdx.y * kMmqTileTokens;
+    const int stages_total = p.blocks / kMmqStageBlocks;
+    volatile int *abort_flag = &sh->abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kMmqStages; ++s) {
+            mbar_init(&sh->smem_full[s], 1);
+            mbar_init(&sh->smem_empty[s], 1);
+        }
+        for (int b = 0; b < kMmqTmemBuffers; ++b) {
+            mbar_init(&sh->tmem_full[b], 1);
+            mbar_init(&sh->tmem_empty[b], kMmqEpilogueWarps);
+        }
+        sh->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(&sh->tmem_base, 512);
+    // activation scales of this token tile: da_s[b][0..127]
+    for (int i = threadIdx.x; i < p.blocks * kMmqTileTokens; i += kMmqThreads) {
+        const int b = i / kMmqTileTokens;
+        const int t = i - b * kMmqTileTokens;
+        da_s[i] = p.act_scales[static_cast<size_t>(b) * p.padded_tokens + token0 + t];
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sh->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        if (lane == 0) {
+            int armed = 0;
+            for (int st = 0; st < stages_total; ++st) {
+                const int s = st % kMmqStages;
+                const int use = st / kMmqStages;
+                if (use > 0 && !mbar_wait_bounded(&sh->smem_empty[s], (use - 1) & 1)) {
+                    atomicExch(p.status, kStatusMmqLoadTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                if (*abort_flag) break;
+                uint8_t *dst = stage_base + s * kMmqStageBytes;
+                mbar_arrive_expect_tx(&sh->smem_full[s], kMmqStageBytes);
+                tma_load_2d(dst, &weights_map, st * 128, row0, &sh->smem_full[s]);
+                tma_load_2d(dst + kMmqTileRows * 128, &act_map, st * 128, token0,
+                    &sh->smem_full[s]);
+                armed = st + 1;
+            }
+            if (*abort_flag) {
+                // let the loads that are still in flight land before the CTA ends
+                const int lap = armed < kMmqStages ? armed : kMmqStages;
+                for (int k = 0; k < lap; ++k) {
+                    const int n = armed - 1 - k;
+                    mbar_wait_bounded(&sh->smem_full[n % kMmqStages], (n / kMmqStages) & 1,
+                        1u << 16);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer --------------------------------
+        if (lane == 0) {
+            const uint32_t idesc = mmq_instr_desc(kMmqTileRows, kMmqTileTokens);
+            bool failed = false;
+            for (int st = 0; st < stages_total && !failed; ++st) {
+                const int s = st % kMmqStages;
+                if (!mbar_wait_bounded(&sh->smem_full[s], (st / kMmqStages) & 1)) {
+                    atomicExch(p.status, kStatusMmqLoadTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc_fence_after();
+                const uint8_t *tile = stage_base + s * kMmqStageBytes;
+                const uint64_t desc_a = smem_desc_k_major_sw128(tile);
+                const uint64_t desc_b = smem_desc_k_major_sw128(tile + kMmqTileRows * 128);
+                for (int j = 0; j < kMmqStageBlocks; ++j) {
+                    const int kb = st * kMmqStageBlocks + j;
+                    const int buf = kb % kMmqTmemBuffers;
+                    const int use = kb / kMmqTmemBuffers;
+                    if (use > 0) {
+                        if (!mbar_wait_bounded(&sh->tmem_empty[buf], (use - 1) & 1)) {
+                            atomicExch(p.status, kStatusMmqDrainTimeout);
+                            *abort_flag = 1;
+                            failed = true;
+                            break;
+                        }
+                        tc_fence_after();
+                    }
+                    if (*abort_flag) {
+                        failed = true;
+                        break;
+                    }
+                    // 32 K-bytes further inside the 128-byte swizzled row: +2 in
+                    // units of 16 bytes on the descriptor's start address
+                    mma_i8(tmem_base + buf * kMmqTileTokens, desc_a + 2 * j, desc_b + 2 * j,
+                        idesc);
+                    mma_commit(&sh->tmem_full[buf]);
+                }
+                if (!failed) mma_commit(&sh->smem_empty[s]);
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ----------------------------------
+        const int ew = warp - 2;
+        const int quadrant = warp & 3;              // TMEM lanes this warp may touch
+        const int col0 = (ew >> 2) * 64;            // token columns of this warp
+        const int row = row0 + quadrant * 32 + lane;
+        const bool row_ok = row < p.rows;
+        const uint8_t *scale_plane = p.weights +
+            static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
+        float acc[64];
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        bool failed = false;
+        for (int kb = 0; kb < p.blocks && !failed; ++kb) {
+            const int buf = kb % kMmqTmemBuffers;
+            bool ready = true;
+            if (lane == 0) {
+                ready = mbar_wait_bounded(&sh->tmem_full[buf], (kb / kMmqTmemBuffers) & 1);
+                if (!ready) {
+                    atomicExch(p.status, kStatusMmqMmaTimeout);
+                    *abort_flag = 1;
+                }
+            }
+            ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+            if (!ready || *abort_flag) {
+                failed = true;
+                break;
+            }
+            mbar_wait_bounded(&sh->tmem_full[buf], (kb / kMmqTmemBuffers) & 1, 1u << 10);
+            tc_fence_after();
+            const float dw = half_bits_to_float(
+                *reinterpret_cast<const uint16_t *>(scale_plane + kb * 2));
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) +
+                buf * kMmqTileTokens + col0;
+            uint32_t v0[32], v1[32];
+            tmem_load_32(taddr, v0);
+            tmem_load_32(taddr + 32, v1);
+            tmem_load_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+            const float *da = da_s + kb * kMmqTileTokens + col0;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                acc[i] = fmaf(dw * da[i], static_cast<float>(static_cast<int>(v0[i])), acc[i]);
+                acc[32 + i] = fmaf(dw * da[32 + i], static_cast<float>(static_cast<int>(v1[i])),
+                    acc[32 + i]);
+            }
+            if (DOTS && row_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int t0 = token0 + col0 + i;
+                    if (t0 < p.tokens)
+                        p.block_dots[(static_cast<size_t>(t0) * p.rows + row) * p.blocks + kb] =
+                            static_cast<int>(v0[i]);
+                    if (t0 + 32 < p.tokens)
+                        p.block_dots[(static_cast<size_t>(t0 + 32) * p.rows + row) * p.blocks + kb] =
+                            static_cast<int>(v1[i]);
+                }
+            }
+        }
+        if (!failed && row_ok && p.output) {
+#pragma unroll
+            for (int i = 0; i < 64; ++i) {
+                const int t = token0 + col0 + i;
+                if (t < p.tokens) p.output[static_cast<size_t>(t) * p.rows + row] = acc[i];
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// ---- host side ----------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+    const cuuint64_t *, const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+    CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn mmq_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *entry = nullptr;
+        cudaDriverEntryPointQueryResult result;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault,
+                &result) == cudaSuccess && result == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(entry);
+    }
+    return fn;
+}
+
+// int8 matrix, `rows` x `width` bytes, row pitch `pitch`; boxes of 128 rows x 128 bytes.
+inline bool mmq_make_map(CUtensorMap *map, const void *base, int rows, int width, size_t pitch) {
+    EncodeTiledFn encode = mmq_encode_fn();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
+    const cuuint32_t box[2] = {128, 128};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides,
+               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+        CUDA_SUCCESS;
+}
+
+inline cudaError_t mmq_reserve(void **aux, size_t *aux_bytes, int rows, int width, int tokens) {
+    (void)rows;
+    const size_t want = mmq_scratch_bytes(width, tokens);
+    if (want <= *aux_bytes) return cudaSuccess;
+    cudaError_t error = cudaFree(*aux);
+    *aux = nullptr;
+    *aux_bytes = 0;
+    if (error != cudaSuccess) return error;
+    error = cudaMalloc(aux, want);
+    if (error == cudaSuccess) *aux_bytes = want;
+    return error;
+}
+
+inline size_t mmq_smem_bytes(int blocks) {
+    return static_cast<size_t>(kMmqStages) * kMmqStageBytes +
+        static_cast<size_t>(blocks) * kMmqTileTokens * 4 + sizeof(MmqShared) + 64 + 1024;
+}
+
+// activation: fp32 [tokens][width] (act == 1) or Q8_0 blocks (act == 0), device memory.
+inline cudaError_t mmq_enqueue(cudaStream_t stream, int sm_count, int *status,
+    MmqWeightsPlan *plan, const uint8_t *weights, int rows, int width, int row_stride,
+    const void *activation, int act, int tokens, float *output, int32_t *block_dots, void **aux,
+    size_t *aux_bytes, uint64_t *launches) {
+    const int blocks = width / kBlockElems;
+    const int padded = mmq_padded_tokens(tokens);
+    cudaError_t error = mmq_reserve(aux, aux_bytes, rows, width, tokens);
+    if (error != cudaSuccess) return error;
+    int8_t *quants = static_cast<int8_t *>(*aux);
+    float *scales = reinterpret_cast<float *>(quants + static_cast<size_t>(padded) * width);
+    if (!plan->ready) {
+        if (!mmq_make_map(&plan->weights_map, weights, rows, width, row_stride))
+            return cudaErrorNotSupported;
+        plan->ready = true;
+    }
+    CUtensorMap act_map;
+    if (!mmq_make_map(&act_map, quants, padded, width, width)) return cudaErrorNotSupported;
+
+    const long long prep_warps = static_cast<long long>(padded) * blocks;
+    const int prep_grid = static_cast<int>(std::max<long long>(1,
+        std::min<long long>((prep_warps + 7) / 8, static_cast<long long>(sm_count) * 16)));
+    if (act == 1)
+        mmq_prepare_kernel<1><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
+            quants, scales);
+    else
+        mmq_prepare_kernel<0><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
+            quants, scales);
+    ++*launches;
+    error = cudaGetLastError();
+    if (error != cudaSuccess) return error;
+
+    MmqParams p = {};
+    p.weights = weights;
+    p.rows = rows;
+    p.width = width;
+    p.blocks = blocks;
+    p.row_stride = row_stride;
+    p.tokens = tokens;
+    p.padded_tokens = padded;
+    p.act_scales = scales;
+    p.output = output;
+    p.block_dots = block_dots;
+    p.status = status;
+    const size_t smem = mmq_smem_bytes(blocks);
+    if (smem > 227 * 1024) return cudaErrorInvalidValue;
+    const dim3 grid((rows + kMmqTileRows - 1) / kMmqTileRows, padded / kMmqTileTokens);
+    if (block_dots) {
+        error = cudaFuncSetAttribute(q8_mmq_kernel<true>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (error != cudaSuccess) return error;
+        q8_mmq_kernel<true><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map, p);
+    } else {
+        error = cudaFuncSetAttribute(q8_mmq_kernel<false>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (error != cudaSuccess) return error;
+        q8_mmq_kernel<false><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map, p);
+    }
+    ++*launches;
+    return cudaGetLastError();
+}
+
+}  // namespace fortai_b200

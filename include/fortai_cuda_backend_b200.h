@@ -195,9 +195,11 @@ uint64_t fortai_cuda_q8_context_launch_count(const fortai_cuda_q8_context *conte
 /* Blocks until the stream is idle, then reports any device-side wait that gave
  * up (bounded mbarrier waits in the staged kernels) as RUNTIME_ERROR. */
 int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context);
-/* Tuning knobs, by name: "gemv_variant" (0 = automatic, 1 = direct vector loads,
- * 2 = bulk-copy ring), "gemv_ctas_per_sm", "ring_stages", "ring_rows",
- * "mmq_min_tokens".  Unknown names return INVALID. */
+/* Tuning knobs, by name: "gemv_variant" (0 = automatic, 1 = half-block-per-lane
+ * kernel with 16-byte loads, 2 = bulk-copy ring, 3 = block-per-lane kernel with
+ * 32-byte loads), "gemv_ctas_per_sm", "gemv_rows_per_warp", "ring_stages",
+ * "ring_rows", "mmq_min_tokens".  Zero means automatic.  Unknown names return
+ * INVALID. */
 int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context, const char *name,
     int value);
 

@@ -104,6 +104,6 @@ def test_wrapper_reports_invalid_like_the_fortran_module():
 
 
 def test_layout_helpers_match_the_documented_row_stride():
-    # row-planar device rows: round_up(34 * blocks, 16) bytes
-    for blocks, stride in ((32, 1088), (80, 2720), (68, 2320), (1, 48), (544, 18496)):
-        assert (blocks * 34 + 15) // 16 * 16 == stride
+    # row-planar device rows: round_up(34 * blocks, 32) bytes
+    for blocks, stride in ((32, 1088), (80, 2720), (68, 2336), (1, 64), (544, 18496)):
+        assert (blocks * 34 + 31) // 32 * 32 == stride
