@@ -407,8 +407,23 @@ def run_gpu_arm(args):
     return 0
 
 
-def bench_mmq(torch, backend, ctx):
+def run_mmq_only(args):
+    import torch
+    from fortai_b200 import backend_cuda as backend
+    ctx = backend.cuda_q8_context_t()
+    stat = ctx.create(0, stream=torch.cuda.current_stream().cuda_stream)
+    if not stat.is_ok():
+        raise SystemExit(f"context creation failed: {stat}")
+    result = bench_mmq(torch, backend, ctx, tokens=args.tokens, iters=max(1, args.steps),
+                       warmup=max(1, args.warmup))
+    ctx.destroy()
+    print(json.dumps(result), flush=True)
+    return 0 if result and result.get("ok") else 1
+
+
+def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3):
     """Batched prefill product, M=512 x K=2560 x N=9728 (BASELINE configs[3])."""
+    MMQ_M = tokens
     host_weights = make_device_weights(torch, backend, ctx, 0, MMQ_N, MMQ_K, seed=2)
     w = backend.cuda_q8_weights_t()
     if not w.upload(ctx, host_weights, host_weights.size, MMQ_N, MMQ_K).is_ok():
@@ -422,12 +437,11 @@ def bench_mmq(torch, backend, ctx):
     def once():
         return backend.cuda_q8_matmul_device_f32(ctx, w, act.data_ptr(), MMQ_M, out.data_ptr(),
                                                  out.numel())
-    for _ in range(3):
+    for _ in range(warmup):
         if not once().is_ok():
             w.destroy()
             return None
     torch.cuda.synchronize()
-    iters = 50
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches = ctx.launch_count()
     start.record(stream)
@@ -461,12 +475,17 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--rows", type=int, default=ROWS,
                         help="row count of the GEMV (smaller cases are for profiler captures)")
+    parser.add_argument("--mmq-only", action="store_true",
+                        help="run only the batched prefill product (profiler captures)")
+    parser.add_argument("--tokens", type=int, default=MMQ_M, help="token count of the prefill leg")
     parser.add_argument("--kernel-only", action="store_true",
                         help="skip the e2e, prefill and CPU legs (profiler captures)")
     args = parser.parse_args()
     set_rows(args.rows)
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.mmq_only:
+        return run_mmq_only(args)
     return run_gpu_arm(args)
 
 
