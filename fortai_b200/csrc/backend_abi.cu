@@ -1207,3 +1207,84 @@ extern "C" int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *c
     }
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "matmul block dots", error);
 }
+
+// ---------------------------------------------------------------------------
+// FFN without any allocation
+// ---------------------------------------------------------------------------
+// Some hosts cannot let this library allocate once they are running: a serving
+// process that has already handed every free byte of HBM to its weight and cache
+// pools (a later cudaMalloc fails or fragments the pool), and a decode loop that
+// cannot afford the device-wide synchronisation that cudaFree/cudaMalloc imply
+// when a scratch buffer grows in the middle of a step.  For them the FFN's two
+// intermediates - the fp32 hidden vector silu(gate.x) * (up.x) and its Q8_0
+// image - live in a fixed array that is part of the library image.  Every GPU
+// that loads the library holds these kStaticFfnBytes until the process exits.
+namespace {
+
+constexpr int kStaticFfnMaxInner = 32768;   // largest supported FFN inner size (gate/up rows)
+constexpr size_t kStaticFfnHiddenBytes = static_cast<size_t>(kStaticFfnMaxInner) * sizeof(float);
+constexpr size_t kStaticFfnQ8Bytes =
+    (static_cast<size_t>(kStaticFfnMaxInner) / kBlockElems * kBlockBytes + 255) / 256 * 256;
+constexpr size_t kStaticFfnBytes = kStaticFfnHiddenBytes + kStaticFfnQ8Bytes;
+
+static __device__ __align__(256) unsigned char g_static_ffn_scratch[kStaticFfnBytes];
+
+constexpr int kStaticFfnMaxDevices = 64;
+unsigned char *g_static_ffn_address[kStaticFfnMaxDevices] = {};
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address; the address on the current device comes from cudaGetSymbolAddress.
+// Looked up once per device, with that device current.
+cudaError_t static_ffn_address(int device, unsigned char **address) {
+    if (device < 0 || device >= kStaticFfnMaxDevices) return cudaErrorInvalidDevice;
+    if (!g_static_ffn_address[device]) {
+        void *pointer = nullptr;
+        const cudaError_t error = cudaGetSymbolAddress(&pointer, g_static_ffn_scratch);
+        if (error != cudaSuccess) return error;
+        g_static_ffn_address[device] = static_cast<unsigned char *>(pointer);
+    }
+    *address = g_static_ffn_address[device];
+    return cudaSuccess;
+}
+
+}  // namespace
+
+extern "C" int fortai_cuda_q8_ffn_device_noalloc(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation,
+    size_t activation_elements, void *device_output, size_t output_elements) {
+    if (!context || !gate_weights || !up_weights || !down_weights || !device_activation ||
+        !device_output) return FORTAI_CUDA_INVALID;
+    if (!ffn_shapes_ok(context, gate_weights, up_weights, down_weights) ||
+        activation_elements != static_cast<size_t>(gate_weights->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(down_weights->rows)) return FORTAI_CUDA_INVALID;
+    if (gate_weights->rows > kStaticFfnMaxInner) {
+        std::snprintf(context->error, sizeof(context->error),
+            "allocation-free FFN supports an inner size of at most %d, got %d",
+            kStaticFfnMaxInner, gate_weights->rows);
+        return FORTAI_CUDA_INVALID;
+    }
+    cudaSetDevice(context->device);
+    unsigned char *scratch = nullptr;
+    cudaError_t error = static_ffn_address(context->device, &scratch);
+    if (error != cudaSuccess) return fail(context, "allocation-free FFN scratch lookup", error);
+    float *hidden = reinterpret_cast<float *>(scratch);
+    uint8_t *hidden_q8 = scratch + kStaticFfnHiddenBytes;
+    // Both intermediates are fully rewritten by every call (each of the `inner`
+    // floats, each of the inner/32 blocks), so nothing has to be cleared first.
+    GemvParams p = single_params(context, gate_weights, device_activation, hidden);
+    p.weights[1] = up_weights->data;
+    p.rows[1] = up_weights->rows;
+    p.segments = 2;
+    error = launch_gemv(context, p, kActF32, kEpiSiluPair);
+    if (error == cudaSuccess)
+        error = launch_quantize(context, hidden, hidden_q8,
+            static_cast<size_t>(down_weights->blocks));
+    if (error == cudaSuccess) {
+        const GemvParams d = single_params(context, down_weights, hidden_q8,
+            static_cast<float *>(device_output));
+        error = launch_gemv(context, d, kActQ8, kEpiPlain);
+    }
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(context, "allocation-free Qwen FFN device", error);
+}

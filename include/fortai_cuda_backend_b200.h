@@ -262,6 +262,26 @@ int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *context,
     size_t activation_elements, void *const *peer_outputs, int peer_count, size_t first_row,
     size_t output_elements);
 
+/* Has no counterpart in the reference.  Same contract and same result as
+ * fortai_cuda_q8_ffn_device, for hosts that must not allocate while they run (all
+ * free device memory already belongs to their own pools, or a cudaMalloc/cudaFree
+ * in the middle of a decode step would stall the whole device): this call makes
+ * no cudaMalloc, cudaFree or other allocating call.  Its two intermediates (the
+ * fp32 hidden vector and its Q8_0 image) live in a fixed 164 KB array inside the
+ * library image, held on every GPU that loads the library until the process
+ * exits.  Limit: gate/up rows (the FFN inner size) <= 32768; larger shapes
+ * return FORTAI_CUDA_INVALID with a message in fortai_cuda_q8_last_error.
+ * The first call on a device looks the array's address up
+ * (cudaGetSymbolAddress); make that first call before any stream capture.
+ * The array is shared by every context and every call on that device and keeps
+ * the previous call's contents; each call rewrites all of the part it reads, so
+ * nothing needs clearing, but two calls that overlap on the GPU (different
+ * streams) race on it.  Enqueue only. */
+int fortai_cuda_q8_ffn_device_noalloc(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation,
+    size_t activation_elements, void *device_output, size_t output_elements);
+
 #ifdef __cplusplus
 }
 #endif
