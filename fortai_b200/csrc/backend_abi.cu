@@ -42,6 +42,8 @@ struct fortai_cuda_q8_context {
     int gemv_variant = 0;      // 0 auto, 1 direct, 2 ring
     int gemv_ctas_per_sm = 0;  // 0 = occupancy-derived
     int gemv_rows_per_warp = 0;
+    int gemv_depth = 1;        // rows in flight per warp in the pipelined kernel (1 or 2)
+    int gemv_balance = 0;      // 1 = trim the grid so that the last round of rows is full
     int ring_stages = 0;
     int ring_rows = 0;
     int mmq_min_tokens = 0;
@@ -185,6 +187,80 @@ cudaError_t launch_direct(fortai_cuda_q8_context *c, const GemvParams &p) {
                               : launch_direct_instance<8, 1, ACT, EPI>(c, p);
 }
 
+// Grid for a persistent warp-per-row kernel: at most `limit` CTAs, but prefer a
+// slightly smaller count when that makes the last round of rows nearly full
+// (151936 rows on 592 CTAs is 32.08 rounds - 2.8 % of the time almost every warp
+// would idle; 576 CTAs make it 32.97).
+int balanced_grid(int total_rows, int rows_per_cta, int limit) {
+    const int needed = (total_rows + rows_per_cta - 1) / rows_per_cta;
+    if (needed <= limit) return std::max(1, needed);
+    int best = limit;
+    double best_efficiency = 0.0;
+    for (int grid = limit; grid >= limit - limit / 8 && grid >= 1; --grid) {
+        const long long per_round = static_cast<long long>(grid) * rows_per_cta;
+        const long long rounds = (total_rows + per_round - 1) / per_round;
+        const double efficiency = static_cast<double>(total_rows) / (rounds * per_round) *
+            (static_cast<double>(grid) / limit > 0.97 ? 1.0 : static_cast<double>(grid) / limit / 0.97);
+        if (efficiency > best_efficiency + 1e-9) {
+            best_efficiency = efficiency;
+            best = grid;
+        }
+    }
+    return best;
+}
+
+template <int CPL, int ACT, int EPI, int DEPTH>
+cudaError_t launch_pipelined_depth(fortai_cuda_q8_context *c, const GemvParams &p) {
+    auto kernel = q8_gemv_pipelined_kernel<CPL, ACT, EPI, DEPTH>;
+    const size_t smem = pipelined_smem_bytes(p.width, p.blocks, CPL, EPI == kEpiSiluPair ? 2 : 1);
+    cudaError_t error = cudaSuccess;
+    if (smem > 48 * 1024) {
+        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            static_cast<int>(smem));
+        if (error != cudaSuccess) return error;
+    }
+    int per_sm = c->gemv_ctas_per_sm;
+    if (per_sm <= 0) {
+        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem);
+        if (error != cudaSuccess) return error;
+        if (per_sm < 1) per_sm = 1;
+    }
+    const int limit = c->sm_count * per_sm;
+    const int needed = (p.total_rows + kGemvWarps - 1) / kGemvWarps;
+    const int grid = c->gemv_balance ? balanced_grid(p.total_rows, kGemvWarps, limit)
+                                     : std::max(1, std::min(needed, limit));
+    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+template <int CPL, int ACT, int EPI>
+cudaError_t launch_pipelined_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
+    // the gate/up pair already has two rows per warp in flight
+    if (EPI != kEpiSiluPair && c->gemv_depth == 2)
+        return launch_pipelined_depth<CPL, ACT, EPI, 2>(c, p);
+    return launch_pipelined_depth<CPL, ACT, EPI, 1>(c, p);
+}
+
+// The pipelined kernel needs width == 512 * CPL exactly and a single matrix (or the
+// gate/up pair).  Returns false when the shape is not covered.
+template <int ACT, int EPI>
+bool launch_pipelined(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *error) {
+    if (p.width % 512 != 0) return false;
+    if (EPI == kEpiPlain && p.segments != 1) return false;
+    if (EPI == kEpiSiluPair && p.width / 512 > 5) return false;   // two rows double-buffered
+    switch (p.width / 512) {
+    case 1: *error = launch_pipelined_instance<1, ACT, EPI>(c, p); return true;
+    case 2: *error = launch_pipelined_instance<2, ACT, EPI>(c, p); return true;
+    case 3: *error = launch_pipelined_instance<3, ACT, EPI>(c, p); return true;
+    case 4: *error = launch_pipelined_instance<4, ACT, EPI>(c, p); return true;
+    case 5: *error = launch_pipelined_instance<5, ACT, EPI>(c, p); return true;
+    case 8: *error = launch_pipelined_instance<8, ACT, EPI>(c, p); return true;
+    case 10: *error = launch_pipelined_instance<10, ACT, EPI>(c, p); return true;
+    default: return false;
+    }
+}
+
 template <int P, int NR, int ACT, int EPI>
 cudaError_t launch_block_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
     auto kernel = q8_gemv_block_kernel<P, NR, ACT, EPI>;
@@ -278,7 +354,16 @@ template <int ACT>
 cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
     RingConfig cfg;
     const bool ring = want_ring(c, p, epi) && ring_plan(c, p, epi, &cfg);
-    const bool half_block = c->gemv_variant == 1;   // the 16-byte-per-lane kernel
+    // automatic: the pipelined kernel where the shape allows, else the half-block kernel
+    const bool half_block = c->gemv_variant <= 1 || c->gemv_variant == 4;
+    if (c->gemv_variant == 0 || c->gemv_variant == 4) {
+        cudaError_t error = cudaSuccess;
+        bool done = false;
+        if (epi == kEpiPlain) done = launch_pipelined<ACT, kEpiPlain>(c, p, &error);
+        else if (epi == kEpiSiluPair) done = launch_pipelined<ACT, kEpiSiluPair>(c, p, &error);
+        else if (epi == kEpiPeers) done = launch_pipelined<ACT, kEpiPeers>(c, p, &error);
+        if (done) return error;
+    }
     switch (epi) {
     case kEpiPlain:
         if (ring) return launch_ring<ACT, kEpiPlain>(c, p, cfg);
@@ -297,6 +382,10 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
 }
 
 cudaError_t launch_gemv(fortai_cuda_q8_context *c, const GemvParams &p, int act, int epi) {
+    // fp32 activations are read with 16-byte loads, Q8_0 ones with 2-byte loads
+    const uintptr_t address = reinterpret_cast<uintptr_t>(p.activation);
+    if ((act == kActF32 && (address & 15)) || (act == kActQ8 && (address & 1)))
+        return cudaErrorMisalignedAddress;
     return act == kActF32 ? launch_gemv_act<kActF32>(c, p, epi)
                           : launch_gemv_act<kActQ8>(c, p, epi);
 }
@@ -972,11 +1061,14 @@ extern "C" int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *contex
 extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context,
     const char *name, int value) {
     if (!context || !name || value < 0) return FORTAI_CUDA_INVALID;
-    if (!std::strcmp(name, "gemv_variant") && value <= 3) context->gemv_variant = value;
+    if (!std::strcmp(name, "gemv_variant") && value <= 4) context->gemv_variant = value;
     else if (!std::strcmp(name, "gemv_ctas_per_sm") && value <= 32)
         context->gemv_ctas_per_sm = value;
     else if (!std::strcmp(name, "gemv_rows_per_warp") && value <= 2)
         context->gemv_rows_per_warp = value;
+    else if (!std::strcmp(name, "gemv_balance") && value <= 1) context->gemv_balance = value;
+    else if (!std::strcmp(name, "gemv_depth") && value >= 1 && value <= 2)
+        context->gemv_depth = value;
     else if (!std::strcmp(name, "ring_stages") && value <= kRingMaxStages)
         context->ring_stages = value;
     else if (!std::strcmp(name, "ring_rows") && value <= 256) context->ring_rows = value;

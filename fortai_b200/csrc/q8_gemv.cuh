@@ -85,13 +85,46 @@ __device__ __forceinline__ void stage_activation(const void *activation, int wid
             else act_q16[b * 16 + (j - 1)] = v;
         }
     } else {
-        const float *x = static_cast<const float *>(activation);
-        const int lane = tid & 31;
-        for (int b = tid >> 5; b < blocks; b += threads >> 5) {
-            uint16_t bits;
-            const int q = quantize_lane(x[b * kBlockElems + lane], &bits);
-            act_q[b * kBlockElems + lane] = static_cast<int8_t>(q);
-            if (lane == 0) act_s[b] = half_bits_to_float(bits);
+        // fp32 -> Q8_0, eight lanes per block: every thread takes four consecutive
+        // floats (one 16-byte load), the block maximum is three shuffles within the
+        // 8-lane group, and the four quants leave as one 32-bit store.  All loads of
+        // a pass are issued before the first shuffle.  Same arithmetic, hence the
+        // same bytes, as quantize_lane.
+        const float4 *x4 = static_cast<const float4 *>(activation);
+        uint32_t *act_q32 = reinterpret_cast<uint32_t *>(act_q);
+        const int groups = width >> 2;              // float4 count; 8 per block
+        constexpr int kPasses = 4;
+        for (int g0 = tid; g0 - tid < groups; g0 += threads * kPasses) {
+            float4 v[kPasses];
+#pragma unroll
+            for (int k = 0; k < kPasses; ++k) {
+                const int g = g0 + k * threads;
+                v[k] = g < groups ? x4[g] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            }
+#pragma unroll
+            for (int k = 0; k < kPasses; ++k) {
+                const int g = g0 + k * threads;
+                float amax = fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)),
+                    fmaxf(fabsf(v[k].z), fabsf(v[k].w)));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                const float scale = __fdiv_rn(amax, 127.0f);
+                const float inverse = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+                const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v[k].x, inverse))));
+                const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v[k].y, inverse))));
+                const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v[k].z, inverse))));
+                const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v[k].w, inverse))));
+                if (g < groups) {
+                    act_q32[g] = static_cast<uint32_t>(q0 & 0xff) |
+                        (static_cast<uint32_t>(q1 & 0xff) << 8) |
+                        (static_cast<uint32_t>(q2 & 0xff) << 16) |
+                        (static_cast<uint32_t>(q3 & 0xff) << 24);
+                    if ((g & 7) == 0)
+                        act_s[g >> 3] = half_bits_to_float(
+                            __half_as_ushort(__float2half_rn(scale)));
+                }
+            }
         }
     }
 }
@@ -208,6 +241,145 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
                     for (int peer = 0; peer < p.peers; ++peer)
                         p.peer_outputs[peer][p.first_row + row] = total;
                 }
+            }
+        }
+    }
+}
+
+// --------------------------------------------------------------------------
+// pipelined variant: two rows in flight per warp, one request for a row's scales
+// --------------------------------------------------------------------------
+// Same lane mapping as the half-block kernel (lane l owns 16-byte chunks l,
+// l + 32, ...; CPL chunks per lane, exact: width == 512 * CPL), rebuilt around
+// what a bare read kernel of the same access pattern showed on B200: the weight
+// stream itself runs at 7.1 TB/s, and what slows a GEMV down is (a) the number of
+// separate load requests - five 2-byte scale loads per row cost 9 % - and (b) the
+// time during which a warp has nothing in flight.  Hence:
+//  * a row's fp16 scales (2 * B bytes, contiguous behind its quants) are fetched by
+//    ONE 16-byte load on lanes < 2 * CPL and handed to the other lanes through a
+//    per-warp shared-memory slot when the row is consumed;
+//  * register double buffering: the loads of the row after next are issued before
+//    a row is consumed, and the first two rows are requested before the activation
+//    is staged, so the quantize prologue runs under a full memory pipeline;
+//  * no predicates and no per-chunk address arithmetic (one pointer per row, all
+//    chunk offsets are immediates);
+//  * each lane scales its own exact int32 half-block dot (no shuffle per chunk):
+//    out = sum over half-blocks of fmaf(half(dw) * half(da), float(dot_half), acc).
+// ROWS is 1 (plain / peers) or 2 (gate row + up row with the SiLU epilogue).
+template <int CPL>
+struct RowRegs {
+    int4 w[CPL];
+    int4 scales;   // lanes < 2 * CPL: eight fp16 scales of this row
+};
+
+template <int CPL>
+__device__ __forceinline__ void row_issue(RowRegs<CPL> &regs, const uint8_t *row, int lane,
+    int width) {
+#pragma unroll
+    for (int u = 0; u < CPL; ++u) regs.w[u] = ldg_stream_16(row + lane * 16 + u * 512);
+    if (lane < 2 * CPL) regs.scales = ldg_stream_16(row + width + lane * 16);
+}
+
+template <int CPL>
+__device__ __forceinline__ float row_consume(const RowRegs<CPL> &regs, const int4 *act_lane,
+    const float *scale_lane, uint8_t *slot, int lane) {
+    if (lane < 2 * CPL) *reinterpret_cast<int4 *>(slot + lane * 16) = regs.scales;
+    __syncwarp();
+    float acc = 0.0f;
+#pragma unroll
+    for (int u = 0; u < CPL; ++u) {
+        const uint16_t dw = *reinterpret_cast<const uint16_t *>(slot + ((lane >> 1) + u * 16) * 2);
+        const int4 a = act_lane[u * 32];
+        const float sa = scale_lane[u * 16];
+        acc = fmaf(half_bits_to_float(dw) * sa, static_cast<float>(dot16(regs.w[u], a)), acc);
+    }
+    __syncwarp();
+    return acc;
+}
+
+// Shared memory of the pipelined kernel: the activation image, then one scale slot
+// per (warp, row-of-the-pair).
+__host__ __device__ inline size_t pipelined_smem_bytes(int width, int blocks, int cpl, int rows) {
+    return activation_smem_bytes(width, blocks) +
+        static_cast<size_t>(kGemvWarps) * rows * (2 * cpl * 16);
+}
+
+// DEPTH is the number of rows a warp keeps in flight: 1 = the next row is
+// requested right after the current one has been consumed (64 registers, four
+// CTAs per SM for CPL = 5), 2 = it is requested one row earlier (register double
+// buffering, fewer resident warps).
+template <int CPL, int ACT, int EPI, int DEPTH>
+__global__ void __launch_bounds__(kGemvThreads)
+q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(16) uint8_t gemv_smem[];
+    constexpr int ROWS = EPI == kEpiSiluPair ? 2 : 1;
+    const int lane = threadIdx.x & 31;
+    const int warp_in_cta = threadIdx.x >> 5;
+    const int warp = blockIdx.x * kGemvWarps + warp_in_cta;
+    const int warps = gridDim.x * kGemvWarps;
+    const size_t stride = static_cast<size_t>(p.row_stride);
+    const size_t step = stride * warps;
+    uint8_t *slots = gemv_smem + activation_smem_bytes(p.width, p.blocks) +
+        warp_in_cta * ROWS * (2 * CPL * 16);
+
+    int row = warp;
+    const uint8_t *base[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) base[r] = p.weights[r] + row * stride;
+    RowRegs<CPL> cur[ROWS], next[DEPTH == 2 ? ROWS : 1];
+    // the first row(s) are requested before the activation is staged, so the
+    // quantize prologue runs under a full memory pipeline
+    if (row < p.total_rows) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) row_issue<CPL>(cur[r], base[r], lane, p.width);
+    }
+    if (DEPTH == 2 && row + warps < p.total_rows) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) row_issue<CPL>(next[r], base[r] + step, lane, p.width);
+    }
+
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
+    __syncthreads();
+    const int4 *act_lane = reinterpret_cast<const int4 *>(gemv_smem) + lane;
+    const float *scale_lane = reinterpret_cast<const float *>(gemv_smem + p.width) + (lane >> 1);
+
+    while (row < p.total_rows) {
+        float partial[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r)
+            partial[r] = row_consume<CPL>(cur[r], act_lane, scale_lane,
+                slots + r * (2 * CPL * 16), lane);
+        const int finished = row;
+        row += warps;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) base[r] += step;
+        if (DEPTH == 1) {
+            // registers of `cur` are free again: request the next row before reducing
+            if (row < p.total_rows) {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) row_issue<CPL>(cur[r], base[r], lane, p.width);
+            }
+        }
+        float total[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) total[r] = warp_sum(partial[r]);
+        if (lane == 0) {
+            if (EPI == kEpiSiluPair) {
+                p.outputs[0][finished] = silu_mul(total[0], total[ROWS - 1]);
+            } else if (EPI == kEpiPeers) {
+                for (int peer = 0; peer < p.peers; ++peer)
+                    p.peer_outputs[peer][p.first_row + finished] = total[0];
+            } else {
+                p.outputs[0][finished] = total[0];
+            }
+        }
+        if (DEPTH == 2) {
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) cur[r] = next[r];
+            if (row + warps < p.total_rows) {
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r)
+                    row_issue<CPL>(next[r], base[r] + step, lane, p.width);
             }
         }
     }

@@ -16,10 +16,16 @@
 // fp32 registers, while the next blocks' MMAs run into the other TMEM buffers.
 //
 //   warp 0        TMA producer: 2-D tiled loads (128B swizzle) of 128 rows x 128
-//                 K-bytes of weights and of activations per stage (= 4 blocks)
+//                 K-bytes of weights and of activations per stage (= 4 blocks), and
+//                 one 2-D load of activation scales per 16 blocks
 //   warp 1        TMEM allocation, MMA issue (one elected thread), commits
 //   warps 2..9    epilogue: warp w owns TMEM lanes 32*(w%4).. and 64 of the 128
-//                 token columns; 64 fp32 accumulators per thread
+//                 token columns; 64 fp32 accumulators per thread, updated with
+//                 packed f32x2 multiply and fused multiply-add
+//
+// The grid is persistent (one CTA per SM); work is split in units of one stage of
+// one tile so that every CTA gets the same number of units, and a tile that two
+// CTAs share is completed with atomic adds onto zeroed output.
 //
 // TMEM: 512 columns = 4 accumulator buffers of 128 int32 columns.  All waits on
 // mbarriers are bounded; a wait that gives up records a status word, raises the
@@ -190,41 +196,92 @@ struct MmqParams {
     int row_stride;
     int tokens;
     int padded_tokens;
-    const float *act_scales;    // [blocks][padded_tokens]
+    int tiles_n;                // row tiles
+    int tiles;                  // row tiles x token tiles
+    int stages_per_tile;        // blocks / 4
     float *output;              // [tokens][rows]
     int32_t *block_dots;        // optional [tokens][rows][blocks]
     int *status;
 };
+
+// Work split.  The unit of work is one pipeline stage (4 blocks) of one 128 x 128
+// tile; units are numbered tile-major and CTA c owns units
+// [c * total / grid, (c + 1) * total / grid): equal shares whatever the tile count
+// (304 tiles on 148 SMs would otherwise run as three waves, the last one 5 % full).
+// A tile whose units fall to more than one CTA is "split": its pieces are added
+// into zeroed output with atomics; other tiles are stored plainly.
+__host__ __device__ inline long long mmq_unit_begin(long long total_units, int grid, int cta) {
+    return total_units * cta / grid;
+}
+
+__host__ __device__ inline bool mmq_tile_is_split(long long total_units, int grid,
+    int stages_per_tile, int tile) {
+    const long long a = static_cast<long long>(tile) * stages_per_tile;
+    const long long b = a + stages_per_tile;
+    // first CTA whose range starts after a
+    long long c = a * grid / total_units;
+    for (long long k = c; k <= c + 2 && k <= grid; ++k) {
+        const long long bound = total_units * k / grid;
+        if (bound > a && bound < b) return true;
+    }
+    return false;
+}
+
+constexpr int kMmqScaleChunkBlocks = 16;   // activation-scale chunk: 16 blocks x 128 tokens
+constexpr int kMmqScaleChunks = 4;
+constexpr int kMmqScaleChunkBytes = kMmqScaleChunkBlocks * kMmqTileTokens * 4;
 
 struct MmqShared {
     uint64_t smem_full[kMmqStages];
     uint64_t smem_empty[kMmqStages];
     uint64_t tmem_full[kMmqTmemBuffers];
     uint64_t tmem_empty[kMmqTmemBuffers];
+    uint64_t scale_full[kMmqScaleChunks];
+    uint64_t scale_empty[kMmqScaleChunks];
     uint32_t tmem_base;
     int abort_flag;
 };
 
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    return static_cast<unsigned long long>(__float_as_uint(lo)) |
+        (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
+}
+
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+    unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 template <bool DOTS>
 __global__ void __launch_bounds__(kMmqThreads, 1)
 q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
-    const __grid_constant__ CUtensorMap act_map, const __grid_constant__ MmqParams p) {
+    const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap scale_map,
+    const __grid_constant__ MmqParams p) {
     extern __shared__ uint8_t mmq_smem_raw[];
-    // [stages x (A 16 KB | B 16 KB)] [activation scales: blocks x 128 floats] [barriers]
+    // [stages x (A 16 KB | B 16 KB)] [scale chunks: 4 x 8 KB] [barriers]
     // Swizzled tiles must start on a 1024-byte boundary: round the base up (the
     // launch reserves the slack).
     uint8_t *mmq_smem = mmq_smem_raw + ((1024u - (smem_u32(mmq_smem_raw) & 1023u)) & 1023u);
     uint8_t *stage_base = mmq_smem;
-    float *da_s = reinterpret_cast<float *>(mmq_smem + kMmqStages * kMmqStageBytes);
-    MmqShared *sh = reinterpret_cast<MmqShared *>(
-        reinterpret_cast<uint8_t *>(da_s) + static_cast<size_t>(p.blocks) * kMmqTileTokens * 4);
+    uint8_t *scale_base = mmq_smem + kMmqStages * kMmqStageBytes;
+    MmqShared *sh = reinterpret_cast<MmqShared *>(scale_base +
+        kMmqScaleChunks * kMmqScaleChunkBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int row0 = blockIdx.x * kMmqTileRows;
-    const int token0 = blockIdx.y * kMmqTileTokens;
-    const int stages_total = p.blocks / kMmqStageBlocks;
     volatile int *abort_flag = &sh->abort_flag;
+
+    const long long total_units = static_cast<long long>(p.tiles) * p.stages_per_tile;
+    const long long unit_begin = mmq_unit_begin(total_units, gridDim.x, blockIdx.x);
+    const long long unit_end = mmq_unit_begin(total_units, gridDim.x, blockIdx.x + 1);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMmqStages; ++s) {
@@ -235,16 +292,14 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
             mbar_init(&sh->tmem_full[b], 1);
             mbar_init(&sh->tmem_empty[b], kMmqEpilogueWarps);
         }
+        for (int c = 0; c < kMmqScaleChunks; ++c) {
+            mbar_init(&sh->scale_full[c], 1);
+            mbar_init(&sh->scale_empty[c], kMmqEpilogueWarps);
+        }
         sh->abort_flag = 0;
         mbar_fence_init();
     }
     if (warp == 1) tmem_alloc(&sh->tmem_base, 512);
-    // activation scales of this token tile: da_s[b][0..127]
-    for (int i = threadIdx.x; i < p.blocks * kMmqTileTokens; i += kMmqThreads) {
-        const int b = i / kMmqTileTokens;
-        const int t = i - b * kMmqTileTokens;
-        da_s[i] = p.act_scales[static_cast<size_t>(b) * p.padded_tokens + token0 + t];
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -253,30 +308,68 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
         if (lane == 0) {
-            int armed = 0;
-            for (int st = 0; st < stages_total; ++st) {
-                const int s = st % kMmqStages;
-                const int use = st / kMmqStages;
-                if (use > 0 && !mbar_wait_bounded(&sh->smem_empty[s], (use - 1) & 1)) {
-                    atomicExch(p.status, kStatusMmqLoadTimeout);
-                    *abort_flag = 1;
-                    break;
+            int armed = 0;          // stages armed so far (ring position)
+            int chunks = 0;         // scale chunks armed so far
+            bool failed = false;
+            for (long long u = unit_begin; u < unit_end && !failed;) {
+                const int tile = static_cast<int>(u / p.stages_per_tile);
+                const int first_stage = static_cast<int>(u - static_cast<long long>(tile) *
+                    p.stages_per_tile);
+                const long long tile_end = static_cast<long long>(tile + 1) * p.stages_per_tile;
+                const int count = static_cast<int>((tile_end < unit_end ? tile_end : unit_end) - u);
+                const int row0 = (tile % p.tiles_n) * kMmqTileRows;
+                const int token0 = (tile / p.tiles_n) * kMmqTileTokens;
+                for (int i = 0; i < count; ++i) {
+                    const int st = first_stage + i;
+                    if ((i & 3) == 0) {
+                        // activation scales of the next 16 blocks of this piece
+                        const int c = chunks % kMmqScaleChunks;
+                        const int use = chunks / kMmqScaleChunks;
+                        if (use > 0 && !mbar_wait_bounded(&sh->scale_empty[c], (use - 1) & 1)) {
+                            atomicExch(p.status, kStatusMmqLoadTimeout);
+                            *abort_flag = 1;
+                            failed = true;
+                            break;
+                        }
+                        mbar_arrive_expect_tx(&sh->scale_full[c], kMmqScaleChunkBytes);
+                        tma_load_2d(scale_base + c * kMmqScaleChunkBytes, &scale_map, token0,
+                            st * kMmqStageBlocks, &sh->scale_full[c]);
+                        ++chunks;
+                    }
+                    const int s = armed % kMmqStages;
+                    const int use = armed / kMmqStages;
+                    if (use > 0 && !mbar_wait_bounded(&sh->smem_empty[s], (use - 1) & 1)) {
+                        atomicExch(p.status, kStatusMmqLoadTimeout);
+                        *abort_flag = 1;
+                        failed = true;
+                        break;
+                    }
+                    if (*abort_flag) {
+                        failed = true;
+                        break;
+                    }
+                    uint8_t *dst = stage_base + s * kMmqStageBytes;
+                    mbar_arrive_expect_tx(&sh->smem_full[s], kMmqStageBytes);
+                    tma_load_2d(dst, &weights_map, st * 128, row0, &sh->smem_full[s]);
+                    tma_load_2d(dst + kMmqTileRows * 128, &act_map, st * 128, token0,
+                        &sh->smem_full[s]);
+                    ++armed;
                 }
-                if (*abort_flag) break;
-                uint8_t *dst = stage_base + s * kMmqStageBytes;
-                mbar_arrive_expect_tx(&sh->smem_full[s], kMmqStageBytes);
-                tma_load_2d(dst, &weights_map, st * 128, row0, &sh->smem_full[s]);
-                tma_load_2d(dst + kMmqTileRows * 128, &act_map, st * 128, token0,
-                    &sh->smem_full[s]);
-                armed = st + 1;
+                u += count;
             }
-            if (*abort_flag) {
+            if (failed || *abort_flag) {
                 // let the loads that are still in flight land before the CTA ends
                 const int lap = armed < kMmqStages ? armed : kMmqStages;
                 for (int k = 0; k < lap; ++k) {
                     const int n = armed - 1 - k;
                     mbar_wait_bounded(&sh->smem_full[n % kMmqStages], (n / kMmqStages) & 1,
                         1u << 16);
+                }
+                const int clap = chunks < kMmqScaleChunks ? chunks : kMmqScaleChunks;
+                for (int k = 0; k < clap; ++k) {
+                    const int n = chunks - 1 - k;
+                    mbar_wait_bounded(&sh->scale_full[n % kMmqScaleChunks],
+                        (n / kMmqScaleChunks) & 1, 1u << 16);
                 }
             }
         }
@@ -285,9 +378,11 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
         if (lane == 0) {
             const uint32_t idesc = mmq_instr_desc(kMmqTileRows, kMmqTileTokens);
             bool failed = false;
-            for (int st = 0; st < stages_total && !failed; ++st) {
-                const int s = st % kMmqStages;
-                if (!mbar_wait_bounded(&sh->smem_full[s], (st / kMmqStages) & 1)) {
+            int consumed = 0;       // stages consumed (ring position)
+            int issued = 0;         // MMAs issued (TMEM ring position)
+            for (long long u = unit_begin; u < unit_end && !failed; ++u, ++consumed) {
+                const int s = consumed % kMmqStages;
+                if (!mbar_wait_bounded(&sh->smem_full[s], (consumed / kMmqStages) & 1)) {
                     atomicExch(p.status, kStatusMmqLoadTimeout);
                     *abort_flag = 1;
                     break;
@@ -296,10 +391,9 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const uint8_t *tile = stage_base + s * kMmqStageBytes;
                 const uint64_t desc_a = smem_desc_k_major_sw128(tile);
                 const uint64_t desc_b = smem_desc_k_major_sw128(tile + kMmqTileRows * 128);
-                for (int j = 0; j < kMmqStageBlocks; ++j) {
-                    const int kb = st * kMmqStageBlocks + j;
-                    const int buf = kb % kMmqTmemBuffers;
-                    const int use = kb / kMmqTmemBuffers;
+                for (int j = 0; j < kMmqStageBlocks; ++j, ++issued) {
+                    const int buf = issued % kMmqTmemBuffers;
+                    const int use = issued / kMmqTmemBuffers;
                     if (use > 0) {
                         if (!mbar_wait_bounded(&sh->tmem_empty[buf], (use - 1) & 1)) {
                             atomicExch(p.status, kStatusMmqDrainTimeout);
@@ -327,68 +421,135 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
         const int ew = warp - 2;
         const int quadrant = warp & 3;              // TMEM lanes this warp may touch
         const int col0 = (ew >> 2) * 64;            // token columns of this warp
-        const int row = row0 + quadrant * 32 + lane;
-        const bool row_ok = row < p.rows;
-        const uint8_t *scale_plane = p.weights +
-            static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
-        float acc[64];
-#pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+        unsigned long long acc[32];                 // 64 fp32 accumulators, packed in pairs
         bool failed = false;
-        for (int kb = 0; kb < p.blocks && !failed; ++kb) {
-            const int buf = kb % kMmqTmemBuffers;
-            bool ready = true;
-            if (lane == 0) {
-                ready = mbar_wait_bounded(&sh->tmem_full[buf], (kb / kMmqTmemBuffers) & 1);
-                if (!ready) {
-                    atomicExch(p.status, kStatusMmqMmaTimeout);
-                    *abort_flag = 1;
+        int drained = 0;        // accumulators drained (TMEM ring position)
+        int chunks = 0;         // scale chunks consumed
+        for (long long u = unit_begin; u < unit_end && !failed;) {
+            const int tile = static_cast<int>(u / p.stages_per_tile);
+            const int first_stage = static_cast<int>(u - static_cast<long long>(tile) *
+                p.stages_per_tile);
+            const long long tile_end = static_cast<long long>(tile + 1) * p.stages_per_tile;
+            const int count = static_cast<int>((tile_end < unit_end ? tile_end : unit_end) - u);
+            const int row0 = (tile % p.tiles_n) * kMmqTileRows;
+            const int token0 = (tile / p.tiles_n) * kMmqTileTokens;
+            const int row = row0 + quadrant * 32 + lane;
+            const bool row_ok = row < p.rows;
+            const uint8_t *scale_plane = p.weights +
+                static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+
+            for (int i = 0; i < count && !failed; ++i) {
+                const int st = first_stage + i;
+                const int chunk = (chunks + (i >> 2)) % kMmqScaleChunks;
+                if ((i & 3) == 0) {
+                    const int n = chunks + (i >> 2);
+                    if (!mbar_wait_bounded(&sh->scale_full[chunk], (n / kMmqScaleChunks) & 1)) {
+                        if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
+                        *abort_flag = 1;
+                        failed = true;
+                        break;
+                    }
+                }
+                // the four weight scales of this stage: 8 bytes, 8-byte aligned
+                const uint2 dw4 = *reinterpret_cast<const uint2 *>(scale_plane +
+                    st * kMmqStageBlocks * 2);
+                const float *da_stage = reinterpret_cast<const float *>(scale_base +
+                    chunk * kMmqScaleChunkBytes) + (i & 3) * kMmqStageBlocks * kMmqTileTokens;
+#pragma unroll
+                for (int j = 0; j < kMmqStageBlocks; ++j, ++drained) {
+                    const int buf = drained % kMmqTmemBuffers;
+                    const uint32_t parity = (drained / kMmqTmemBuffers) & 1;
+                    bool ready = true;
+                    if (lane == 0) {
+                        ready = mbar_wait_bounded(&sh->tmem_full[buf], parity);
+                        if (!ready) {
+                            atomicExch(p.status, kStatusMmqMmaTimeout);
+                            *abort_flag = 1;
+                        }
+                    }
+                    ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+                    if (!ready || *abort_flag) {
+                        failed = true;
+                        break;
+                    }
+                    mbar_wait_bounded(&sh->tmem_full[buf], parity, 1u << 10);
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base +
+                        (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kMmqTileTokens + col0;
+                    uint32_t v0[32], v1[32];
+                    tmem_load_32(taddr, v0);
+                    tmem_load_32(taddr + 32, v1);
+                    tmem_load_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+
+                    const uint32_t word = j < 2 ? dw4.x : dw4.y;
+                    const float dw = half_bits_to_float(
+                        static_cast<uint16_t>((j & 1) ? (word >> 16) : (word & 0xffffu)));
+                    const unsigned long long dw2 = pack2(dw, dw);
+                    const float4 *da = reinterpret_cast<const float4 *>(da_stage +
+                        j * kMmqTileTokens + col0);
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) {
+                        const float4 a = da[q];
+                        const float4 b = da[8 + q];
+                        acc[2 * q] = fma2(pack2(static_cast<float>(static_cast<int>(v0[4 * q])),
+                            static_cast<float>(static_cast<int>(v0[4 * q + 1]))),
+                            mul2(dw2, pack2(a.x, a.y)), acc[2 * q]);
+                        acc[2 * q + 1] = fma2(
+                            pack2(static_cast<float>(static_cast<int>(v0[4 * q + 2])),
+                                static_cast<float>(static_cast<int>(v0[4 * q + 3]))),
+                            mul2(dw2, pack2(a.z, a.w)), acc[2 * q + 1]);
+                        acc[16 + 2 * q] = fma2(
+                            pack2(static_cast<float>(static_cast<int>(v1[4 * q])),
+                                static_cast<float>(static_cast<int>(v1[4 * q + 1]))),
+                            mul2(dw2, pack2(b.x, b.y)), acc[16 + 2 * q]);
+                        acc[16 + 2 * q + 1] = fma2(
+                            pack2(static_cast<float>(static_cast<int>(v1[4 * q + 2])),
+                                static_cast<float>(static_cast<int>(v1[4 * q + 3]))),
+                            mul2(dw2, pack2(b.z, b.w)), acc[16 + 2 * q + 1]);
+                    }
+                    if (DOTS && row_ok) {
+                        const int kb = st * kMmqStageBlocks + j;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const int t0 = token0 + col0 + e;
+                            if (t0 < p.tokens)
+                                p.block_dots[(static_cast<size_t>(t0) * p.rows + row) * p.blocks +
+                                    kb] = static_cast<int>(v0[e]);
+                            if (t0 + 32 < p.tokens)
+                                p.block_dots[(static_cast<size_t>(t0 + 32) * p.rows + row) *
+                                    p.blocks + kb] = static_cast<int>(v1[e]);
+                        }
+                    }
+                }
+                if (!failed && ((i & 3) == 3 || i == count - 1)) {
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sh->scale_empty[chunk]);
                 }
             }
-            ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-            if (!ready || *abort_flag) {
-                failed = true;
-                break;
-            }
-            mbar_wait_bounded(&sh->tmem_full[buf], (kb / kMmqTmemBuffers) & 1, 1u << 10);
-            tc_fence_after();
-            const float dw = half_bits_to_float(
-                *reinterpret_cast<const uint16_t *>(scale_plane + kb * 2));
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quadrant * 32) << 16) +
-                buf * kMmqTileTokens + col0;
-            uint32_t v0[32], v1[32];
-            tmem_load_32(taddr, v0);
-            tmem_load_32(taddr + 32, v1);
-            tmem_load_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
-            const float *da = da_s + kb * kMmqTileTokens + col0;
+            chunks += (count + 3) >> 2;
+            if (!failed && row_ok && p.output) {
+                const bool split = count != p.stages_per_tile;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                acc[i] = fmaf(dw * da[i], static_cast<float>(static_cast<int>(v0[i])), acc[i]);
-                acc[32 + i] = fmaf(dw * da[32 + i], static_cast<float>(static_cast<int>(v1[i])),
-                    acc[32 + i]);
-            }
-            if (DOTS && row_ok) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int t0 = token0 + col0 + i;
-                    if (t0 < p.tokens)
-                        p.block_dots[(static_cast<size_t>(t0) * p.rows + row) * p.blocks + kb] =
-                            static_cast<int>(v0[i]);
-                    if (t0 + 32 < p.tokens)
-                        p.block_dots[(static_cast<size_t>(t0 + 32) * p.rows + row) * p.blocks + kb] =
-                            static_cast<int>(v1[i]);
+                for (int e = 0; e < 32; ++e) {
+                    const int t = token0 + col0 + 2 * e;
+                    const float lo = __uint_as_float(static_cast<uint32_t>(acc[e]));
+                    const float hi = __uint_as_float(static_cast<uint32_t>(acc[e] >> 32));
+                    float *dst = p.output + static_cast<size_t>(t) * p.rows + row;
+                    if (split) {
+                        if (t < p.tokens) atomicAdd(dst, lo);
+                        if (t + 1 < p.tokens) atomicAdd(dst + p.rows, hi);
+                    } else {
+                        if (t < p.tokens) *dst = lo;
+                        if (t + 1 < p.tokens) dst[p.rows] = hi;
+                    }
                 }
             }
-        }
-        if (!failed && row_ok && p.output) {
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const int t = token0 + col0 + i;
-                if (t < p.tokens) p.output[static_cast<size_t>(t) * p.rows + row] = acc[i];
-            }
+            u += count;
         }
     }
 
@@ -397,6 +558,23 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Zeroes the output of every split tile (their pieces arrive as atomic adds).
+__global__ void __launch_bounds__(256)
+mmq_zero_split_kernel(float *__restrict__ output, int rows, int tokens, int tiles_n, int tiles,
+    int stages_per_tile, int grid) {
+    const long long total_units = static_cast<long long>(tiles) * stages_per_tile;
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+        if (!mmq_tile_is_split(total_units, grid, stages_per_tile, tile)) continue;
+        const int row0 = (tile % tiles_n) * kMmqTileRows;
+        const int token0 = (tile / tiles_n) * kMmqTileTokens;
+        for (int i = threadIdx.x; i < kMmqTileRows * kMmqTileTokens; i += blockDim.x) {
+            const int r = row0 + (i & (kMmqTileRows - 1));
+            const int t = token0 + i / kMmqTileRows;
+            if (r < rows && t < tokens) output[static_cast<size_t>(t) * rows + r] = 0.0f;
+        }
     }
 }
 
@@ -415,6 +593,20 @@ inline EncodeTiledFn mmq_encode_fn() {
             fn = reinterpret_cast<EncodeTiledFn>(entry);
     }
     return fn;
+}
+
+// fp32 matrix `rows` x `cols`, dense; boxes of 16 rows x 128 columns, no swizzle.
+inline bool mmq_make_scale_map(CUtensorMap *map, const void *base, int rows, int cols) {
+    EncodeTiledFn encode = mmq_encode_fn();
+    if (!encode) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(float)};
+    const cuuint32_t box[2] = {kMmqTileTokens, kMmqScaleChunkBlocks};
+    const cuuint32_t elem[2] = {1, 1};
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims,
+               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+        CUDA_SUCCESS;
 }
 
 // int8 matrix, `rows` x `width` bytes, row pitch `pitch`; boxes of 128 rows x 128 bytes.
@@ -444,9 +636,10 @@ inline cudaError_t mmq_reserve(void **aux, size_t *aux_bytes, int rows, int widt
     return error;
 }
 
-inline size_t mmq_smem_bytes(int blocks) {
+inline size_t mmq_smem_bytes() {
     return static_cast<size_t>(kMmqStages) * kMmqStageBytes +
-        static_cast<size_t>(blocks) * kMmqTileTokens * 4 + sizeof(MmqShared) + 64 + 1024;
+        static_cast<size_t>(kMmqScaleChunks) * kMmqScaleChunkBytes + sizeof(MmqShared) + 64 +
+        1024;
 }
 
 // activation: fp32 [tokens][width] (act == 1) or Q8_0 blocks (act == 0), device memory.
@@ -465,8 +658,9 @@ inline cudaError_t mmq_enqueue(cudaStream_t stream, int sm_count, int *status,
             return cudaErrorNotSupported;
         plan->ready = true;
     }
-    CUtensorMap act_map;
+    CUtensorMap act_map, scale_map;
     if (!mmq_make_map(&act_map, quants, padded, width, width)) return cudaErrorNotSupported;
+    if (!mmq_make_scale_map(&scale_map, scales, blocks, padded)) return cudaErrorNotSupported;
 
     const long long prep_warps = static_cast<long long>(padded) * blocks;
     const int prep_grid = static_cast<int>(std::max<long long>(1,
@@ -489,23 +683,34 @@ inline cudaError_t mmq_enqueue(cudaStream_t stream, int sm_count, int *status,
     p.row_stride = row_stride;
     p.tokens = tokens;
     p.padded_tokens = padded;
-    p.act_scales = scales;
+    p.tiles_n = (rows + kMmqTileRows - 1) / kMmqTileRows;
+    p.tiles = p.tiles_n * (padded / kMmqTileTokens);
+    p.stages_per_tile = blocks / kMmqStageBlocks;
     p.output = output;
     p.block_dots = block_dots;
     p.status = status;
-    const size_t smem = mmq_smem_bytes(blocks);
-    if (smem > 227 * 1024) return cudaErrorInvalidValue;
-    const dim3 grid((rows + kMmqTileRows - 1) / kMmqTileRows, padded / kMmqTileTokens);
+    const size_t smem = mmq_smem_bytes();
+    const long long total_units = static_cast<long long>(p.tiles) * p.stages_per_tile;
+    const int grid = static_cast<int>(std::min<long long>(sm_count, total_units));
+    if (output) {
+        mmq_zero_split_kernel<<<std::min(p.tiles, sm_count * 4), 256, 0, stream>>>(output, rows,
+            tokens, p.tiles_n, p.tiles, p.stages_per_tile, grid);
+        ++*launches;
+        error = cudaGetLastError();
+        if (error != cudaSuccess) return error;
+    }
     if (block_dots) {
         error = cudaFuncSetAttribute(q8_mmq_kernel<true>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (error != cudaSuccess) return error;
-        q8_mmq_kernel<true><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map, p);
+        q8_mmq_kernel<true><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map,
+            scale_map, p);
     } else {
         error = cudaFuncSetAttribute(q8_mmq_kernel<false>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (error != cudaSuccess) return error;
-        q8_mmq_kernel<false><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map, p);
+        q8_mmq_kernel<false><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map,
+            scale_map, p);
     }
     ++*launches;
     return cudaGetLastError();

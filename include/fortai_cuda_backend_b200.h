@@ -19,6 +19,9 @@
  *    them and must be destroyed before it;
  *  - "host" calls block until the result is in host memory; "device" calls only
  *    enqueue on the context's stream;
+ *  - device fp32 activation pointers must be 16-byte aligned and device Q8_0
+ *    activation pointers 2-byte aligned (anything from device_buffer_create is);
+ *    a misaligned pointer is reported as RUNTIME_ERROR, not dereferenced;
  *  - a Q8_0 block is 34 bytes: little-endian binary16 scale, then 32 int8.
  *    Weight matrices arrive as rows x (width/32) blocks, row-major.  The device
  *    copy is re-laid-out at upload (the handle is opaque), so a weights handle
@@ -197,7 +200,7 @@ uint64_t fortai_cuda_q8_context_launch_count(const fortai_cuda_q8_context *conte
 int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context);
 /* Tuning knobs, by name: "gemv_variant" (0 = automatic, 1 = half-block-per-lane
  * kernel with 16-byte loads, 2 = bulk-copy ring, 3 = block-per-lane kernel with
- * 32-byte loads), "gemv_ctas_per_sm", "gemv_rows_per_warp", "ring_stages",
+ * 32-byte loads, 4 = register-pipelined kernel where the shape allows it), "gemv_ctas_per_sm", "gemv_rows_per_warp", "ring_stages",
  * "ring_rows", "mmq_min_tokens".  Zero means automatic.  Unknown names return
  * INVALID. */
 int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context, const char *name,

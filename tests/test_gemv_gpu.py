@@ -9,7 +9,7 @@ from conftest import ROOT, golden, l2_tolerance, reference_gate
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [1, 2, 3]   # 1 = half-block per lane, 2 = bulk-copy ring, 3 = block per lane
+VARIANTS = [0, 1, 2, 3]   # 0 = automatic (register-pipelined where the shape allows), 1 = half-block per lane, 2 = bulk-copy ring, 3 = block per lane
 
 
 def check_vector(actual, expected):
