@@ -196,7 +196,7 @@ def workload_config(n_gpus):
     return {
         "workload": f"lm_head Q8_0 GEMV {ROWS}x{WIDTH} batch 1 (BASELINE configs[2])",
         "rows": ROWS, "width": WIDTH, "weight_bytes": WEIGHT_BYTES,
-        "sharding": "none" if n_gpus == 1 else f"rows/{n_gpus} per rank + all-gather of fp32 logits",
+        "sharding": "none" if n_gpus == 1 else f"rows/{n_gpus} per rank, fp32 logits reassembled on every rank",
         "cache": "inputs larger than L2 (413 MB of weights per step, L2 is 126 MB)",
         "inputs": "weights ~N(0,0.02) quantized to Q8_0 on the device, activation ~N(0,1), seed 0",
     }
@@ -252,10 +252,10 @@ def run_gpu_arm(args):
         raise SystemExit(f"context creation failed: {stat}")
 
     # ---- this rank's shard of the lm_head
-    base, extra = divmod(ROWS, world)
-    counts = [base + (1 if r < extra else 0) for r in range(world)]
-    first_row = sum(counts[:rank])
-    my_rows = counts[rank]
+    from fortai_b200 import sharded
+    ranges = sharded.partition(ROWS, world)
+    counts = [c for _, c in ranges]
+    first_row, my_rows = ranges[rank]
     host_weights = make_device_weights(torch, backend, ctx, first_row, my_rows, WIDTH, seed=0)
     weights = backend.cuda_q8_weights_t()
     stat = weights.upload(ctx, host_weights, host_weights.size, my_rows, WIDTH)
@@ -265,21 +265,65 @@ def run_gpu_arm(args):
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
     x = torch.randn(WIDTH, generator=gen, device="cuda", dtype=torch.float32)
-    logits = torch.empty(ROWS, device="cuda", dtype=torch.float32)
-    equal_split = extra == 0
-    my_slice = logits[first_row:first_row + my_rows]
-    pieces = [logits[sum(counts[:r]):sum(counts[:r]) + counts[r]] for r in range(world)]
 
-    def step():
+    # The logits vector lives in symmetric memory when there are peers, so that the GEMV
+    # epilogue can store this rank's slice straight into every rank's copy.
+    peer_ptrs, symm_handle = None, None
+    logits = None
+    if world > 1 and args.exchange in ("auto", "peers"):
+        try:
+            import torch.distributed._symmetric_memory as symm
+            logits = symm.empty(ROWS, dtype=torch.float32, device=torch.device("cuda", local_rank))
+            symm_handle = symm.rendezvous(logits, dist.group.WORLD)
+            peer_ptrs = [int(p) for p in symm_handle.buffer_ptrs]
+        except Exception as error:  # no peer access on this box: fall back to NCCL
+            if args.exchange == "peers":
+                raise SystemExit(f"symmetric memory unavailable: {error}")
+            peer_ptrs, symm_handle, logits = None, None, None
+    if logits is None:
+        logits = torch.empty(ROWS, device="cuda", dtype=torch.float32)
+    my_slice = logits[first_row:first_row + my_rows]
+
+    def step_allgather():
         stat = backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH,
                                                  my_slice.data_ptr(), my_rows)
         if not stat.is_ok():
             raise RuntimeError(f"matvec failed: {stat}")
         if world > 1:
-            if equal_split:
-                dist.all_gather_into_tensor(logits, my_slice)
-            else:
-                dist.all_gather(pieces, my_slice)
+            sharded.all_gather_rows(dist, my_slice, counts, logits)
+
+    def step_peers():
+        stat = backend.cuda_q8_matvec_device_f32_peers(ctx, weights, x.data_ptr(), WIDTH,
+                                                       peer_ptrs, first_row, ROWS)
+        if not stat.is_ok():
+            raise RuntimeError(f"peer matvec failed: {stat}")
+        symm_handle.barrier(channel=0)
+
+    def time_steps(fn, n):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(n):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / n], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    exchange = "none"
+    exchange_ms = {}
+    step = step_allgather
+    if world > 1:
+        exchange = "allgather"
+        exchange_ms["allgather"] = time_steps(step_allgather, 200)
+        if peer_ptrs is not None:
+            exchange_ms["peers"] = time_steps(step_peers, 200)
+            if args.exchange == "peers" or exchange_ms["peers"] < exchange_ms["allgather"]:
+                exchange, step = "peers", step_peers
 
     def barrier():
         torch.cuda.synchronize()
@@ -349,10 +393,7 @@ def run_gpu_arm(args):
         _, stat = backend.cuda_q8_matvec_host_f32(ctx, weights, hx, ho)
         if world > 1:
             my_slice.copy_(host_out, non_blocking=True)
-            if equal_split:
-                dist.all_gather_into_tensor(logits, my_slice)
-            else:
-                dist.all_gather(pieces, my_slice)
+            sharded.all_gather_rows(dist, my_slice, counts, logits)
             torch.cuda.synchronize()
     barrier()
     e2e_s = time.perf_counter() - te
@@ -383,7 +424,7 @@ def run_gpu_arm(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 scales", "data": "synthetic",
-        "config": workload_config(world),
+        "config": dict(workload_config(world), exchange=exchange, exchange_ms_per_step=exchange_ms),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "traffic": GEMV_DRAM_TRAFFIC_BYTES,
                      "peak_source": f"of {peak_kind}",
@@ -473,6 +514,8 @@ def main():
     parser.add_argument("--steps", type=int, default=20000)
     parser.add_argument("--warmup", type=int, default=200)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    parser.add_argument("--exchange", default="auto", choices=["auto", "allgather", "peers"],
+                        help="how row shards are reassembled when --gpus > 1")
     parser.add_argument("--rows", type=int, default=ROWS,
                         help="row count of the GEMV (smaller cases are for profiler captures)")
     parser.add_argument("--mmq-only", action="store_true",

@@ -19,8 +19,8 @@
 //                 K-bytes of weights and of activations per stage (= 4 blocks), and
 //                 one 2-D load of activation scales per 16 blocks
 //   warp 1        TMEM allocation, MMA issue (one elected thread), commits
-//   warps 2..9    epilogue: warp w owns TMEM lanes 32*(w%4).. and 64 of the 128
-//                 token columns; 64 fp32 accumulators per thread, updated with
+//   warps 2..17   epilogue: warp w owns TMEM lanes 32*(w%4).. and 32 of the 128
+//                 token columns; 32 fp32 accumulators per thread, updated with
 //                 packed f32x2 multiply and fused multiply-add
 //
 // The grid is persistent (one CTA per SM); work is split in units of one stage of
@@ -44,7 +44,7 @@ constexpr int kMmqTileTokens = 128;   // tokens per CTA (MMA N)
 constexpr int kMmqStageBlocks = 4;    // Q8_0 blocks per pipeline stage (128 K-bytes)
 constexpr int kMmqStages = 4;
 constexpr int kMmqTmemBuffers = 4;
-constexpr int kMmqEpilogueWarps = 8;
+constexpr int kMmqEpilogueWarps = 16;
 constexpr int kMmqThreads = (2 + kMmqEpilogueWarps) * 32;
 constexpr int kMmqStageBytes = (kMmqTileRows + kMmqTileTokens) * 128;
 
@@ -242,9 +242,24 @@ struct MmqShared {
     int abort_flag;
 };
 
+// Two floats as one 64-bit register pair.  mov.b64 lets ptxas put the halves in
+// adjacent registers instead of assembling the pair with integer moves.
 __device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
-    return static_cast<unsigned long long>(__float_as_uint(lo)) |
-        (static_cast<unsigned long long>(__float_as_uint(hi)) << 32);
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+// (float(a), float(b)) of two int32 accumulator words, packed.
+__device__ __forceinline__ unsigned long long cvt2(uint32_t a, uint32_t b) {
+    float lo, hi;
+    asm("cvt.rn.f32.s32 %0, %1;" : "=f"(lo) : "r"(a));
+    asm("cvt.rn.f32.s32 %0, %1;" : "=f"(hi) : "r"(b));
+    return pack2(lo, hi);
 }
 
 __device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
@@ -420,8 +435,8 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
         // ------------------------------ epilogue ----------------------------------
         const int ew = warp - 2;
         const int quadrant = warp & 3;              // TMEM lanes this warp may touch
-        const int col0 = (ew >> 2) * 64;            // token columns of this warp
-        unsigned long long acc[32];                 // 64 fp32 accumulators, packed in pairs
+        const int col0 = (ew >> 2) * 32;            // token columns of this warp
+        unsigned long long acc[16];                 // 32 fp32 accumulators, packed in pairs
         bool failed = false;
         int drained = 0;        // accumulators drained (TMEM ring position)
         int chunks = 0;         // scale chunks consumed
@@ -438,7 +453,12 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
             const uint8_t *scale_plane = p.weights +
                 static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) acc[i] = 0ull;
+            for (int i = 0; i < 16; ++i) acc[i] = 0ull;
+            // The four fp16 weight scales of a stage are 8 aligned bytes of the row's
+            // scale plane; they are fetched one stage ahead so that the L2 latency
+            // hides behind a whole stage of drain work.
+            uint2 dw_next = *reinterpret_cast<const uint2 *>(scale_plane +
+                first_stage * kMmqStageBlocks * 2);
 
             for (int i = 0; i < count && !failed; ++i) {
                 const int st = first_stage + i;
@@ -452,35 +472,27 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                         break;
                     }
                 }
-                // the four weight scales of this stage: 8 bytes, 8-byte aligned
-                const uint2 dw4 = *reinterpret_cast<const uint2 *>(scale_plane +
-                    st * kMmqStageBlocks * 2);
+                const uint2 dw4 = dw_next;
+                if (i + 1 < count)
+                    dw_next = *reinterpret_cast<const uint2 *>(scale_plane +
+                        (st + 1) * kMmqStageBlocks * 2);
                 const float *da_stage = reinterpret_cast<const float *>(scale_base +
                     chunk * kMmqScaleChunkBytes) + (i & 3) * kMmqStageBlocks * kMmqTileTokens;
 #pragma unroll
                 for (int j = 0; j < kMmqStageBlocks; ++j, ++drained) {
                     const int buf = drained % kMmqTmemBuffers;
                     const uint32_t parity = (drained / kMmqTmemBuffers) & 1;
-                    bool ready = true;
-                    if (lane == 0) {
-                        ready = mbar_wait_bounded(&sh->tmem_full[buf], parity);
-                        if (!ready) {
-                            atomicExch(p.status, kStatusMmqMmaTimeout);
-                            *abort_flag = 1;
-                        }
-                    }
-                    ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-                    if (!ready || *abort_flag) {
+                    if (!mbar_wait_bounded(&sh->tmem_full[buf], parity)) {
+                        if (lane == 0) atomicExch(p.status, kStatusMmqMmaTimeout);
+                        *abort_flag = 1;
                         failed = true;
                         break;
                     }
-                    mbar_wait_bounded(&sh->tmem_full[buf], parity, 1u << 10);
                     tc_fence_after();
                     const uint32_t taddr = tmem_base +
                         (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kMmqTileTokens + col0;
-                    uint32_t v0[32], v1[32];
-                    tmem_load_32(taddr, v0);
-                    tmem_load_32(taddr + 32, v1);
+                    uint32_t v[32];
+                    tmem_load_32(taddr, v);
                     tmem_load_wait();
                     tc_fence_before();
                     __syncwarp();
@@ -495,22 +507,10 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
                         const float4 a = da[q];
-                        const float4 b = da[8 + q];
-                        acc[2 * q] = fma2(pack2(static_cast<float>(static_cast<int>(v0[4 * q])),
-                            static_cast<float>(static_cast<int>(v0[4 * q + 1]))),
+                        acc[2 * q] = fma2(cvt2(v[4 * q], v[4 * q + 1]),
                             mul2(dw2, pack2(a.x, a.y)), acc[2 * q]);
-                        acc[2 * q + 1] = fma2(
-                            pack2(static_cast<float>(static_cast<int>(v0[4 * q + 2])),
-                                static_cast<float>(static_cast<int>(v0[4 * q + 3]))),
+                        acc[2 * q + 1] = fma2(cvt2(v[4 * q + 2], v[4 * q + 3]),
                             mul2(dw2, pack2(a.z, a.w)), acc[2 * q + 1]);
-                        acc[16 + 2 * q] = fma2(
-                            pack2(static_cast<float>(static_cast<int>(v1[4 * q])),
-                                static_cast<float>(static_cast<int>(v1[4 * q + 1]))),
-                            mul2(dw2, pack2(b.x, b.y)), acc[16 + 2 * q]);
-                        acc[16 + 2 * q + 1] = fma2(
-                            pack2(static_cast<float>(static_cast<int>(v1[4 * q + 2])),
-                                static_cast<float>(static_cast<int>(v1[4 * q + 3]))),
-                            mul2(dw2, pack2(b.z, b.w)), acc[16 + 2 * q + 1]);
                     }
                     if (DOTS && row_ok) {
                         const int kb = st * kMmqStageBlocks + j;
@@ -519,10 +519,7 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                             const int t0 = token0 + col0 + e;
                             if (t0 < p.tokens)
                                 p.block_dots[(static_cast<size_t>(t0) * p.rows + row) * p.blocks +
-                                    kb] = static_cast<int>(v0[e]);
-                            if (t0 + 32 < p.tokens)
-                                p.block_dots[(static_cast<size_t>(t0 + 32) * p.rows + row) *
-                                    p.blocks + kb] = static_cast<int>(v1[e]);
+                                    kb] = static_cast<int>(v[e]);
                         }
                     }
                 }
@@ -535,10 +532,10 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
             if (!failed && row_ok && p.output) {
                 const bool split = count != p.stages_per_tile;
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
+                for (int e = 0; e < 16; ++e) {
                     const int t = token0 + col0 + 2 * e;
-                    const float lo = __uint_as_float(static_cast<uint32_t>(acc[e]));
-                    const float hi = __uint_as_float(static_cast<uint32_t>(acc[e] >> 32));
+                    float lo, hi;
+                    unpack2(acc[e], lo, hi);
                     float *dst = p.output + static_cast<size_t>(t) * p.rows + row;
                     if (split) {
                         if (t < p.tokens) atomicAdd(dst, lo);

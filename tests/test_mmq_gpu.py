@@ -53,7 +53,9 @@ def test_ragged_shapes_and_block_dots(backend, context, dev, oracle, tokens, row
     dres = dev.buffer(4 * tokens * rows)
     ms, stat = backend.cuda_q8_matmul_resident(context, w, dq, tokens, dres)
     assert stat.is_ok(), stat
-    assert np.array_equal(dev.floats(dres, tokens * rows), dev.floats(dout, tokens * rows))
+    # a tile shared by two CTAs is completed with fp32 atomic adds, so two runs may differ
+    # in the last bit; both must meet the bound against the oracle
+    check_rows(dev.floats(dres, tokens * rows).reshape(tokens, rows), expected)
     ddots = dev.buffer(4 * tokens * rows * blocks)
     assert backend.cuda_q8_matmul_block_dots_device(context, w, dq, tokens, ddots,
                                                     tokens * rows * blocks).is_ok()

@@ -1,0 +1,140 @@
+"""Sharded paths on real GPUs.  Single-GPU parts check the shard kernels against the
+oracle; the multi-rank part spawns one process per GPU (needs >= 2 GPUs)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, l2_tolerance
+
+pytestmark = pytest.mark.gpu
+
+
+def test_row_shards_on_one_gpu_reproduce_the_full_matvec(backend, context, dev, oracle):
+    from fortai_b200 import sharded
+    rows, width, world = 1003, 2560, 4
+    weights = oracle.make_weights(rows, width, seed=1)
+    x = oracle.normal(width, seed=2)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    dx = dev.to_device(x)
+    out = np.zeros(rows, np.float32)
+    for rank in range(world):
+        shard = sharded.RowShardedMatvec(backend, context, weights, rows, width, rank, world)
+        dout = dev.buffer(4 * shard.count)
+        shard.local(dx, dout)
+        out[shard.first:shard.first + shard.count] = dev.floats(dout, shard.count)
+        shard.destroy()
+    assert float(np.abs(out - expected).max()) <= l2_tolerance(expected)
+
+
+def test_peer_epilogue_writes_every_output_vector(backend, context, dev, oracle):
+    rows, width = 300, 1024
+    weights = oracle.make_weights(rows, width, seed=3)
+    x = oracle.normal(width, seed=4)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    w = dev.weights(weights, rows, width)
+    dx = dev.to_device(x)
+    total = rows + 50
+    outs = [dev.to_device(np.full(total, -7.0, np.float32)) for _ in range(3)]
+    stat = backend.cuda_q8_matvec_device_f32_peers(context, w, dx, width, outs, 20, total)
+    assert stat.is_ok(), stat
+    for ptr in outs:
+        got = dev.floats(ptr, total)
+        assert (got[:20] == -7.0).all() and (got[20 + rows:] == -7.0).all()
+        assert float(np.abs(got[20:20 + rows] - expected).max()) <= l2_tolerance(expected)
+    # the slice must fit inside the output vectors
+    assert not backend.cuda_q8_matvec_device_f32_peers(context, w, dx, width, outs, 60, total).is_ok()
+
+
+def test_column_shards_sum_to_the_full_ffn(backend, context, dev, oracle):
+    from fortai_b200 import sharded
+    hidden, inner, world = 1024, 3840, 4
+    gate = oracle.make_weights(inner, hidden, seed=1)
+    up = oracle.make_weights(inner, hidden, seed=2)
+    down = oracle.make_weights(hidden, inner, seed=3)
+    x = oracle.normal(hidden, seed=4)
+    expected = oracle.ffn(gate, up, down, inner, hidden, hidden, x)
+    dx = dev.to_device(x)
+    total = np.zeros(hidden, np.float64)
+    for rank in range(world):
+        ffn = sharded.ShardedFfn(backend, context, gate, up, down, hidden, inner, rank, world)
+        dout = dev.buffer(4 * hidden)
+        stat = backend.cuda_q8_ffn_device(context, ffn.gate, ffn.up, ffn.down, dx, hidden, dout,
+                                          hidden)
+        assert stat.is_ok(), stat
+        total += dev.floats(dout, hidden)
+        ffn.destroy()
+    assert float(np.abs(total - expected).max()) <= 2 * l2_tolerance(expected)
+
+
+def _rank_main(rank, world, port, result_path):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    from fortai_b200 import backend_cuda as b, sharded
+    from oracle import q8_oracle as o
+    failures = []
+    ctx = b.cuda_q8_context_t()
+    assert ctx.create(rank, stream=torch.cuda.current_stream().cuda_stream).is_ok()
+    rows, width = 4099, 2560
+    weights = o.make_weights(rows, width, seed=1)
+    xh = o.normal(width, seed=2)
+    expected = o.matvec(weights, rows, width, xh)[0]
+    x = torch.from_numpy(xh).cuda()
+    shard = sharded.PeerGatherMatvec(b, ctx, weights, rows, width, rank, world)
+    out = torch.zeros(rows, device="cuda")
+    shard.matvec(dist, x, out)
+    torch.cuda.synchronize()
+    if float(np.abs(out.cpu().numpy() - expected).max()) > 1e-5 * float(np.linalg.norm(expected)):
+        failures.append("all-gather path differs from the oracle")
+    try:
+        import torch.distributed._symmetric_memory as symm
+        buf = symm.empty(rows, dtype=torch.float32, device=torch.device("cuda", rank))
+        handle = symm.rendezvous(buf, dist.group.WORLD)
+        buf.zero_()
+        handle.barrier(channel=0)
+        shard.attach([int(p) for p in handle.buffer_ptrs], lambda: handle.barrier(channel=0))
+        shard.matvec_peers(x)
+        torch.cuda.synchronize()
+        if float(np.abs(buf.cpu().numpy() - expected).max()) > 1e-5 * float(np.linalg.norm(expected)):
+            failures.append("peer-store path differs from the oracle")
+    except Exception as error:  # symmetric memory is optional; say so rather than fail
+        failures.append(f"SKIP-PEERS {type(error).__name__}: {error}")
+    # FFN: rows of gate/up, columns of down, all-reduce
+    hidden, inner = 1024, 3840
+    gate, up = o.make_weights(inner, hidden, seed=5), o.make_weights(inner, hidden, seed=6)
+    down = o.make_weights(hidden, inner, seed=7)
+    xf = o.normal(hidden, seed=8)
+    expected_ffn = o.ffn(gate, up, down, inner, hidden, hidden, xf)
+    ffn = sharded.ShardedFfn(b, ctx, gate, up, down, hidden, inner, rank, world)
+    outf = torch.zeros(hidden, device="cuda")
+    ffn.forward(dist, torch.from_numpy(xf).cuda(), outf)
+    torch.cuda.synchronize()
+    if float(np.abs(outf.cpu().numpy() - expected_ffn).max()) > 2e-5 * float(np.linalg.norm(expected_ffn)):
+        failures.append("sharded FFN differs from the oracle")
+    shard.destroy()
+    ffn.destroy()
+    ctx.destroy()
+    with open(f"{result_path}.{rank}", "w") as f:
+        f.write("\n".join(failures))
+    dist.destroy_process_group()
+
+
+def test_ranks_on_separate_gpus(tmp_path):
+    import torch
+    import torch.multiprocessing as mp
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    port = 29600 + (os.getpid() % 2000)
+    result = str(tmp_path / "result")
+    mp.spawn(_rank_main, args=(world, port, result), nprocs=world, join=True)
+    for rank in range(world):
+        lines = [l for l in open(f"{result}.{rank}").read().splitlines() if l]
+        assert [l for l in lines if not l.startswith("SKIP-PEERS")] == [], lines
