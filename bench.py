@@ -37,9 +37,10 @@ BLOCKS = WIDTH // 32
 WEIGHT_BYTES = ROWS * BLOCKS * 34
 MMQ_M, MMQ_K, MMQ_N = 512, 2560, 9728
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of one GEMV launch, from the ncu
-# capture summarised in profiles/ (None until a capture exists)
-GEMV_DRAM_TRAFFIC_BYTES = None
+# dram__bytes_read.sum + dram__bytes_write.sum per weight row, from the ncu capture of a
+# 65536-row launch (181.95 MB; profiles/q8_gemv_pipelined_lm_head.md); traffic grows in
+# proportion to rows, so a launch's traffic is this times its row count
+GEMV_DRAM_TRAFFIC_PER_ROW = 181.95e6 / 65536
 
 
 def set_rows(rows: int) -> None:
@@ -426,7 +427,7 @@ def run_gpu_arm(args):
         "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 scales", "data": "synthetic",
         "config": dict(workload_config(world), exchange=exchange, exchange_ms_per_step=exchange_ms),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": achieved / hbm_peak, "traffic": GEMV_DRAM_TRAFFIC_BYTES,
+                     "frac": achieved / hbm_peak, "traffic": GEMV_DRAM_TRAFFIC_PER_ROW * my_rows,
                      "peak_source": f"of {peak_kind}",
                      "kernel": "q8_gemv (quantize prologue + streaming dot), this rank's shard",
                      "kernel_ms": kernel_ms, "algorithmic_bytes": shard_bytes,
