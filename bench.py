@@ -269,16 +269,22 @@ def run_gpu_arm(args):
 
     # The logits vector lives in symmetric memory when there are peers, so that the GEMV
     # epilogue can store this rank's slice straight into every rank's copy.
-    peer_ptrs, symm_handle = None, None
+    peer_ptrs, symm_handle, flag_ptrs = None, None, None
     logits = None
-    if world > 1 and args.exchange in ("auto", "peers"):
+    if world > 1 and args.exchange in ("auto", "peers", "fused"):
         try:
             import torch.distributed._symmetric_memory as symm
             logits = symm.empty(ROWS, dtype=torch.float32, device=torch.device("cuda", local_rank))
             symm_handle = symm.rendezvous(logits, dist.group.WORLD)
             peer_ptrs = [int(p) for p in symm_handle.buffer_ptrs]
+            flags = symm.empty(world, dtype=torch.int32, device=torch.device("cuda", local_rank))
+            flags.zero_()
+            flag_handle = symm.rendezvous(flags, dist.group.WORLD)
+            flag_ptrs = [int(p) for p in flag_handle.buffer_ptrs]
+            torch.cuda.synchronize()
+            dist.barrier()
         except Exception as error:  # no peer access on this box: fall back to NCCL
-            if args.exchange == "peers":
+            if args.exchange in ("peers", "fused"):
                 raise SystemExit(f"symmetric memory unavailable: {error}")
             peer_ptrs, symm_handle, logits = None, None, None
     if logits is None:
@@ -299,6 +305,13 @@ def run_gpu_arm(args):
         if not stat.is_ok():
             raise RuntimeError(f"peer matvec failed: {stat}")
         symm_handle.barrier(channel=0)
+
+    def step_fused():
+        stat = backend.cuda_q8_matvec_device_f32_allgather(ctx, weights, x.data_ptr(), WIDTH,
+                                                           peer_ptrs, flag_ptrs, rank, first_row,
+                                                           ROWS)
+        if not stat.is_ok():
+            raise RuntimeError(f"all-gather matvec failed: {stat}")
 
     def time_steps(fn, n):
         for _ in range(5):
@@ -323,8 +336,13 @@ def run_gpu_arm(args):
         exchange_ms["allgather"] = time_steps(step_allgather, 200)
         if peer_ptrs is not None:
             exchange_ms["peers"] = time_steps(step_peers, 200)
-            if args.exchange == "peers" or exchange_ms["peers"] < exchange_ms["allgather"]:
-                exchange, step = "peers", step_peers
+            exchange_ms["fused"] = time_steps(step_fused, 200)
+            candidates = {"allgather": step_allgather, "peers": step_peers, "fused": step_fused}
+            if args.exchange in ("peers", "fused"):
+                exchange = args.exchange
+            else:
+                exchange = min(exchange_ms, key=exchange_ms.get)
+            step = candidates[exchange]
 
     def barrier():
         torch.cuda.synchronize()
@@ -515,7 +533,7 @@ def main():
     parser.add_argument("--steps", type=int, default=20000)
     parser.add_argument("--warmup", type=int, default=200)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--exchange", default="auto", choices=["auto", "allgather", "peers"],
+    parser.add_argument("--exchange", default="auto", choices=["auto", "allgather", "peers", "fused"],
                         help="how row shards are reassembled when --gpus > 1")
     parser.add_argument("--rows", type=int, default=ROWS,
                         help="row count of the GEMV (smaller cases are for profiler captures)")

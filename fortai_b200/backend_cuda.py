@@ -593,3 +593,22 @@ def cuda_q8_matvec_device_f32_peers(context, weights, device_activation, activat
     if code != FORTAI_CUDA_OK:
         return _failed(stat, context, "CUDA Q8 peer matvec failed")
     return stat
+
+
+def cuda_q8_matvec_device_f32_allgather(context, weights, device_activation, activation_elements,
+                                        peer_outputs, peer_flags, my_rank, first_row,
+                                        output_elements) -> status_t:
+    """Row shard + all-gather in one kernel (flag words in every rank's memory)."""
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not peer_outputs or
+            len(peer_outputs) != len(peer_flags)):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 all-gather matvec")
+        return stat
+    outs = (c_void_p * len(peer_outputs))(*[c_void_p(p) for p in peer_outputs])
+    flags = (c_void_p * len(peer_flags))(*[c_void_p(p) for p in peer_flags])
+    code = _lib().fortai_cuda_q8_matvec_device_f32_allgather(
+        context.handle, weights.handle, device_activation, activation_elements, outs, flags,
+        len(peer_outputs), int(my_rank), int(first_row), int(output_elements))
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 all-gather matvec failed")
+    return stat

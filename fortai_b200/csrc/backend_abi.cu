@@ -33,6 +33,8 @@ struct fortai_cuda_q8_context {
     uint8_t *scratch_aux = nullptr;          // prefill: planar activation, partial tiles
     size_t scratch_aux_bytes = 0;
     int *position = nullptr;
+    unsigned *cta_counter = nullptr;         // device word used by the fused all-gather tail
+    unsigned allgather_sequence = 0;
     int *status_host = nullptr;              // pinned + mapped: kernels write, host reads
     int *status_device = nullptr;
     cudaGraph_t graph = nullptr;
@@ -373,6 +375,8 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
         return half_block ? launch_direct<ACT, kEpiSiluPair>(c, p)
                           : launch_block<ACT, kEpiSiluPair>(c, p);
     case kEpiPeers:
+        // the fused all-gather tail lives in the pipelined and half-block kernels
+        if (p.sequence != 0) return launch_direct<ACT, kEpiPeers>(c, p);
         if (ring) return launch_ring<ACT, kEpiPeers>(c, p, cfg);
         return half_block ? launch_direct<ACT, kEpiPeers>(c, p) : launch_block<ACT, kEpiPeers>(c, p);
     default:
@@ -436,6 +440,9 @@ int create_context(int device, bool borrow, cudaStream_t stream, fortai_cuda_q8_
         cudaEventCreate(&c->stop) == cudaSuccess;
     ok = ok && cudaMalloc(reinterpret_cast<void **>(&c->position), sizeof(int)) == cudaSuccess &&
         cudaMemsetAsync(c->position, 0, sizeof(int), c->stream) == cudaSuccess;
+    ok = ok && cudaMalloc(reinterpret_cast<void **>(&c->cta_counter), sizeof(unsigned)) ==
+        cudaSuccess && cudaMemsetAsync(c->cta_counter, 0, sizeof(unsigned), c->stream) ==
+        cudaSuccess;
     ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&c->status_host), sizeof(int),
         cudaHostAllocMapped) == cudaSuccess;
     if (ok) {
@@ -632,6 +639,7 @@ extern "C" int fortai_cuda_q8_context_destroy(fortai_cuda_q8_context *context) {
     if (context->graph_exec) cudaGraphExecDestroy(context->graph_exec);
     if (context->graph) cudaGraphDestroy(context->graph);
     cudaFree(context->position);
+    cudaFree(context->cta_counter);
     cudaFree(context->scratch_activation);
     cudaFree(context->scratch_output);
     cudaFree(context->scratch_aux);
@@ -1150,6 +1158,34 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *co
     p.first_row = static_cast<int>(first_row);
     const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "peer-output matvec", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_outputs, void *const *peer_flags,
+    int peer_count, int my_rank, size_t first_row, size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !peer_outputs || !peer_flags ||
+        peer_count <= 0 || peer_count > kMaxPeers || my_rank < 0 || my_rank >= peer_count ||
+        activation_elements != static_cast<size_t>(weights->blocks) * kBlockElems ||
+        first_row + static_cast<size_t>(weights->rows) > output_elements ||
+        output_elements > static_cast<size_t>(INT32_MAX)) return FORTAI_CUDA_INVALID;
+    for (int i = 0; i < peer_count; ++i)
+        if (!peer_outputs[i] || !peer_flags[i]) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    GemvParams p = single_params(context, weights, device_activation, nullptr);
+    for (int i = 0; i < peer_count; ++i) {
+        p.peer_outputs[i] = static_cast<float *>(peer_outputs[i]);
+        p.peer_flags[i] = static_cast<unsigned *>(peer_flags[i]);
+    }
+    p.peers = peer_count;
+    p.first_row = static_cast<int>(first_row);
+    p.my_flags = static_cast<unsigned *>(peer_flags[my_rank]);
+    p.cta_counter = context->cta_counter;
+    p.my_rank = my_rank;
+    if (++context->allgather_sequence == 0) ++context->allgather_sequence;   // 0 means "off"
+    p.sequence = context->allgather_sequence;
+    const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-gather matvec", error);
 }
 
 // ---------------------------------------------------------------------------

@@ -59,7 +59,50 @@ struct GemvParams {
     float *peer_outputs[kMaxPeers];
     int peers;
     int first_row;  // element offset of this shard inside the peers' vectors
+    // fused all-gather (sequence != 0): flag words in every rank's memory
+    unsigned *peer_flags[kMaxPeers];   // peer_flags[p][my_rank] is written with `sequence`
+    unsigned *my_flags;                // this rank's own flag array, one word per peer
+    unsigned *cta_counter;             // device word, zero between launches
+    unsigned sequence;
+    int my_rank;
 };
+
+// Tail of a peer-output GEMV: turns "every rank stored its slice everywhere" into "this
+// launch is complete only when every rank's slice has arrived here", without a second
+// kernel.  Every CTA publishes its stores system-wide and counts itself; the last one
+// raises this rank's flag in every peer's memory and then waits, for at most about one
+// second, until every peer has raised its flag here.  A wait that runs out writes a
+// status word and returns; the kernel never spins without a bound.  All ranks must run
+// on different GPUs (they wait on one another).
+__device__ __forceinline__ void peer_allgather_tail(const GemvParams &p) {
+    if (p.sequence == 0) return;
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    __threadfence_system();
+    const unsigned arrived = atomicAdd(p.cta_counter, 1u);
+    if (arrived != gridDim.x - 1) return;
+    *p.cta_counter = 0;                       // ready for the next launch
+    __threadfence_system();
+    for (int peer = 0; peer < p.peers; ++peer) {
+        unsigned *flag = p.peer_flags[peer] + p.my_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.sequence) : "memory");
+    }
+    const long long start = clock64();
+    const long long limit = 2000000000LL;     // about a second of SM clocks
+    for (int peer = 0; peer < p.peers; ++peer) {
+        const unsigned *flag = p.my_flags + peer;
+        for (;;) {
+            unsigned seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+            // sequence numbers only grow; the signed difference survives wrap-around
+            if (static_cast<int>(seen - p.sequence) >= 0) break;
+            if (clock64() - start > limit) {
+                atomicExch(p.status, kStatusPeerFlagTimeout);
+                return;
+            }
+        }
+    }
+}
 
 // Shared-memory image of the activation: `width` int8 quants, then `blocks`
 // floats holding half(da[b]).
@@ -244,6 +287,7 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
             }
         }
     }
+    if (EPI == kEpiPeers) peer_allgather_tail(p);
 }
 
 // --------------------------------------------------------------------------
@@ -383,6 +427,7 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
             }
         }
     }
+    if (EPI == kEpiPeers) peer_allgather_tail(p);
 }
 
 // --------------------------------------------------------------------------

@@ -145,9 +145,20 @@ class PeerGatherMatvec(RowShardedMatvec):
     vector (peer pointers from symmetric memory), followed by a cross-rank barrier: one
     kernel and one barrier instead of a kernel and an all-gather."""
 
-    def attach(self, peer_output_ptrs: Sequence[int], barrier: Callable[[], None]):
+    def attach(self, peer_output_ptrs: Sequence[int], barrier: Callable[[], None],
+               peer_flag_ptrs: Sequence[int] = None):
         self.peer_ptrs = list(peer_output_ptrs)
         self.barrier = barrier
+        self.flag_ptrs = list(peer_flag_ptrs) if peer_flag_ptrs is not None else None
+
+    def matvec_fused(self, activation: "torch.Tensor"):
+        """Slice + all-gather in ONE kernel: the last CTA of every rank raises a flag in
+        every rank's memory and waits (bounded) for the others' flags."""
+        stat = self.backend.cuda_q8_matvec_device_f32_allgather(
+            self.context, self.weights, activation.data_ptr(), self.width, self.peer_ptrs,
+            self.flag_ptrs, self.rank, self.first, self.rows)
+        if not stat.is_ok():
+            raise RuntimeError(f"fused all-gather matvec failed: {stat}")
 
     def matvec_peers(self, activation: "torch.Tensor"):
         stat = self.backend.cuda_q8_matvec_device_f32_peers(

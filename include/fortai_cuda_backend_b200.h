@@ -265,6 +265,19 @@ int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *context,
     size_t activation_elements, void *const *peer_outputs, int peer_count, size_t first_row,
     size_t output_elements);
 
+/* The same with the all-gather fused into the kernel: peer_flags[p] is rank p's flag array
+ * (peer_count 32-bit words, zero-initialised once, e.g. in symmetric memory).  Each rank's
+ * last CTA raises word [my_rank] in every rank's array with a per-context sequence number
+ * and then waits - for about a second at most - until every word of its own array has
+ * reached that number, so when the launch completes every rank's slice is in this rank's
+ * output vector.  Every rank must make the same sequence of these calls, each on its own
+ * GPU (the kernels wait on one another).  A wait that runs out is reported as
+ * RUNTIME_ERROR by the next synchronizing call.  Enqueue only. */
+int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_outputs, void *const *peer_flags,
+    int peer_count, int my_rank, size_t first_row, size_t output_elements);
+
 /* Has no counterpart in the reference.  Same contract and same result as
  * fortai_cuda_q8_ffn_device, for hosts that must not allocate while they run (all
  * free device memory already belongs to their own pools, or a cudaMalloc/cudaFree

@@ -47,6 +47,25 @@ def test_peer_epilogue_writes_every_output_vector(backend, context, dev, oracle)
     assert not backend.cuda_q8_matvec_device_f32_peers(context, w, dx, width, outs, 60, total).is_ok()
 
 
+def test_fused_allgather_with_a_single_rank(backend, context, dev, oracle):
+    """World size 1: the flag protocol runs against this rank's own flag word."""
+    rows, width = 777, 2560
+    weights = oracle.make_weights(rows, width, seed=5)
+    x = oracle.normal(width, seed=6)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    w = dev.weights(weights, rows, width)
+    dx = dev.to_device(x)
+    out = dev.to_device(np.zeros(rows, np.float32))
+    flags = dev.to_device(np.zeros(1, np.int32))
+    for call in range(3):
+        stat = backend.cuda_q8_matvec_device_f32_allgather(context, w, dx, width, [out], [flags],
+                                                           0, 0, rows)
+        assert stat.is_ok(), stat
+        assert context.synchronize().is_ok()
+        assert dev.int32s(flags, 1)[0] == call + 1
+    assert float(np.abs(dev.floats(out, rows) - expected).max()) <= l2_tolerance(expected)
+
+
 def test_column_shards_sum_to_the_full_ffn(backend, context, dev, oracle):
     from fortai_b200 import sharded
     hidden, inner, world = 1024, 3840, 4
@@ -99,11 +118,26 @@ def _rank_main(rank, world, port, result_path):
         handle = symm.rendezvous(buf, dist.group.WORLD)
         buf.zero_()
         handle.barrier(channel=0)
-        shard.attach([int(p) for p in handle.buffer_ptrs], lambda: handle.barrier(channel=0))
+        flags = symm.empty(world, dtype=torch.int32, device=torch.device("cuda", rank))
+        flags.zero_()
+        flag_handle = symm.rendezvous(flags, dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier()
+        shard.attach([int(p) for p in handle.buffer_ptrs], lambda: handle.barrier(channel=0),
+                     [int(p) for p in flag_handle.buffer_ptrs])
         shard.matvec_peers(x)
         torch.cuda.synchronize()
         if float(np.abs(buf.cpu().numpy() - expected).max()) > 1e-5 * float(np.linalg.norm(expected)):
             failures.append("peer-store path differs from the oracle")
+        for _ in range(3):
+            buf.zero_()
+            handle.barrier(channel=0)
+            shard.matvec_fused(x)
+            torch.cuda.synchronize()
+            if not ctx.synchronize().is_ok():
+                failures.append("fused all-gather reported a device-side timeout")
+            if float(np.abs(buf.cpu().numpy() - expected).max()) > 1e-5 * float(np.linalg.norm(expected)):
+                failures.append("fused all-gather differs from the oracle")
     except Exception as error:  # symmetric memory is optional; say so rather than fail
         failures.append(f"SKIP-PEERS {type(error).__name__}: {error}")
     # FFN: rows of gate/up, columns of down, all-reduce
