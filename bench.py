@@ -520,6 +520,116 @@ def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3):
             "frac_of_4500_TOPS_nominal": ops / (ms * 1e-3) / 1e12 / 4500.0, "ok": ok}
 
 
+def decode_shapes():
+    """BASELINE configs[0], [1] and [4]: (label, rows, width)."""
+    shapes = [("config0 3072x1024", 3072, 1024)]
+    for hidden in (1024, 2048, 2560):
+        inner = int(round(3.8 * hidden / 256.0)) * 256
+        shapes += [(f"H{hidden} qkv", 3 * hidden, hidden), (f"H{hidden} out", hidden, hidden),
+                   (f"H{hidden} gate/up", inner, hidden), (f"H{hidden} down", hidden, inner)]
+    shapes += [("27B gate/up", 17408, 5120), ("27B down", 5120, 17408)]
+    return shapes
+
+
+def run_sweep(args):
+    """Every named batch-1 shape, timed by replaying a CUDA graph of back-to-back launches
+    (small kernels are launch-bound from Python otherwise).  Two numbers per shape: L2-warm
+    (the same matrix every launch) and HBM-cold (rotating over copies that together exceed
+    twice the L2 size), as one JSON line per shape."""
+    import torch
+    from fortai_b200 import backend_cuda as backend
+    stream = torch.cuda.current_stream()
+    l2_bytes = 126 * 1024 * 1024
+    for label, rows, width in decode_shapes():
+        nbytes = rows * (width // 32) * 34
+        copies = max(2, min(64, (2 * l2_bytes + nbytes - 1) // nbytes + 1))
+        result = {"shape": label, "rows": rows, "width": width, "weight_bytes": nbytes,
+                  "copies": int(copies)}
+        for mode in ("l2_warm", "hbm_cold"):
+            ctx = backend.cuda_q8_context_t()
+            if not ctx.create(0, stream=stream.cuda_stream).is_ok():
+                raise SystemExit("context creation failed")
+            n = 1 if mode == "l2_warm" else int(copies)
+            handles = []
+            for c in range(n):
+                host = make_device_weights(torch, backend, ctx, 0, rows, width, seed=10 + c)
+                w = backend.cuda_q8_weights_t()
+                if not w.upload(ctx, host, host.size, rows, width).is_ok():
+                    raise SystemExit("weight upload failed")
+                handles.append(w)
+            x = torch.randn(width, device="cuda", dtype=torch.float32)
+            out = torch.empty(rows, device="cuda", dtype=torch.float32)
+            per_graph = 40
+            for i in range(4):
+                backend.cuda_q8_matvec_device_f32(ctx, handles[i % n], x.data_ptr(), width,
+                                                  out.data_ptr(), rows)
+            torch.cuda.synchronize()
+            assert ctx.capture_begin().is_ok()
+            for i in range(per_graph):
+                backend.cuda_q8_matvec_device_f32(ctx, handles[i % n], x.data_ptr(), width,
+                                                  out.data_ptr(), rows)
+            assert ctx.capture_end().is_ok()
+            for _ in range(3):
+                ctx.graph_launch()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            replays = 25
+            a.record(stream)
+            for _ in range(replays):
+                ctx.graph_launch()
+            b.record(stream)
+            torch.cuda.synchronize()
+            us = a.elapsed_time(b) * 1e3 / (replays * per_graph)
+            result[mode + "_us"] = us
+            result[mode + "_gbs"] = nbytes / us / 1e3
+            for w in handles:
+                w.destroy()
+            ctx.destroy()
+        print(json.dumps(result), flush=True)
+    # fused FFN at the three hidden sizes and the 27B-class layer
+    for hidden, inner in ((1024, 3840), (2048, 7680), (2560, 9728), (5120, 17408)):
+        ctx = backend.cuda_q8_context_t()
+        ctx.create(0, stream=stream.cuda_stream)
+        mats = []
+        for seed, (r, k) in enumerate(((inner, hidden), (inner, hidden), (hidden, inner))):
+            host = make_device_weights(torch, backend, ctx, 0, r, k, seed=30 + seed)
+            w = backend.cuda_q8_weights_t()
+            w.upload(ctx, host, host.size, r, k)
+            mats.append(w)
+        x = torch.randn(hidden, device="cuda", dtype=torch.float32)
+        out = torch.empty(hidden, device="cuda", dtype=torch.float32)
+        for _ in range(3):
+            backend.cuda_q8_ffn_device(ctx, mats[0], mats[1], mats[2], x.data_ptr(), hidden,
+                                       out.data_ptr(), hidden)
+        torch.cuda.synchronize()
+        launches = ctx.launch_count()
+        assert ctx.capture_begin().is_ok()
+        per_graph = 20
+        for _ in range(per_graph):
+            backend.cuda_q8_ffn_device(ctx, mats[0], mats[1], mats[2], x.data_ptr(), hidden,
+                                       out.data_ptr(), hidden)
+        assert ctx.capture_end().is_ok()
+        launches = (ctx.launch_count() - launches) // per_graph
+        for _ in range(3):
+            ctx.graph_launch()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(25):
+            ctx.graph_launch()
+        b.record(stream)
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) * 1e3 / (25 * per_graph)
+        nbytes = 3 * inner * (hidden // 32) * 34
+        print(json.dumps({"shape": f"FFN H{hidden} F{inner}", "weight_bytes": nbytes,
+                          "us": us, "gbs": nbytes / us / 1e3, "launches_per_call": int(launches),
+                          "note": "same matrices every call; L2-warm when they fit"}), flush=True)
+        for w in mats:
+            w.destroy()
+        ctx.destroy()
+    return 0
+
+
 def ctx_cleanup(weights, ctx, dist):
     weights.destroy()
     ctx.destroy()
@@ -540,6 +650,8 @@ def main():
     parser.add_argument("--mmq-only", action="store_true",
                         help="run only the batched prefill product (profiler captures)")
     parser.add_argument("--tokens", type=int, default=MMQ_M, help="token count of the prefill leg")
+    parser.add_argument("--sweep", action="store_true",
+                        help="time every named batch-1 shape and the fused FFN (one JSON line each)")
     parser.add_argument("--kernel-only", action="store_true",
                         help="skip the e2e, prefill and CPU legs (profiler captures)")
     args = parser.parse_args()
@@ -548,6 +660,8 @@ def main():
         return run_reference_arm(args)
     if args.mmq_only:
         return run_mmq_only(args)
+    if args.sweep:
+        return run_sweep(args)
     return run_gpu_arm(args)
 
 

@@ -231,6 +231,18 @@ cudaError_t launch_pipelined_depth(fortai_cuda_q8_context *c, const GemvParams &
     const int needed = (p.total_rows + kGemvWarps - 1) / kGemvWarps;
     const int grid = c->gemv_balance ? balanced_grid(p.total_rows, kGemvWarps, limit)
                                      : std::max(1, std::min(needed, limit));
+    if (EPI == kEpiPeers) {
+        // room for one CTA's block of results, stored to the peers as whole lines
+        const size_t staged = static_cast<size_t>((p.total_rows + grid - 1) / grid) * sizeof(float);
+        if (smem + staged > 48 * 1024) {
+            error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                static_cast<int>(smem + staged));
+            if (error != cudaSuccess) return error;
+        }
+        kernel<<<grid, kGemvThreads, smem + staged, c->stream>>>(p);
+        ++c->launches;
+        return cudaGetLastError();
+    }
     kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
     ++c->launches;
     return cudaGetLastError();

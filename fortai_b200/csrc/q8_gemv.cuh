@@ -359,25 +359,41 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
     constexpr int ROWS = EPI == kEpiSiluPair ? 2 : 1;
     const int lane = threadIdx.x & 31;
     const int warp_in_cta = threadIdx.x >> 5;
-    const int warp = blockIdx.x * kGemvWarps + warp_in_cta;
-    const int warps = gridDim.x * kGemvWarps;
     const size_t stride = static_cast<size_t>(p.row_stride);
-    const size_t step = stride * warps;
     uint8_t *slots = gemv_smem + activation_smem_bytes(p.width, p.blocks) +
         warp_in_cta * ROWS * (2 * CPL * 16);
 
-    int row = warp;
+    // Row assignment.  Ordinary outputs: grid-stride over warps (warp g takes rows g,
+    // g + W, ...).  Peer outputs: each CTA takes one contiguous block of rows, collects
+    // its results in shared memory and stores them to every peer as whole 128-byte lines
+    // at the end - one NVLink packet per 32 rows instead of one per row.
+    int row, row_step, row_end, cta_first = 0;
+    if (EPI == kEpiPeers) {
+        const int per_cta = (p.total_rows + gridDim.x - 1) / gridDim.x;
+        cta_first = blockIdx.x * per_cta;
+        row = cta_first + warp_in_cta;
+        row_step = kGemvWarps;
+        row_end = min(p.total_rows, cta_first + per_cta);
+    } else {
+        row = blockIdx.x * kGemvWarps + warp_in_cta;
+        row_step = gridDim.x * kGemvWarps;
+        row_end = p.total_rows;
+    }
+    const size_t step = stride * row_step;
+    float *staged = reinterpret_cast<float *>(gemv_smem +
+        pipelined_smem_bytes(p.width, p.blocks, CPL, ROWS));
+
     const uint8_t *base[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) base[r] = p.weights[r] + row * stride;
     RowRegs<CPL> cur[ROWS], next[DEPTH == 2 ? ROWS : 1];
     // the first row(s) are requested before the activation is staged, so the
     // quantize prologue runs under a full memory pipeline
-    if (row < p.total_rows) {
+    if (row < row_end) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) row_issue<CPL>(cur[r], base[r], lane, p.width);
     }
-    if (DEPTH == 2 && row + warps < p.total_rows) {
+    if (DEPTH == 2 && row + row_step < row_end) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) row_issue<CPL>(next[r], base[r] + step, lane, p.width);
     }
@@ -387,19 +403,19 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
     const int4 *act_lane = reinterpret_cast<const int4 *>(gemv_smem) + lane;
     const float *scale_lane = reinterpret_cast<const float *>(gemv_smem + p.width) + (lane >> 1);
 
-    while (row < p.total_rows) {
+    while (row < row_end) {
         float partial[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
             partial[r] = row_consume<CPL>(cur[r], act_lane, scale_lane,
                 slots + r * (2 * CPL * 16), lane);
         const int finished = row;
-        row += warps;
+        row += row_step;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) base[r] += step;
         if (DEPTH == 1) {
             // registers of `cur` are free again: request the next row before reducing
-            if (row < p.total_rows) {
+            if (row < row_end) {
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) row_issue<CPL>(cur[r], base[r], lane, p.width);
             }
@@ -411,8 +427,7 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
             if (EPI == kEpiSiluPair) {
                 p.outputs[0][finished] = silu_mul(total[0], total[ROWS - 1]);
             } else if (EPI == kEpiPeers) {
-                for (int peer = 0; peer < p.peers; ++peer)
-                    p.peer_outputs[peer][p.first_row + finished] = total[0];
+                staged[finished - cta_first] = total[0];
             } else {
                 p.outputs[0][finished] = total[0];
             }
@@ -420,11 +435,19 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         if (DEPTH == 2) {
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) cur[r] = next[r];
-            if (row + warps < p.total_rows) {
+            if (row + row_step < row_end) {
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r)
                     row_issue<CPL>(next[r], base[r] + step, lane, p.width);
             }
+        }
+    }
+    if (EPI == kEpiPeers) {
+        __syncthreads();
+        const int count = row_end - cta_first;
+        for (int peer = 0; peer < p.peers; ++peer) {
+            float *dst = p.peer_outputs[peer] + p.first_row + cta_first;
+            for (int i = threadIdx.x; i < count; i += kGemvThreads) dst[i] = staged[i];
         }
     }
     if (EPI == kEpiPeers) peer_allgather_tail(p);
