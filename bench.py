@@ -520,6 +520,14 @@ def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3):
             "frac_of_4500_TOPS_nominal": ops / (ms * 1e-3) / 1e12 / 4500.0, "ok": ok}
 
 
+def apply_options(ctx, spec):
+    """--options name=value,name=value: tuning knobs of fortai_cuda_q8_context_set_option."""
+    for item in filter(None, (spec or "").split(",")):
+        name, value = item.split("=")
+        if not ctx.set_option(name.strip(), int(value)).is_ok():
+            raise SystemExit(f"unknown backend option {name}")
+
+
 def decode_shapes():
     """BASELINE configs[0], [1] and [4]: (label, rows, width)."""
     shapes = [("config0 3072x1024", 3072, 1024)]
@@ -538,17 +546,21 @@ def run_sweep(args):
     twice the L2 size), as one JSON line per shape."""
     import torch
     from fortai_b200 import backend_cuda as backend
-    stream = torch.cuda.current_stream()
+    # graphs cannot be captured on the legacy default stream: each context owns its stream
     l2_bytes = 126 * 1024 * 1024
     for label, rows, width in decode_shapes():
+        if args.only and args.only not in label:
+            continue
         nbytes = rows * (width // 32) * 34
         copies = max(2, min(64, (2 * l2_bytes + nbytes - 1) // nbytes + 1))
         result = {"shape": label, "rows": rows, "width": width, "weight_bytes": nbytes,
                   "copies": int(copies)}
         for mode in ("l2_warm", "hbm_cold"):
             ctx = backend.cuda_q8_context_t()
-            if not ctx.create(0, stream=stream.cuda_stream).is_ok():
+            if not ctx.create(0).is_ok():
                 raise SystemExit("context creation failed")
+            apply_options(ctx, args.options)
+            stream = torch.cuda.ExternalStream(ctx.stream())
             n = 1 if mode == "l2_warm" else int(copies)
             handles = []
             for c in range(n):
@@ -559,6 +571,7 @@ def run_sweep(args):
                 handles.append(w)
             x = torch.randn(width, device="cuda", dtype=torch.float32)
             out = torch.empty(rows, device="cuda", dtype=torch.float32)
+            torch.cuda.synchronize()
             per_graph = 40
             for i in range(4):
                 backend.cuda_q8_matvec_device_f32(ctx, handles[i % n], x.data_ptr(), width,
@@ -588,8 +601,12 @@ def run_sweep(args):
         print(json.dumps(result), flush=True)
     # fused FFN at the three hidden sizes and the 27B-class layer
     for hidden, inner in ((1024, 3840), (2048, 7680), (2560, 9728), (5120, 17408)):
+        if args.only and args.only not in "FFN":
+            continue
         ctx = backend.cuda_q8_context_t()
-        ctx.create(0, stream=stream.cuda_stream)
+        ctx.create(0)
+        apply_options(ctx, args.options)
+        stream = torch.cuda.ExternalStream(ctx.stream())
         mats = []
         for seed, (r, k) in enumerate(((inner, hidden), (inner, hidden), (hidden, inner))):
             host = make_device_weights(torch, backend, ctx, 0, r, k, seed=30 + seed)
@@ -598,6 +615,7 @@ def run_sweep(args):
             mats.append(w)
         x = torch.randn(hidden, device="cuda", dtype=torch.float32)
         out = torch.empty(hidden, device="cuda", dtype=torch.float32)
+        torch.cuda.synchronize()
         for _ in range(3):
             backend.cuda_q8_ffn_device(ctx, mats[0], mats[1], mats[2], x.data_ptr(), hidden,
                                        out.data_ptr(), hidden)
@@ -650,6 +668,9 @@ def main():
     parser.add_argument("--mmq-only", action="store_true",
                         help="run only the batched prefill product (profiler captures)")
     parser.add_argument("--tokens", type=int, default=MMQ_M, help="token count of the prefill leg")
+    parser.add_argument("--options", default="",
+                        help="backend tuning knobs, name=value[,name=value...]")
+    parser.add_argument("--only", default="", help="--sweep: only shapes whose label contains this")
     parser.add_argument("--sweep", action="store_true",
                         help="time every named batch-1 shape and the fused FFN (one JSON line each)")
     parser.add_argument("--kernel-only", action="store_true",

@@ -32,6 +32,9 @@ struct fortai_cuda_q8_context {
     size_t scratch_output_bytes = 0;
     uint8_t *scratch_aux = nullptr;          // prefill: planar activation, partial tiles
     size_t scratch_aux_bytes = 0;
+    uint8_t *scratch_planar = nullptr;       // batch 1: prepared activation image (long vectors)
+    size_t scratch_planar_bytes = 0;
+    int planar_min_width = 6144;             // vectors at least this long are prepared once
     int *position = nullptr;
     unsigned *cta_counter = nullptr;         // device word used by the fused all-gather tail
     unsigned allgather_sequence = 0;
@@ -45,6 +48,7 @@ struct fortai_cuda_q8_context {
     int gemv_ctas_per_sm = 0;  // 0 = occupancy-derived
     int gemv_rows_per_warp = 0;
     int gemv_depth = 1;        // rows in flight per warp in the pipelined kernel (1 or 2)
+    int gemv_split = 1;        // warps per row in the split-row kernel: 1 off (default: it never won), 0 auto, 2/4/8
     int gemv_balance = 0;      // 1 = trim the grid so that the last round of rows is full
     int ring_stages = 0;
     int ring_rows = 0;
@@ -256,6 +260,52 @@ cudaError_t launch_pipelined_instance(fortai_cuda_q8_context *c, const GemvParam
     return launch_pipelined_depth<CPL, ACT, EPI, 1>(c, p);
 }
 
+template <int SPLIT, int ACT, int EPI>
+cudaError_t launch_splitrow_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
+    auto kernel = q8_gemv_splitrow_kernel<SPLIT, ACT, EPI>;
+    const size_t smem = activation_smem_bytes(p.width, p.blocks);
+    cudaError_t error = cudaSuccess;
+    if (smem > 48 * 1024) {
+        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            static_cast<int>(smem));
+        if (error != cudaSuccess) return error;
+    }
+    int per_sm = c->gemv_ctas_per_sm;
+    if (per_sm <= 0) {
+        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem);
+        if (error != cudaSuccess) return error;
+        if (per_sm < 1) per_sm = 1;
+    }
+    const int rows_per_cta = kGemvWarps / SPLIT;
+    const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
+    const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
+    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+// Rows are split across warps when a warp-per-row grid would have fewer than about two
+// rows per resident warp and the rows are long enough for every slice to stay busy.
+template <int ACT, int EPI>
+bool launch_splitrow(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *error) {
+    if (p.segments != 1 || c->gemv_split == 1) return false;
+    const long long resident_warps = static_cast<long long>(c->sm_count) * 4 * kGemvWarps;
+    int split = c->gemv_split;
+    if (split == 0) {
+        if (p.total_rows * 2 > resident_warps * 3 || p.blocks < 128) return false;
+        split = 2;
+        while (split < 8 && static_cast<long long>(p.total_rows) * split < resident_warps &&
+               p.blocks / (split * 2) >= 64)
+            split *= 2;
+    }
+    switch (split) {
+    case 2: *error = launch_splitrow_instance<2, ACT, EPI>(c, p); return true;
+    case 4: *error = launch_splitrow_instance<4, ACT, EPI>(c, p); return true;
+    case 8: *error = launch_splitrow_instance<8, ACT, EPI>(c, p); return true;
+    default: return false;
+    }
+}
+
 // The pipelined kernel needs width == 512 * CPL exactly and a single matrix (or the
 // gate/up pair).  Returns false when the shape is not covered.
 template <int ACT, int EPI>
@@ -370,6 +420,12 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
     const bool ring = want_ring(c, p, epi) && ring_plan(c, p, epi, &cfg);
     // automatic: the pipelined kernel where the shape allows, else the half-block kernel
     const bool half_block = c->gemv_variant <= 1 || c->gemv_variant == 4;
+    if (c->gemv_variant == 0 && (epi == kEpiPlain || epi == kEpiPeers)) {
+        cudaError_t error = cudaSuccess;
+        const bool done = epi == kEpiPlain ? launch_splitrow<ACT, kEpiPlain>(c, p, &error)
+                                           : launch_splitrow<ACT, kEpiPeers>(c, p, &error);
+        if (done) return error;
+    }
     if (c->gemv_variant == 0 || c->gemv_variant == 4) {
         cudaError_t error = cudaSuccess;
         bool done = false;
@@ -397,13 +453,46 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
     }
 }
 
-cudaError_t launch_gemv(fortai_cuda_q8_context *c, const GemvParams &p, int act, int epi) {
-    // fp32 activations are read with 16-byte loads, Q8_0 ones with 2-byte loads
+// Launch with the activation exactly as given (no preparation pass, no allocation).
+cudaError_t launch_gemv_raw(fortai_cuda_q8_context *c, const GemvParams &p, int act, int epi) {
+    // fp32 and prepared activations are read with 16-byte loads, Q8_0 ones with 2-byte loads
     const uintptr_t address = reinterpret_cast<uintptr_t>(p.activation);
-    if ((act == kActF32 && (address & 15)) || (act == kActQ8 && (address & 1)))
+    if ((act != kActQ8 && (address & 15)) || (act == kActQ8 && (address & 1)))
         return cudaErrorMisalignedAddress;
-    return act == kActF32 ? launch_gemv_act<kActF32>(c, p, epi)
-                          : launch_gemv_act<kActQ8>(c, p, epi);
+    if (act == kActF32) return launch_gemv_act<kActF32>(c, p, epi);
+    if (act == kActPlanar) return launch_gemv_act<kActPlanar>(c, p, epi);
+    return launch_gemv_act<kActQ8>(c, p, epi);
+}
+
+cudaError_t launch_planar_prepare(fortai_cuda_q8_context *c, const void *activation, int act,
+    int width, int blocks, uint8_t *image) {
+    const int grid = std::max(1, std::min((blocks + 7) / 8, c->sm_count * 4));
+    if (act == kActF32)
+        q8_planar_prepare_kernel<kActF32><<<grid, 256, 0, c->stream>>>(activation, width, blocks,
+            image);
+    else
+        q8_planar_prepare_kernel<kActQ8><<<grid, 256, 0, c->stream>>>(activation, width, blocks,
+            image);
+    ++c->launches;
+    return cudaGetLastError();
+}
+
+// Long activation vectors are quantized / unpacked once into the context's prepared image
+// instead of in every CTA's prologue (K = 17408 is 68 KB of fp32 per CTA otherwise).
+cudaError_t launch_gemv(fortai_cuda_q8_context *c, const GemvParams &p, int act, int epi) {
+    if (act == kActPlanar || epi == kEpiBlockDots || p.width < c->planar_min_width)
+        return launch_gemv_raw(c, p, act, epi);
+    const uintptr_t address = reinterpret_cast<uintptr_t>(p.activation);
+    if ((act == kActF32 && (address & 3)) || (act == kActQ8 && (address & 1)))
+        return cudaErrorMisalignedAddress;
+    cudaError_t error = grow(reinterpret_cast<void **>(&c->scratch_planar),
+        &c->scratch_planar_bytes, activation_smem_bytes(p.width, p.blocks));
+    if (error == cudaSuccess)
+        error = launch_planar_prepare(c, p.activation, act, p.width, p.blocks, c->scratch_planar);
+    if (error != cudaSuccess) return error;
+    GemvParams prepared = p;
+    prepared.activation = c->scratch_planar;
+    return launch_gemv_raw(c, prepared, kActPlanar, epi);
 }
 
 GemvParams single_params(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
@@ -611,10 +700,30 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
     p.weights[1] = up->data;
     p.rows[1] = up->rows;
     p.segments = 2;
-    cudaError_t error = launch_gemv(c, p, act, kEpiSiluPair);
-    if (error == cudaSuccess)
-        error = launch_quantize(c, c->scratch_output, c->scratch_activation,
-            static_cast<size_t>(down->blocks));
+    // size the prepared-image scratch for both halves before anything is enqueued, so that
+    // it is never reallocated between the two GEMVs
+    const int widest = std::max(gate->width, down->width);
+    cudaError_t error = cudaSuccess;
+    if (widest >= c->planar_min_width)
+        error = grow(reinterpret_cast<void **>(&c->scratch_planar), &c->scratch_planar_bytes,
+            activation_smem_bytes(widest, widest / kBlockElems));
+    if (error == cudaSuccess) error = launch_gemv(c, p, act, kEpiSiluPair);
+    if (error != cudaSuccess) return error;
+    if (down->width >= c->planar_min_width) {
+        // long hidden vector: quantize it once, straight into the prepared image
+        error = grow(reinterpret_cast<void **>(&c->scratch_planar), &c->scratch_planar_bytes,
+            activation_smem_bytes(down->width, down->blocks));
+        if (error == cudaSuccess)
+            error = launch_planar_prepare(c, c->scratch_output, kActF32, down->width,
+                down->blocks, c->scratch_planar);
+        if (error == cudaSuccess) {
+            GemvParams d = single_params(c, down, c->scratch_planar, output);
+            error = launch_gemv_raw(c, d, kActPlanar, kEpiPlain);
+        }
+        return error;
+    }
+    error = launch_quantize(c, c->scratch_output, c->scratch_activation,
+        static_cast<size_t>(down->blocks));
     if (error == cudaSuccess) {
         GemvParams d = single_params(c, down, c->scratch_activation, output);
         error = launch_gemv(c, d, kActQ8, kEpiPlain);
@@ -655,6 +764,7 @@ extern "C" int fortai_cuda_q8_context_destroy(fortai_cuda_q8_context *context) {
     cudaFree(context->scratch_activation);
     cudaFree(context->scratch_output);
     cudaFree(context->scratch_aux);
+    cudaFree(context->scratch_planar);
     if (context->status_host) cudaFreeHost(context->status_host);
     if (context->start) cudaEventDestroy(context->start);
     if (context->stop) cudaEventDestroy(context->stop);
@@ -1087,6 +1197,9 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
     else if (!std::strcmp(name, "gemv_rows_per_warp") && value <= 2)
         context->gemv_rows_per_warp = value;
     else if (!std::strcmp(name, "gemv_balance") && value <= 1) context->gemv_balance = value;
+    else if (!std::strcmp(name, "planar_min_width")) context->planar_min_width = value;
+    else if (!std::strcmp(name, "gemv_split") && (value <= 2 || value == 4 || value == 8))
+        context->gemv_split = value;
     else if (!std::strcmp(name, "gemv_depth") && value >= 1 && value <= 2)
         context->gemv_depth = value;
     else if (!std::strcmp(name, "ring_stages") && value <= kRingMaxStages)
@@ -1363,8 +1476,9 @@ namespace {
 
 constexpr int kStaticFfnMaxInner = 32768;   // largest supported FFN inner size (gate/up rows)
 constexpr size_t kStaticFfnHiddenBytes = static_cast<size_t>(kStaticFfnMaxInner) * sizeof(float);
+// the prepared Q8_0 image of the hidden vector: int8 quants + one float scale per block
 constexpr size_t kStaticFfnQ8Bytes =
-    (static_cast<size_t>(kStaticFfnMaxInner) / kBlockElems * kBlockBytes + 255) / 256 * 256;
+    (static_cast<size_t>(kStaticFfnMaxInner) + kStaticFfnMaxInner / kBlockElems * 4 + 255) / 256 * 256;
 constexpr size_t kStaticFfnBytes = kStaticFfnHiddenBytes + kStaticFfnQ8Bytes;
 
 static __device__ __align__(256) unsigned char g_static_ffn_scratch[kStaticFfnBytes];
@@ -1416,14 +1530,14 @@ extern "C" int fortai_cuda_q8_ffn_device_noalloc(fortai_cuda_q8_context *context
     p.weights[1] = up_weights->data;
     p.rows[1] = up_weights->rows;
     p.segments = 2;
-    error = launch_gemv(context, p, kActF32, kEpiSiluPair);
+    error = launch_gemv_raw(context, p, kActF32, kEpiSiluPair);
     if (error == cudaSuccess)
-        error = launch_quantize(context, hidden, hidden_q8,
-            static_cast<size_t>(down_weights->blocks));
+        error = launch_planar_prepare(context, hidden, kActF32, down_weights->width,
+            down_weights->blocks, hidden_q8);
     if (error == cudaSuccess) {
         const GemvParams d = single_params(context, down_weights, hidden_q8,
             static_cast<float *>(device_output));
-        error = launch_gemv(context, d, kActQ8, kEpiPlain);
+        error = launch_gemv_raw(context, d, kActPlanar, kEpiPlain);
     }
     return error == cudaSuccess ? FORTAI_CUDA_OK
                                 : fail(context, "allocation-free Qwen FFN device", error);

@@ -41,8 +41,9 @@ enum GemvEpilogue : int {
 };
 
 enum ActivationKind : int {
-    kActQ8 = 0,   // width/32 blocks of 34 bytes (GGUF Q8_0)
-    kActF32 = 1   // width floats, quantized in the prologue
+    kActQ8 = 0,      // width/32 blocks of 34 bytes (GGUF Q8_0)
+    kActF32 = 1,     // width floats, quantized in the prologue
+    kActPlanar = 2   // the shared-memory image itself, prepared once in global memory
 };
 
 struct GemvParams {
@@ -115,7 +116,14 @@ __device__ __forceinline__ void stage_activation(const void *activation, int wid
     uint8_t *smem, int tid, int threads) {
     int8_t *act_q = reinterpret_cast<int8_t *>(smem);
     float *act_s = reinterpret_cast<float *>(smem + width);
-    if (ACT == kActQ8) {
+    if (ACT == kActPlanar) {
+        // long vectors are quantized once by q8_planar_prepare_kernel; every CTA only
+        // copies the finished image (16-byte loads) instead of redoing the work
+        const int4 *src = static_cast<const int4 *>(activation);
+        int4 *dst = reinterpret_cast<int4 *>(smem);
+        const int count = static_cast<int>(activation_smem_bytes(width, blocks) >> 4);
+        for (int i = tid; i < count; i += threads) dst[i] = src[i];
+    } else if (ACT == kActQ8) {
         // 17 two-byte words per block: word 0 is the scale, words 1..16 the quants.
         const uint16_t *raw = static_cast<const uint16_t *>(activation);
         uint16_t *act_q16 = reinterpret_cast<uint16_t *>(act_q);
@@ -286,6 +294,82 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
                 }
             }
         }
+    }
+    if (EPI == kEpiPeers) peer_allgather_tail(p);
+}
+
+// --------------------------------------------------------------------------
+// split-row variant: few rows, long rows (FFN down projections)
+// --------------------------------------------------------------------------
+// With fewer rows than resident warps (5120 rows of 18.5 KB on 4736 warps) a
+// warp-per-row grid leaves most of the machine idle in its last round.  Here SPLIT
+// adjacent warps of a CTA share a row: each takes a contiguous K-slice (a whole
+// number of blocks), and the SPLIT partial sums meet in shared memory.  Same lane
+// mapping and arithmetic as the half-block kernel; only the fp32 summation order
+// differs.
+template <int SPLIT, int ACT, int EPI>
+__global__ void __launch_bounds__(kGemvThreads)
+q8_gemv_splitrow_kernel(const __grid_constant__ GemvParams p) {
+    extern __shared__ __align__(16) uint8_t gemv_smem[];
+    __shared__ float partial[kGemvWarps];
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
+    __syncthreads();
+    const int4 *act_q = reinterpret_cast<const int4 *>(gemv_smem);
+    const float *act_s = reinterpret_cast<const float *>(gemv_smem + p.width);
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    constexpr int ROWS_PER_ROUND = kGemvWarps / SPLIT;
+    constexpr int U = 8;
+    const int slice = warp % SPLIT;
+    const int blocks_per_slice = (p.blocks + SPLIT - 1) / SPLIT;
+    const int chunk_begin = min(p.blocks, slice * blocks_per_slice) * 2;
+    const int chunk_end = min(p.blocks, (slice + 1) * blocks_per_slice) * 2;
+    const size_t stride = static_cast<size_t>(p.row_stride);
+
+    for (int first = blockIdx.x * ROWS_PER_ROUND; first < p.total_rows;
+         first += gridDim.x * ROWS_PER_ROUND) {
+        const int row = first + warp / SPLIT;
+        const bool row_ok = row < p.total_rows;
+        const uint8_t *base = p.weights[0] + static_cast<size_t>(row_ok ? row : first) * stride;
+        float acc = 0.0f;
+        for (int c0 = chunk_begin; c0 < chunk_end; c0 += 32 * U) {
+            int4 w[U];
+            uint16_t d[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = c0 + u * 32 + lane;
+                if (idx < chunk_end) {
+                    w[u] = ldg_stream_16(base + static_cast<size_t>(idx) * 16);
+                    d[u] = ldg_stream_u16(base + p.width + (idx >> 1) * 2);
+                } else {
+                    w[u] = make_int4(0, 0, 0, 0);
+                    d[u] = 0;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int idx = c0 + u * 32 + lane;
+                const bool ok = idx < chunk_end;
+                const int4 a = ok ? act_q[idx] : make_int4(0, 0, 0, 0);
+                const float sa = ok ? act_s[idx >> 1] : 0.0f;
+                acc = fmaf(half_bits_to_float(d[u]) * sa, static_cast<float>(dot16(w[u], a)), acc);
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) partial[warp] = acc;
+        __syncthreads();
+        if (lane == 0 && slice == 0 && row_ok) {
+            float total = 0.0f;
+#pragma unroll
+            for (int k = 0; k < SPLIT; ++k) total += partial[warp + k];
+            if (EPI == kEpiPeers) {
+                for (int peer = 0; peer < p.peers; ++peer)
+                    p.peer_outputs[peer][p.first_row + row] = total;
+            } else {
+                p.outputs[0][row] = total;
+            }
+        }
+        __syncthreads();
     }
     if (EPI == kEpiPeers) peer_allgather_tail(p);
 }
@@ -817,6 +901,35 @@ q8_quantize_kernel(const float *__restrict__ input, uint8_t *__restrict__ output
         uint8_t *dst = output + b * kBlockBytes;
         dst[2 + lane] = static_cast<uint8_t>(q);
         if (lane == 0) *reinterpret_cast<uint16_t *>(dst) = bits;
+    }
+}
+
+// --------------------------------------------------------------------------
+// activation image prepared once in global memory (long vectors)
+// --------------------------------------------------------------------------
+// One warp per block: fp32 -> (quants, scale) or GGUF Q8_0 block -> (quants, scale),
+// written in the layout the GEMV kernels keep in shared memory.
+template <int ACT>
+__global__ void __launch_bounds__(256)
+q8_planar_prepare_kernel(const void *__restrict__ activation, int width, int blocks,
+    uint8_t *__restrict__ image) {
+    int8_t *act_q = reinterpret_cast<int8_t *>(image);
+    float *act_s = reinterpret_cast<float *>(image + width);
+    const int lane = threadIdx.x & 31;
+    for (int b = blockIdx.x * 8 + (threadIdx.x >> 5); b < blocks; b += gridDim.x * 8) {
+        if (ACT == kActF32) {
+            uint16_t bits;
+            const int q = quantize_lane(
+                static_cast<const float *>(activation)[b * kBlockElems + lane], &bits);
+            act_q[b * kBlockElems + lane] = static_cast<int8_t>(q);
+            if (lane == 0) act_s[b] = half_bits_to_float(bits);
+        } else {
+            const uint8_t *block = static_cast<const uint8_t *>(activation) +
+                static_cast<size_t>(b) * kBlockBytes;
+            act_q[b * kBlockElems + lane] = static_cast<int8_t>(block[2 + lane]);
+            if (lane == 0)
+                act_s[b] = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
+        }
     }
 }
 
