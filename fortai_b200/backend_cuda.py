@@ -612,3 +612,131 @@ def cuda_q8_matvec_device_f32_allgather(context, weights, device_activation, act
     if code != FORTAI_CUDA_OK:
         return _failed(stat, context, "CUDA Q8 all-gather matvec failed")
     return stat
+
+
+# --------------------------------------------------------------------------- layer objects
+class cuda_qwen35_recurrent_t:
+    """fortai_backend_cuda.f90:35-43 (gated-delta-net layer; state lives on the device)."""
+
+    def __init__(self):
+        self.handle = 0
+        self.context = None
+
+    def create(self, context, qkv, gate, alpha, beta, output, conv_weights, conv_size,
+               conv_kernel, ssm_a, ssm_dt, ssm_norm, state_size, key_heads, value_heads,
+               head_size, inner_size, norm_epsilon) -> status_t:
+        stat = status_t()
+        handles = (qkv, gate, alpha, beta, output)
+        if not context.handle or any(not w.handle for w in handles):
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen recurrent layer")
+            return stat
+        arrays = [np.ascontiguousarray(a, dtype=np.float32)
+                  for a in (conv_weights, ssm_a, ssm_dt, ssm_norm)]
+        out = c_void_p()
+        code = _lib().fortai_cuda_qwen35_recurrent_create(
+            context.handle, qkv.handle, gate.handle, alpha.handle, beta.handle, output.handle,
+            _host_ptr(arrays[0]), arrays[0].nbytes, int(conv_size), int(conv_kernel),
+            _host_ptr(arrays[1]), arrays[1].nbytes, _host_ptr(arrays[2]), arrays[2].nbytes,
+            _host_ptr(arrays[3]), arrays[3].nbytes, int(state_size), int(key_heads),
+            int(value_heads), int(head_size), int(inner_size), c_float(norm_epsilon), byref(out))
+        if code != FORTAI_CUDA_OK:
+            return _failed(stat, context, "CUDA Qwen recurrent layer creation failed")
+        self.handle, self.context = out.value, context
+        return stat
+
+    def destroy(self) -> status_t:
+        stat = status_t()
+        if self.handle:
+            _lib().fortai_cuda_qwen35_recurrent_destroy(self.handle)
+            self.handle = 0
+        return stat
+
+    def reset(self) -> status_t:
+        stat = status_t()
+        if not self.handle:
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen recurrent layer")
+        elif _lib().fortai_cuda_qwen35_recurrent_reset(self.handle) != FORTAI_CUDA_OK:
+            return _failed(stat, self.context, "CUDA Qwen recurrent reset failed")
+        return stat
+
+    def run(self, activation, activation_bytes, output, output_bytes):
+        stat = status_t()
+        act = _as_bytes(activation)
+        if not self.handle or act.size <= 0 or output.size <= 0:
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen recurrent run")
+            return 0.0, stat
+        ms = c_float(0.0)
+        code = _lib().fortai_cuda_qwen35_recurrent_run(self.handle, _host_ptr(act),
+                                                       activation_bytes, _host_ptr(output),
+                                                       output_bytes, byref(ms))
+        if code != FORTAI_CUDA_OK:
+            return 0.0, _failed(stat, self.context, "CUDA Qwen recurrent run failed")
+        return ms.value, stat
+
+    def run_device(self, device_activation, activation_elements, device_output,
+                   output_elements) -> status_t:
+        stat = status_t()
+        if not self.handle or not device_activation or not device_output:
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen recurrent device run")
+            return stat
+        code = _lib().fortai_cuda_qwen35_recurrent_run_device(
+            self.handle, device_activation, activation_elements, device_output, output_elements)
+        if code != FORTAI_CUDA_OK:
+            return _failed(stat, self.context, "CUDA Qwen recurrent device run failed")
+        return stat
+
+
+class cuda_qwen35_attention_t:
+    """fortai_backend_cuda.f90:45-52 (gated attention layer; binary16 KV cache on the device)."""
+
+    def __init__(self):
+        self.handle = 0
+        self.context = None
+
+    def create(self, context, query, key, value, output, query_norm, key_norm, heads,
+               key_value_heads, head_size, value_size, max_context, rope_dimension, rope_base,
+               norm_epsilon) -> status_t:
+        stat = status_t()
+        if not context.handle or any(not w.handle for w in (query, key, value, output)):
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen attention layer")
+            return stat
+        qn = np.ascontiguousarray(query_norm, dtype=np.float32)
+        kn = np.ascontiguousarray(key_norm, dtype=np.float32)
+        out = c_void_p()
+        code = _lib().fortai_cuda_qwen35_attention_create(
+            context.handle, query.handle, key.handle, value.handle, output.handle, _host_ptr(qn),
+            qn.nbytes, _host_ptr(kn), kn.nbytes, int(heads), int(key_value_heads), int(head_size),
+            int(value_size), int(max_context), int(rope_dimension), c_float(rope_base),
+            c_float(norm_epsilon), byref(out))
+        if code != FORTAI_CUDA_OK:
+            return _failed(stat, context, "CUDA Qwen attention layer creation failed")
+        self.handle, self.context = out.value, context
+        return stat
+
+    def destroy(self) -> status_t:
+        stat = status_t()
+        if self.handle:
+            _lib().fortai_cuda_qwen35_attention_destroy(self.handle)
+            self.handle = 0
+        return stat
+
+    def reset(self) -> status_t:
+        stat = status_t()
+        if not self.handle:
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen attention layer")
+        elif _lib().fortai_cuda_qwen35_attention_reset(self.handle) != FORTAI_CUDA_OK:
+            return _failed(stat, self.context, "CUDA Qwen attention reset failed")
+        return stat
+
+    def run_device(self, device_activation, activation_elements, position, device_output,
+                   output_elements) -> status_t:
+        stat = status_t()
+        if not self.handle or not device_activation or not device_output:
+            stat.set(FORTAI_INVALID, "invalid CUDA Qwen attention device run")
+            return stat
+        code = _lib().fortai_cuda_qwen35_attention_run_device(
+            self.handle, device_activation, activation_elements, int(position), device_output,
+            output_elements)
+        if code != FORTAI_CUDA_OK:
+            return _failed(stat, self.context, "CUDA Qwen attention device run failed")
+        return stat

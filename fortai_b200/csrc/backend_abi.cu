@@ -16,6 +16,7 @@
 #include "q8_common.cuh"
 #include "q8_gemv.cuh"
 #include "q8_mmq.cuh"
+#include "qwen35_layers.cuh"
 
 using namespace fortai_b200;
 
@@ -66,12 +67,31 @@ struct fortai_cuda_q8_weights {
     MmqWeightsPlan mmq;   // tensor maps for the prefill kernel, built lazily
 };
 
+// Layer objects borrow their weight handles (the caller keeps them alive and destroys
+// layers first, as the reference does: src/models/qwen35/fortai_qwen35_cpu.f90:519-530).
 struct fortai_cuda_qwen35_recurrent {
     fortai_cuda_q8_context *context = nullptr;
+    const fortai_cuda_q8_weights *qkv = nullptr, *gate = nullptr, *alpha = nullptr,
+        *beta = nullptr, *out = nullptr;
+    float *conv_weights = nullptr, *ssm_a = nullptr, *ssm_dt = nullptr, *ssm_norm = nullptr;
+    float *conv_state = nullptr, *gdn_state = nullptr;
+    float *projections = nullptr;   // qkv | gate | alpha | beta outputs, back to back
+    float *gdn_output = nullptr;
+    int conv_size = 0, conv_kernel = 0, state_size = 0, key_heads = 0, value_heads = 0,
+        head_size = 0, inner_size = 0;
+    float epsilon = 1.0e-6f;
 };
 
 struct fortai_cuda_qwen35_attention {
     fortai_cuda_q8_context *context = nullptr;
+    const fortai_cuda_q8_weights *q = nullptr, *k = nullptr, *v = nullptr, *out = nullptr;
+    float *q_norm = nullptr, *k_norm = nullptr;
+    __half *key_cache = nullptr, *value_cache = nullptr;
+    float *projections = nullptr;   // query | key | value outputs, back to back
+    float *attention = nullptr;
+    int heads = 0, kv_heads = 0, head_size = 0, value_size = 0, max_context = 0,
+        rope_dimension = 0;
+    float rope_base = 1.0f, epsilon = 1.0e-6f;
 };
 
 namespace {
@@ -731,14 +751,6 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
     return error;
 }
 
-int not_built(fortai_cuda_q8_context *context, const char *what) {
-    // "unsupported backends fail explicitly and never fall back silently"
-    // (reference README.md:38)
-    if (context)
-        std::snprintf(context->error, sizeof(context->error),
-            "%s is not implemented in the B200 Q8_0 backend", what);
-    return FORTAI_CUDA_RUNTIME_ERROR;
-}
 
 }  // namespace
 
@@ -1119,52 +1131,382 @@ extern "C" int fortai_cuda_q8_ffn_device(fortai_cuda_q8_context *context,
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "Qwen FFN device", error);
 }
 
-// --- gated-delta-net and attention layers: outside the Q8_0 matvec path -------
+// ---------------------------------------------------------------------------
+// Qwen3.5 gated-delta-net ("recurrent") layer
+// reference: backend/cuda/fortai_cuda_backend.cu:1298-1567
+// ---------------------------------------------------------------------------
+namespace {
+
+cudaError_t device_copy_of(fortai_cuda_q8_context *c, float **destination, const void *source,
+    size_t bytes) {
+    cudaError_t error = cudaMalloc(reinterpret_cast<void **>(destination), bytes);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(*destination, source, bytes, cudaMemcpyHostToDevice, c->stream);
+    return error;
+}
+
+void free_recurrent(fortai_cuda_qwen35_recurrent *layer) {
+    cudaFree(layer->conv_weights);
+    cudaFree(layer->ssm_a);
+    cudaFree(layer->ssm_dt);
+    cudaFree(layer->ssm_norm);
+    cudaFree(layer->conv_state);
+    cudaFree(layer->gdn_state);
+    cudaFree(layer->projections);
+    cudaFree(layer->gdn_output);
+}
+
+cudaError_t clear_recurrent_state(fortai_cuda_qwen35_recurrent *layer) {
+    fortai_cuda_q8_context *c = layer->context;
+    cudaError_t error = cudaMemsetAsync(layer->conv_state, 0,
+        static_cast<size_t>(layer->conv_kernel - 1) * layer->conv_size * sizeof(float), c->stream);
+    if (error == cudaSuccess)
+        error = cudaMemsetAsync(layer->gdn_state, 0, static_cast<size_t>(layer->value_heads) *
+            layer->head_size * layer->head_size * sizeof(float), c->stream);
+    if (error == cudaSuccess) error = cudaStreamSynchronize(c->stream);
+    return error;
+}
+
+// qkv, gate, alpha and beta share one activation: one fused launch, then the
+// convolution, the normalisations, the state update and the output projection
+// (whose prologue quantizes the fp32 layer output, so no scratch is touched).
+cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *activation,
+    int act, float *output) {
+    fortai_cuda_q8_context *c = layer->context;
+    float *qkv = layer->projections;
+    float *gate = qkv + layer->conv_size;
+    float *alpha = gate + layer->inner_size;
+    float *beta = alpha + layer->value_heads;
+    GemvParams p = single_params(c, layer->qkv, activation, qkv);
+    const fortai_cuda_q8_weights *mats[4] = {layer->qkv, layer->gate, layer->alpha, layer->beta};
+    float *outs[4] = {qkv, gate, alpha, beta};
+    p.total_rows = 0;
+    for (int i = 0; i < 4; ++i) {
+        p.weights[i] = mats[i]->data;
+        p.outputs[i] = outs[i];
+        p.rows[i] = mats[i]->rows;
+        p.total_rows += mats[i]->rows;
+    }
+    p.segments = 4;
+    cudaError_t error = launch_gemv(c, p, act, kEpiPlain);
+    if (error != cudaSuccess) return error;
+    gdn_conv_silu_kernel<<<(layer->conv_size + 255) / 256, 256, 0, c->stream>>>(qkv,
+        layer->conv_weights, layer->conv_state, layer->conv_size, layer->conv_kernel);
+    gdn_l2_normalize_kernel<<<(2 * layer->key_heads + 7) / 8, 256, 0, c->stream>>>(qkv,
+        layer->key_heads, layer->head_size, layer->state_size, layer->epsilon);
+    gdn_step_kernel<<<layer->value_heads, 256, layer->head_size * sizeof(float), c->stream>>>(qkv,
+        gate, alpha, beta, layer->ssm_a, layer->ssm_dt, layer->ssm_norm, layer->gdn_state,
+        layer->gdn_output, layer->state_size, layer->key_heads, layer->value_heads,
+        layer->head_size, layer->epsilon);
+    c->launches += 3;
+    error = cudaGetLastError();
+    if (error != cudaSuccess) return error;
+    const GemvParams o = single_params(c, layer->out, layer->gdn_output, output);
+    return launch_gemv(c, o, kActF32, kEpiPlain);
+}
+
+}  // namespace
+
 extern "C" int fortai_cuda_qwen35_recurrent_create(fortai_cuda_q8_context *context,
-    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *,
-    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *,
-    const fortai_cuda_q8_weights *, const void *, size_t, int, int, const void *, size_t,
-    const void *, size_t, const void *, size_t, int, int, int, int, int, float,
-    fortai_cuda_qwen35_recurrent **layer) {
-    if (layer) *layer = nullptr;
-    if (!context || !layer) return FORTAI_CUDA_INVALID;
-    return not_built(context, "the Qwen3.5 recurrent layer");
+    const fortai_cuda_q8_weights *qkv_weights, const fortai_cuda_q8_weights *gate_weights,
+    const fortai_cuda_q8_weights *alpha_weights, const fortai_cuda_q8_weights *beta_weights,
+    const fortai_cuda_q8_weights *output_weights, const void *conv_weights,
+    size_t conv_weight_bytes, int conv_size, int conv_kernel, const void *ssm_a,
+    size_t ssm_a_bytes, const void *ssm_dt, size_t ssm_dt_bytes, const void *ssm_norm,
+    size_t ssm_norm_bytes, int state_size, int key_heads, int value_heads, int head_size,
+    int inner_size, float norm_epsilon, fortai_cuda_qwen35_recurrent **layer) {
+    if (!context || !layer || !qkv_weights || !gate_weights || !alpha_weights || !beta_weights ||
+        !output_weights || !conv_weights || !ssm_a || !ssm_dt || !ssm_norm || conv_size <= 0 ||
+        conv_kernel < 2 || state_size <= 0 || key_heads <= 0 || value_heads <= 0 ||
+        head_size <= 0 || inner_size <= 0 || value_heads % key_heads != 0 ||
+        value_heads * head_size != inner_size) return FORTAI_CUDA_INVALID;
+    *layer = nullptr;
+    if (!owned(context, qkv_weights) || !owned(context, gate_weights) ||
+        !owned(context, alpha_weights) || !owned(context, beta_weights) ||
+        !owned(context, output_weights)) return FORTAI_CUDA_INVALID;
+    // shapes this layer relies on: all four input projections read the same vector, the
+    // projection outputs are what the later kernels index, and the output projection
+    // consumes the inner vector
+    if (gate_weights->width != qkv_weights->width || alpha_weights->width != qkv_weights->width ||
+        beta_weights->width != qkv_weights->width || qkv_weights->rows != conv_size ||
+        gate_weights->rows != inner_size || alpha_weights->rows != value_heads ||
+        beta_weights->rows != value_heads || output_weights->width != inner_size ||
+        conv_size < 2 * state_size * key_heads + inner_size) return FORTAI_CUDA_INVALID;
+    if (conv_weight_bytes < static_cast<size_t>(conv_size) * conv_kernel * sizeof(float) ||
+        ssm_a_bytes < static_cast<size_t>(value_heads) * sizeof(float) ||
+        ssm_dt_bytes < static_cast<size_t>(value_heads) * sizeof(float) ||
+        ssm_norm_bytes < static_cast<size_t>(head_size) * sizeof(float))
+        return FORTAI_CUDA_INVALID;
+    auto *created = new (std::nothrow) fortai_cuda_qwen35_recurrent;
+    if (!created) return FORTAI_CUDA_RUNTIME_ERROR;
+    created->context = context;
+    created->qkv = qkv_weights;
+    created->gate = gate_weights;
+    created->alpha = alpha_weights;
+    created->beta = beta_weights;
+    created->out = output_weights;
+    created->conv_size = conv_size;
+    created->conv_kernel = conv_kernel;
+    created->state_size = state_size;
+    created->key_heads = key_heads;
+    created->value_heads = value_heads;
+    created->head_size = head_size;
+    created->inner_size = inner_size;
+    created->epsilon = norm_epsilon;
+    cudaSetDevice(context->device);
+    cudaError_t error = device_copy_of(context, &created->conv_weights, conv_weights,
+        static_cast<size_t>(conv_size) * conv_kernel * sizeof(float));
+    if (error == cudaSuccess)
+        error = device_copy_of(context, &created->ssm_a, ssm_a, value_heads * sizeof(float));
+    if (error == cudaSuccess)
+        error = device_copy_of(context, &created->ssm_dt, ssm_dt, value_heads * sizeof(float));
+    if (error == cudaSuccess)
+        error = device_copy_of(context, &created->ssm_norm, ssm_norm, head_size * sizeof(float));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->conv_state),
+            static_cast<size_t>(conv_kernel - 1) * conv_size * sizeof(float));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->gdn_state),
+            static_cast<size_t>(value_heads) * head_size * head_size * sizeof(float));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->projections),
+            (static_cast<size_t>(conv_size) + inner_size + 2 * value_heads) * sizeof(float));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->gdn_output),
+            static_cast<size_t>(inner_size) * sizeof(float));
+    if (error == cudaSuccess) error = clear_recurrent_state(created);
+    if (error != cudaSuccess) {
+        free_recurrent(created);
+        delete created;
+        return fail(context, "Qwen recurrent create", error);
+    }
+    *layer = created;
+    return FORTAI_CUDA_OK;
 }
+
 extern "C" int fortai_cuda_qwen35_recurrent_destroy(fortai_cuda_qwen35_recurrent *layer) {
+    if (!layer) return FORTAI_CUDA_OK;
+    if (layer->context) {
+        cudaSetDevice(layer->context->device);
+        free_recurrent(layer);
+    }
     delete layer;
     return FORTAI_CUDA_OK;
 }
+
 extern "C" int fortai_cuda_qwen35_recurrent_reset(fortai_cuda_qwen35_recurrent *layer) {
-    return layer ? not_built(layer->context, "the Qwen3.5 recurrent layer") : FORTAI_CUDA_INVALID;
+    if (!layer || !layer->context) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(layer->context->device);
+    const cudaError_t error = clear_recurrent_state(layer);
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(layer->context, "Qwen recurrent reset", error);
 }
-extern "C" int fortai_cuda_qwen35_recurrent_run(fortai_cuda_qwen35_recurrent *layer, const void *,
-    size_t, float *, size_t, float *elapsed_ms) {
-    if (elapsed_ms) *elapsed_ms = 0.0f;
-    return layer ? not_built(layer->context, "the Qwen3.5 recurrent layer") : FORTAI_CUDA_INVALID;
+
+extern "C" int fortai_cuda_qwen35_recurrent_run(fortai_cuda_qwen35_recurrent *layer,
+    const void *host_activation, size_t activation_bytes, float *host_output,
+    size_t output_bytes, float *elapsed_ms) {
+    if (!layer || !layer->context || !host_activation || !host_output || !elapsed_ms)
+        return FORTAI_CUDA_INVALID;
+    fortai_cuda_q8_context *c = layer->context;
+    const size_t expected_activation = static_cast<size_t>(layer->qkv->blocks) * kBlockBytes;
+    const size_t expected_output = static_cast<size_t>(layer->out->rows) * sizeof(float);
+    if (activation_bytes < expected_activation || output_bytes < expected_output)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(c->device);
+    cudaError_t error = ensure_scratch(c, expected_activation, expected_output);
+    if (error == cudaSuccess) error = cudaEventRecord(c->start, c->stream);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(c->scratch_activation, host_activation, expected_activation,
+            cudaMemcpyHostToDevice, c->stream);
+    if (error == cudaSuccess)
+        error = enqueue_recurrent(layer, c->scratch_activation, kActQ8, c->scratch_output);
+    if (error == cudaSuccess)
+        error = cudaMemcpyAsync(host_output, c->scratch_output, expected_output,
+            cudaMemcpyDeviceToHost, c->stream);
+    if (error == cudaSuccess) error = cudaEventRecord(c->stop, c->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(c->stop);
+    if (error == cudaSuccess) error = cudaEventElapsedTime(elapsed_ms, c->start, c->stop);
+    return finish(c, "Qwen recurrent run", error);
 }
+
 extern "C" int fortai_cuda_qwen35_recurrent_run_device(fortai_cuda_qwen35_recurrent *layer,
-    const void *, size_t, void *, size_t) {
-    return layer ? not_built(layer->context, "the Qwen3.5 recurrent layer") : FORTAI_CUDA_INVALID;
+    const void *device_activation, size_t activation_elements, void *device_output,
+    size_t output_elements) {
+    if (!layer || !layer->context || !device_activation || !device_output)
+        return FORTAI_CUDA_INVALID;
+    if (activation_elements != static_cast<size_t>(layer->qkv->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(layer->out->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(layer->context->device);
+    const cudaError_t error = enqueue_recurrent(layer, device_activation, kActF32,
+        static_cast<float *>(device_output));
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(layer->context, "Qwen recurrent device run", error);
 }
+
+// ---------------------------------------------------------------------------
+// Qwen3.5 gated attention layer
+// reference: backend/cuda/fortai_cuda_backend.cu:1569-1731
+// ---------------------------------------------------------------------------
+namespace {
+
+void free_attention(fortai_cuda_qwen35_attention *layer) {
+    cudaFree(layer->q_norm);
+    cudaFree(layer->k_norm);
+    cudaFree(layer->key_cache);
+    cudaFree(layer->value_cache);
+    cudaFree(layer->projections);
+    cudaFree(layer->attention);
+}
+
+cudaError_t clear_attention_state(fortai_cuda_qwen35_attention *layer) {
+    fortai_cuda_q8_context *c = layer->context;
+    cudaError_t error = cudaMemsetAsync(layer->key_cache, 0, static_cast<size_t>(layer->max_context) *
+        layer->kv_heads * layer->head_size * sizeof(__half), c->stream);
+    if (error == cudaSuccess)
+        error = cudaMemsetAsync(layer->value_cache, 0, static_cast<size_t>(layer->max_context) *
+            layer->kv_heads * layer->value_size * sizeof(__half), c->stream);
+    if (error == cudaSuccess) error = cudaStreamSynchronize(c->stream);
+    return error;
+}
+
+}  // namespace
+
 extern "C" int fortai_cuda_qwen35_attention_create(fortai_cuda_q8_context *context,
-    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *,
-    const fortai_cuda_q8_weights *, const fortai_cuda_q8_weights *, const void *, size_t,
-    const void *, size_t, int, int, int, int, int, int, float, float,
+    const fortai_cuda_q8_weights *query_weights, const fortai_cuda_q8_weights *key_weights,
+    const fortai_cuda_q8_weights *value_weights, const fortai_cuda_q8_weights *output_weights,
+    const void *query_norm, size_t query_norm_bytes, const void *key_norm,
+    size_t key_norm_bytes, int heads, int key_value_heads, int head_size, int value_size,
+    int max_context, int rope_dimension, float rope_base, float norm_epsilon,
     fortai_cuda_qwen35_attention **layer) {
-    if (layer) *layer = nullptr;
-    if (!context || !layer) return FORTAI_CUDA_INVALID;
-    return not_built(context, "the Qwen3.5 attention layer");
+    if (!context || !layer || !query_weights || !key_weights || !value_weights ||
+        !output_weights || !query_norm || !key_norm || heads <= 0 || key_value_heads <= 0 ||
+        head_size <= 0 || value_size <= 0 || max_context <= 0 || heads % key_value_heads != 0 ||
+        rope_dimension < 0 ||
+        (rope_dimension > 0 && (rope_dimension > head_size || rope_dimension % 2 != 0)) ||
+        rope_base <= 0.0f || norm_epsilon <= 0.0f) return FORTAI_CUDA_INVALID;
+    if (!owned(context, query_weights) || !owned(context, key_weights) ||
+        !owned(context, value_weights) || !owned(context, output_weights) ||
+        query_weights->rows != heads * 2 * head_size ||
+        key_weights->rows != key_value_heads * head_size ||
+        value_weights->rows != key_value_heads * value_size ||
+        output_weights->blocks * kBlockElems != heads * value_size ||
+        // the output gate of a head is the second half of its query slot
+        value_size > head_size ||
+        query_norm_bytes < static_cast<size_t>(head_size) * sizeof(float) ||
+        key_norm_bytes < static_cast<size_t>(head_size) * sizeof(float))
+        return FORTAI_CUDA_INVALID;
+    *layer = nullptr;
+    auto *created = new (std::nothrow) fortai_cuda_qwen35_attention;
+    if (!created) return FORTAI_CUDA_RUNTIME_ERROR;
+    created->context = context;
+    created->q = query_weights;
+    created->k = key_weights;
+    created->v = value_weights;
+    created->out = output_weights;
+    created->heads = heads;
+    created->kv_heads = key_value_heads;
+    created->head_size = head_size;
+    created->value_size = value_size;
+    created->max_context = max_context;
+    created->rope_dimension = rope_dimension;
+    created->rope_base = rope_base;
+    created->epsilon = norm_epsilon;
+    cudaSetDevice(context->device);
+    const size_t projection_floats = static_cast<size_t>(heads) * 2 * head_size +
+        static_cast<size_t>(key_value_heads) * (head_size + value_size);
+    cudaError_t error = device_copy_of(context, &created->q_norm, query_norm,
+        head_size * sizeof(float));
+    if (error == cudaSuccess)
+        error = device_copy_of(context, &created->k_norm, key_norm, head_size * sizeof(float));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->key_cache),
+            static_cast<size_t>(max_context) * key_value_heads * head_size * sizeof(__half));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->value_cache),
+            static_cast<size_t>(max_context) * key_value_heads * value_size * sizeof(__half));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->projections),
+            projection_floats * sizeof(float));
+    if (error == cudaSuccess)
+        error = cudaMalloc(reinterpret_cast<void **>(&created->attention),
+            static_cast<size_t>(heads) * value_size * sizeof(float));
+    if (error == cudaSuccess) error = clear_attention_state(created);
+    if (error != cudaSuccess) {
+        free_attention(created);
+        delete created;
+        return fail(context, "Qwen attention create", error);
+    }
+    *layer = created;
+    return FORTAI_CUDA_OK;
 }
+
 extern "C" int fortai_cuda_qwen35_attention_destroy(fortai_cuda_qwen35_attention *layer) {
+    if (!layer) return FORTAI_CUDA_OK;
+    if (layer->context) {
+        cudaSetDevice(layer->context->device);
+        free_attention(layer);
+    }
     delete layer;
     return FORTAI_CUDA_OK;
 }
+
 extern "C" int fortai_cuda_qwen35_attention_reset(fortai_cuda_qwen35_attention *layer) {
-    return layer ? not_built(layer->context, "the Qwen3.5 attention layer") : FORTAI_CUDA_INVALID;
+    if (!layer || !layer->context) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(layer->context->device);
+    const cudaError_t error = clear_attention_state(layer);
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(layer->context, "Qwen attention reset", error);
 }
+
+// The position used by the kernels is the context's device-side position word
+// (fortai_cuda_q8_context_set_position), as in the reference; `position` only bounds it.
 extern "C" int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attention *layer,
-    const void *, size_t, int, void *, size_t) {
-    return layer ? not_built(layer->context, "the Qwen3.5 attention layer") : FORTAI_CUDA_INVALID;
+    const void *device_activation, size_t activation_elements, int position,
+    void *device_output, size_t output_elements) {
+    if (!layer || !layer->context || !device_activation || !device_output || position < 0 ||
+        position >= layer->max_context) return FORTAI_CUDA_INVALID;
+    fortai_cuda_q8_context *c = layer->context;
+    if (activation_elements != static_cast<size_t>(layer->q->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(layer->out->rows) ||
+        layer->q->blocks != layer->k->blocks || layer->q->blocks != layer->v->blocks)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(c->device);
+    float *query = layer->projections;
+    float *key = query + static_cast<size_t>(layer->heads) * 2 * layer->head_size;
+    float *value = key + static_cast<size_t>(layer->kv_heads) * layer->head_size;
+    GemvParams p = single_params(c, layer->q, device_activation, query);
+    p.weights[1] = layer->k->data;
+    p.outputs[1] = key;
+    p.rows[1] = layer->k->rows;
+    p.weights[2] = layer->v->data;
+    p.outputs[2] = value;
+    p.rows[2] = layer->v->rows;
+    p.segments = 3;
+    p.total_rows = layer->q->rows + layer->k->rows + layer->v->rows;
+    cudaError_t error = launch_gemv(c, p, kActF32, kEpiPlain);
+    if (error == cudaSuccess) {
+        attention_prepare_kernel<<<layer->heads + layer->kv_heads, 256, 0, c->stream>>>(query, key,
+            value, layer->q_norm, layer->k_norm, layer->key_cache, layer->value_cache,
+            layer->heads, layer->kv_heads, layer->head_size, layer->value_size, c->position,
+            layer->rope_dimension, layer->rope_base, layer->epsilon);
+        const size_t shared = static_cast<size_t>(layer->max_context) * sizeof(float);
+        if (shared > 48 * 1024)
+            error = cudaFuncSetAttribute(attention_apply_kernel,
+                cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
+        if (error == cudaSuccess)
+            attention_apply_kernel<<<layer->heads, 256, shared, c->stream>>>(query,
+                layer->key_cache, layer->value_cache, layer->attention, layer->heads,
+                layer->kv_heads, layer->head_size, layer->value_size, c->position);
+        c->launches += 2;
+        if (error == cudaSuccess) error = cudaGetLastError();
+    }
+    if (error == cudaSuccess) {
+        const GemvParams o = single_params(c, layer->out, layer->attention,
+            static_cast<float *>(device_output));
+        error = launch_gemv(c, o, kActF32, kEpiPlain);
+    }
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(c, "Qwen attention device run", error);
 }
 
 extern "C" const char *fortai_cuda_q8_last_error(const fortai_cuda_q8_context *context) {

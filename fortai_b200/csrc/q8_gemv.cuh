@@ -70,37 +70,41 @@ struct GemvParams {
 
 // Tail of a peer-output GEMV: turns "every rank stored its slice everywhere" into "this
 // launch is complete only when every rank's slice has arrived here", without a second
-// kernel.  Every CTA publishes its stores system-wide and counts itself; the last one
-// raises this rank's flag in every peer's memory and then waits, for at most about one
-// second, until every peer has raised its flag here.  A wait that runs out writes a
+// kernel.  Every CTA publishes its stores system-wide and counts itself; in the last one,
+// one lane per peer raises this rank's flag in that peer's memory and then waits, for at
+// most about one second, until that peer has raised its flag here.  A wait that runs out writes a
 // status word and returns; the kernel never spins without a bound.  All ranks must run
 // on different GPUs (they wait on one another).
 __device__ __forceinline__ void peer_allgather_tail(const GemvParams &p) {
     if (p.sequence == 0) return;
+    __shared__ int is_last_cta;
     __syncthreads();
-    if (threadIdx.x != 0) return;
-    __threadfence_system();
-    const unsigned arrived = atomicAdd(p.cta_counter, 1u);
-    if (arrived != gridDim.x - 1) return;
-    *p.cta_counter = 0;                       // ready for the next launch
-    __threadfence_system();
-    for (int peer = 0; peer < p.peers; ++peer) {
-        unsigned *flag = p.peer_flags[peer] + p.my_rank;
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(p.sequence) : "memory");
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        const unsigned arrived = atomicAdd(p.cta_counter, 1u);
+        is_last_cta = arrived == gridDim.x - 1;
+        if (is_last_cta) {
+            *p.cta_counter = 0;                   // ready for the next launch
+            __threadfence_system();
+        }
     }
+    __syncthreads();
+    if (!is_last_cta || threadIdx.x >= p.peers) return;
+    // one lane per peer: raise this rank's flag there, then wait for that peer's flag here
+    const int peer = threadIdx.x;
+    unsigned *remote = p.peer_flags[peer] + p.my_rank;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.sequence) : "memory");
+    const unsigned *local = p.my_flags + peer;
     const long long start = clock64();
-    const long long limit = 2000000000LL;     // about a second of SM clocks
-    for (int peer = 0; peer < p.peers; ++peer) {
-        const unsigned *flag = p.my_flags + peer;
-        for (;;) {
-            unsigned seen;
-            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
-            // sequence numbers only grow; the signed difference survives wrap-around
-            if (static_cast<int>(seen - p.sequence) >= 0) break;
-            if (clock64() - start > limit) {
-                atomicExch(p.status, kStatusPeerFlagTimeout);
-                return;
-            }
+    const long long limit = 2000000000LL;         // about a second of SM clocks
+    for (;;) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(local) : "memory");
+        // sequence numbers only grow; the signed difference survives wrap-around
+        if (static_cast<int>(seen - p.sequence) >= 0) break;
+        if (clock64() - start > limit) {
+            atomicExch(p.status, kStatusPeerFlagTimeout);
+            break;
         }
     }
 }

@@ -1,0 +1,244 @@
+// Device kernels of the two Qwen3.5 layer objects of the C ABI: the gated-delta-net
+// ("recurrent") layer and the gated single-query attention layer.  They sit next to the
+// Q8_0 hot path (every projection inside them is a Q8_0 GEMV from q8_gemv.cuh) and
+// exist so that the reference's device pipeline runs on this backend end to end.
+//
+// Semantics follow the reference CPU model, which is the correctness reference of that
+// project (src/models/qwen35/fortai_qwen35_cpu.f90:801-918 recurrent, :978-1035
+// attention, helpers :1434-1539) and its C step function
+// (src/backend/cpu/fortai_q8_dot.c:355-445); the reference's own CUDA versions are
+// backend/cuda/fortai_cuda_backend.cu:386-481 and :539-669.
+#pragma once
+
+#include <cuda_fp16.h>
+
+#include "q8_common.cuh"
+
+namespace fortai_b200 {
+
+__device__ __forceinline__ float silu_ieee(float x) {
+    return __fdiv_rn(x, 1.0f + expf(-x));
+}
+
+__device__ __forceinline__ float sigmoid_stable(float x) {
+    if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+    const float e = expf(x);
+    return e / (1.0f + e);
+}
+
+__device__ __forceinline__ float softplus_clamped(float x) {
+    if (x > 20.0f) return x;
+    if (x < -20.0f) return expf(x);
+    return logf(1.0f + expf(x));
+}
+
+__device__ __forceinline__ double warp_sum_double(double v) {
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    return v;
+}
+
+// Sum over a CTA of up to 1024 threads; every thread gets the result.
+__device__ __forceinline__ double cta_sum_double(double v, double *scratch32) {
+    v = warp_sum_double(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) scratch32[warp] = v;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) total += scratch32[w];
+    return total;
+}
+
+// ---- recurrent layer ------------------------------------------------------------
+// Causal depthwise convolution over the last `kernel` inputs of every channel, SiLU,
+// and the shift of the per-channel history.  conv_state is (kernel - 1) x conv_size,
+// oldest first.
+__global__ void __launch_bounds__(256)
+gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_weights,
+    float *__restrict__ conv_state, int conv_size, int kernel) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= conv_size) return;
+    const float now = qkv[c];
+    float acc = 0.0f;
+    for (int slot = 0; slot < kernel - 1; ++slot) {
+        const float held = conv_state[slot * conv_size + c];
+        acc += conv_weights[c * kernel + slot] * held;
+        if (slot > 0) conv_state[(slot - 1) * conv_size + c] = held;
+    }
+    acc += conv_weights[c * kernel + kernel - 1] * now;
+    conv_state[(kernel - 2) * conv_size + c] = now;
+    qkv[c] = silu_ieee(acc);
+}
+
+// L2 normalisation of the query heads and the key heads of the convolved vector: one
+// warp per head.  Queries start at head * head_size, keys at state_size * key_heads +
+// head * head_size.
+__global__ void __launch_bounds__(256)
+gdn_l2_normalize_kernel(float *__restrict__ values, int key_heads, int head_size, int state_size,
+    float epsilon) {
+    const int slice = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (slice >= 2 * key_heads) return;
+    float *v = values + (slice < key_heads ? slice * head_size
+                                           : state_size * key_heads + (slice - key_heads) * head_size);
+    double sum = 0.0;
+    for (int i = lane; i < head_size; i += 32) sum += static_cast<double>(v[i]) * v[i];
+    sum = warp_sum_double(sum);
+    const float inverse = 1.0f / fmaxf(sqrtf(static_cast<float>(sum)), epsilon);
+    for (int i = lane; i < head_size; i += 32) v[i] *= inverse;
+}
+
+// One gated-delta-net step for one value head per CTA: every warp owns rows of the
+// head_size x head_size state (decay, key dot, delta update, query dot), then the
+// head's output is RMS-normalised, scaled by ssm_norm and gated by silu(gate).
+__global__ void __launch_bounds__(256)
+gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
+    const float *__restrict__ alpha, const float *__restrict__ beta,
+    const float *__restrict__ ssm_a, const float *__restrict__ ssm_dt,
+    const float *__restrict__ ssm_norm, float *__restrict__ state, float *__restrict__ output,
+    int state_size, int key_heads, int value_heads, int head_size, float epsilon) {
+    extern __shared__ float gdn_shared[];     // head_size outputs
+    __shared__ double reduce[32];
+    const int head = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int key_head = head / (value_heads / key_heads);
+    const float *query = conv + key_head * head_size;
+    const float *key = conv + state_size * key_heads + key_head * head_size;
+    const float *value = conv + 2 * state_size * key_heads + head * head_size;
+    const float decay = expf(ssm_a[head] * softplus_clamped(alpha[head] + ssm_dt[head]));
+    const float b = sigmoid_stable(beta[head]);
+    const float scale = 1.0f / sqrtf(static_cast<float>(head_size));
+    float *head_state = state + static_cast<size_t>(head) * head_size * head_size;
+    for (int row = warp; row < head_size; row += warps) {
+        float *s = head_state + static_cast<size_t>(row) * head_size;
+        float key_dot = 0.0f;
+        for (int c = lane; c < head_size; c += 32) {
+            const float decayed = s[c] * decay;
+            s[c] = decayed;
+            key_dot = fmaf(decayed, key[c], key_dot);
+        }
+        key_dot = warp_sum(key_dot);
+        const float delta = (value[row] - key_dot) * b;
+        float query_dot = 0.0f;
+        for (int c = lane; c < head_size; c += 32) {
+            const float updated = fmaf(delta, key[c], s[c]);
+            s[c] = updated;
+            query_dot = fmaf(updated, query[c], query_dot);
+        }
+        query_dot = warp_sum(query_dot);
+        if (lane == 0) gdn_shared[row] = query_dot * scale;
+    }
+    __syncthreads();
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < head_size; i += blockDim.x)
+        sum += static_cast<double>(gdn_shared[i]) * gdn_shared[i];
+    sum = cta_sum_double(sum, reduce);
+    const float norm = sqrtf(static_cast<float>(sum / head_size) + epsilon);
+    for (int i = threadIdx.x; i < head_size; i += blockDim.x)
+        output[head * head_size + i] = gdn_shared[i] / norm * ssm_norm[i] *
+            silu_ieee(gate[head * head_size + i]);
+}
+
+// ---- attention layer --------------------------------------------------------------
+__device__ __forceinline__ void rope_pair(float *v, int dimension, int i, int position,
+    float base) {
+    const float angle = static_cast<float>(position) /
+        powf(base, static_cast<float>(2 * i) / static_cast<float>(dimension));
+    const float c = cosf(angle), s = sinf(angle);
+    const float first = v[i], second = v[i + dimension / 2];
+    v[i] = first * c - second * s;
+    v[i + dimension / 2] = first * s + second * c;
+}
+
+// Blocks [0, heads): RMS-normalise (learned scale) and rotate the query part of each
+// head (the second half of a head's 2 * head_size slot is its output gate and is left
+// alone).  Blocks [heads, heads + kv_heads): the same for a key head, then store key and
+// value of this position in the binary16 caches.
+__global__ void __launch_bounds__(256)
+attention_prepare_kernel(float *__restrict__ query, float *__restrict__ key,
+    const float *__restrict__ value, const float *__restrict__ query_norm,
+    const float *__restrict__ key_norm, __half *__restrict__ key_cache,
+    __half *__restrict__ value_cache, int heads, int kv_heads, int head_size, int value_size,
+    const int *__restrict__ position_ptr, int rope_dimension, float rope_base, float epsilon) {
+    __shared__ double reduce[32];
+    const int position = *position_ptr;
+    const bool is_query = static_cast<int>(blockIdx.x) < heads;
+    const int head = is_query ? blockIdx.x : blockIdx.x - heads;
+    float *v = is_query ? query + head * 2 * head_size : key + head * head_size;
+    const float *weights = is_query ? query_norm : key_norm;
+    double sum = 0.0;
+    for (int i = threadIdx.x; i < head_size; i += blockDim.x)
+        sum += static_cast<double>(v[i]) * v[i];
+    sum = cta_sum_double(sum, reduce);
+    const float inverse = 1.0f / sqrtf(static_cast<float>(sum / head_size) + epsilon);
+    for (int i = threadIdx.x; i < head_size; i += blockDim.x) v[i] = v[i] * inverse * weights[i];
+    __syncthreads();
+    if (rope_dimension > 0)
+        for (int i = threadIdx.x; i < rope_dimension / 2; i += blockDim.x)
+            rope_pair(v, rope_dimension, i, position, rope_base);
+    if (is_query) return;
+    __syncthreads();
+    for (int i = threadIdx.x; i < head_size; i += blockDim.x)
+        key_cache[(static_cast<size_t>(position) * kv_heads + head) * head_size + i] =
+            __float2half_rn(v[i]);
+    for (int i = threadIdx.x; i < value_size; i += blockDim.x)
+        value_cache[(static_cast<size_t>(position) * kv_heads + head) * value_size + i] =
+            __float2half_rn(value[head * value_size + i]);
+}
+
+// One CTA per head: scores against every cached key (one warp per position), softmax
+// over positions, weighted sum of cached values, sigmoid output gate.
+__global__ void __launch_bounds__(256)
+attention_apply_kernel(const float *__restrict__ query, const __half *__restrict__ key_cache,
+    const __half *__restrict__ value_cache, float *__restrict__ attention, int heads, int kv_heads,
+    int head_size, int value_size, const int *__restrict__ position_ptr) {
+    extern __shared__ float scores[];        // position + 1 entries
+    __shared__ float reduce[32];
+    const int head = blockIdx.x;
+    const int position = *position_ptr;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int kv_head = head / (heads / kv_heads);
+    const float *q = query + head * 2 * head_size;
+    const float *gate = q + head_size;
+    const float scale = 1.0f / sqrtf(static_cast<float>(head_size));
+    for (int p = warp; p <= position; p += warps) {
+        const __half *k = key_cache + (static_cast<size_t>(p) * kv_heads + kv_head) * head_size;
+        float dot = 0.0f;
+        for (int i = lane; i < head_size; i += 32) dot = fmaf(q[i], __half2float(k[i]), dot);
+        dot = warp_sum(dot);
+        if (lane == 0) scores[p] = dot * scale;
+    }
+    __syncthreads();
+    float maximum = -3.402823466e+38f;
+    for (int p = threadIdx.x; p <= position; p += blockDim.x) maximum = fmaxf(maximum, scores[p]);
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1)
+        maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+    if (lane == 0) reduce[warp] = maximum;
+    __syncthreads();
+    maximum = reduce[0];
+    for (int w = 1; w < warps; ++w) maximum = fmaxf(maximum, reduce[w]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (int p = threadIdx.x; p <= position; p += blockDim.x) {
+        const float e = expf(scores[p] - maximum);
+        scores[p] = e;
+        sum += e;
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) reduce[warp] = sum;
+    __syncthreads();
+    float normalizer = 0.0f;
+    for (int w = 0; w < warps; ++w) normalizer += reduce[w];
+    for (int i = threadIdx.x; i < value_size; i += blockDim.x) {
+        float total = 0.0f;
+        for (int p = 0; p <= position; ++p) {
+            const __half *v = value_cache + (static_cast<size_t>(p) * kv_heads + kv_head) * value_size;
+            total = fmaf(scores[p] / normalizer, __half2float(v[i]), total);
+        }
+        attention[head * value_size + i] = total * sigmoid_stable(gate[i]);
+    }
+}
+
+}  // namespace fortai_b200

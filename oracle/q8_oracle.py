@@ -303,6 +303,9 @@ class Reference:
                                            c_void_p, c_void_p, c_int]
         L.ref_thread_count.restype = c_int
         L.ref_uses_avx2.restype = c_int
+        L.fortai_gdn_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float,
+                                      c_int64, c_float, c_void_p]
+        L.fortai_silu.argtypes = [c_void_p, c_int64]
 
     @staticmethod
     def available(fast: bool = False) -> bool:
@@ -349,6 +352,21 @@ class Reference:
         out = np.ascontiguousarray(left, dtype=np.float32).copy()
         r = np.ascontiguousarray(right, dtype=np.float32)
         self.lib.fortai_silu_product(_ptr(out), _ptr(r), out.size)
+        return out
+
+    def gdn_step(self, state, key, value, query, decay, beta, output_scale):
+        """fortai_gdn_step: `state` (head_size x head_size, float32) is updated in place."""
+        hs = key.size
+        out = np.zeros(hs, dtype=np.float32)
+        self.lib.fortai_gdn_step(_ptr(state), _ptr(np.ascontiguousarray(key, np.float32)),
+                                 _ptr(np.ascontiguousarray(value, np.float32)),
+                                 _ptr(np.ascontiguousarray(query, np.float32)), c_float(decay),
+                                 c_float(beta), hs, c_float(output_scale), _ptr(out))
+        return out
+
+    def silu(self, values):
+        out = np.ascontiguousarray(values, dtype=np.float32).copy()
+        self.lib.fortai_silu(_ptr(out), out.size)
         return out
 
     def dequantize_row(self, weights, row, blocks):
