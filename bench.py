@@ -474,16 +474,17 @@ def run_mmq_only(args):
     stat = ctx.create(0, stream=torch.cuda.current_stream().cuda_stream)
     if not stat.is_ok():
         raise SystemExit(f"context creation failed: {stat}")
+    apply_options(ctx, args.options)
     result = bench_mmq(torch, backend, ctx, tokens=args.tokens, iters=max(1, args.steps),
-                       warmup=max(1, args.warmup))
+                       warmup=max(1, args.warmup), rows=args.mmq_rows, width=args.mmq_width)
     ctx.destroy()
     print(json.dumps(result), flush=True)
     return 0 if result and result.get("ok") else 1
 
 
-def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3):
-    """Batched prefill product, M=512 x K=2560 x N=9728 (BASELINE configs[3])."""
-    MMQ_M = tokens
+def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3, rows=MMQ_N, width=MMQ_K):
+    """Batched product; by default M=512 x K=2560 x N=9728 (BASELINE configs[3])."""
+    MMQ_M, MMQ_N, MMQ_K = tokens, rows, width
     host_weights = make_device_weights(torch, backend, ctx, 0, MMQ_N, MMQ_K, seed=2)
     w = backend.cuda_q8_weights_t()
     if not w.upload(ctx, host_weights, host_weights.size, MMQ_N, MMQ_K).is_ok():
@@ -537,6 +538,108 @@ def decode_shapes():
                    (f"H{hidden} gate/up", inner, hidden), (f"H{hidden} down", hidden, inner)]
     shapes += [("27B gate/up", 17408, 5120), ("27B down", 5120, 17408)]
     return shapes
+
+
+def graph_time_us(torch, ctx, enqueue, per_graph=20, replays=25, warm=3):
+    """Average device time of one `enqueue()` when `per_graph` of them are captured into a
+    CUDA graph on the context's own stream and the graph is replayed `replays` times."""
+    stream = torch.cuda.ExternalStream(ctx.stream())
+    for i in range(warm):
+        enqueue(i)
+    torch.cuda.synchronize()
+    before = ctx.launch_count()
+    assert ctx.capture_begin().is_ok()
+    for i in range(per_graph):
+        enqueue(i)
+    assert ctx.capture_end().is_ok()
+    launches = (ctx.launch_count() - before) // per_graph
+    for _ in range(3):
+        ctx.graph_launch()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(replays):
+        ctx.graph_launch()
+    b.record(stream)
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / (replays * per_graph), int(launches)
+
+
+def sweep_batched(torch, backend, args):
+    """Batched product at the token counts of BASELINE configs[3] and the batch-8 decode of
+    configs[4]; weights rotate over copies that together exceed twice the L2 size."""
+    l2_bytes = 126 * 1024 * 1024
+    cases = [("prefill 9728x2560", 9728, 2560, (2, 4, 8, 16, 32, 64, 128, 512)),
+             ("27B gate/up 17408x5120", 17408, 5120, (8,)),
+             ("27B down 5120x17408", 5120, 17408, (8,))]
+    for label, rows, width, token_counts in cases:
+        if args.only and args.only not in label and args.only not in "batched":
+            continue
+        nbytes = rows * (width // 32) * 34
+        copies = int(max(2, min(64, (2 * l2_bytes + nbytes - 1) // nbytes + 1)))
+        for tokens in token_counts:
+            # a context holds one captured graph, so every token count gets its own
+            ctx = backend.cuda_q8_context_t()
+            if not ctx.create(0).is_ok():
+                raise SystemExit("context creation failed")
+            apply_options(ctx, args.options)
+            handles = []
+            for c in range(copies):
+                host = make_device_weights(torch, backend, ctx, 0, rows, width, seed=50 + c)
+                w = backend.cuda_q8_weights_t()
+                if not w.upload(ctx, host, host.size, rows, width).is_ok():
+                    raise SystemExit("weight upload failed")
+                handles.append(w)
+            x = torch.randn(tokens, width, device="cuda", dtype=torch.float32)
+            out = torch.empty(tokens, rows, device="cuda", dtype=torch.float32)
+
+            def enqueue(i):
+                stat = backend.cuda_q8_matmul_device_f32(ctx, handles[i % copies], x.data_ptr(),
+                                                         tokens, out.data_ptr(), out.numel())
+                assert stat.is_ok(), stat
+            us, launches = graph_time_us(torch, ctx, enqueue, per_graph=max(copies, 10))
+            ops = 2.0 * tokens * width * rows
+            print(json.dumps({"shape": f"{label} M={tokens}", "weight_bytes": nbytes,
+                              "hbm_cold_us": us, "weight_gbs": nbytes / us / 1e3,
+                              "tops": ops / us / 1e6, "launches_per_call": launches,
+                              "copies": copies}), flush=True)
+            for w in handles:
+                w.destroy()
+            ctx.destroy()
+
+
+def sweep_batched_ffn(torch, backend, args):
+    """BASELINE configs[4] at batch 8: the 27B-class FFN for eight activations per call."""
+    for hidden, inner, tokens in ((5120, 17408, 8), (2560, 9728, 8)):
+        label = f"FFN H{hidden} F{inner} M={tokens}"
+        if args.only and args.only not in label and args.only not in "batched":
+            continue
+        ctx = backend.cuda_q8_context_t()
+        if not ctx.create(0).is_ok():
+            raise SystemExit("context creation failed")
+        apply_options(ctx, args.options)
+        mats = []
+        for seed, (r, k) in enumerate(((inner, hidden), (inner, hidden), (hidden, inner))):
+            host = make_device_weights(torch, backend, ctx, 0, r, k, seed=30 + seed)
+            w = backend.cuda_q8_weights_t()
+            w.upload(ctx, host, host.size, r, k)
+            mats.append(w)
+        x = torch.randn(tokens, hidden, device="cuda", dtype=torch.float32)
+        out = torch.empty(tokens, hidden, device="cuda", dtype=torch.float32)
+
+        def enqueue(i):
+            stat = backend.cuda_q8_ffn_batch_device(ctx, mats[0], mats[1], mats[2], x.data_ptr(),
+                                                    tokens, out.data_ptr(), out.numel())
+            assert stat.is_ok(), stat
+        us, launches = graph_time_us(torch, ctx, enqueue, per_graph=10)
+        nbytes = 3 * inner * (hidden // 32) * 34
+        print(json.dumps({"shape": label, "weight_bytes": nbytes, "us": us,
+                          "gbs": nbytes / us / 1e3, "launches_per_call": launches,
+                          "note": "same matrices every call; 284 MB exceeds L2 for the 27B layer"}),
+              flush=True)
+        for w in mats:
+            w.destroy()
+        ctx.destroy()
 
 
 def run_sweep(args):
@@ -645,6 +748,8 @@ def run_sweep(args):
         for w in mats:
             w.destroy()
         ctx.destroy()
+    sweep_batched(torch, backend, args)
+    sweep_batched_ffn(torch, backend, args)
     return 0
 
 
@@ -668,6 +773,8 @@ def main():
     parser.add_argument("--mmq-only", action="store_true",
                         help="run only the batched prefill product (profiler captures)")
     parser.add_argument("--tokens", type=int, default=MMQ_M, help="token count of the prefill leg")
+    parser.add_argument("--mmq-rows", type=int, default=MMQ_N, help="--mmq-only: weight rows")
+    parser.add_argument("--mmq-width", type=int, default=MMQ_K, help="--mmq-only: weight width")
     parser.add_argument("--options", default="",
                         help="backend tuning knobs, name=value[,name=value...]")
     parser.add_argument("--only", default="", help="--sweep: only shapes whose label contains this")

@@ -580,6 +580,24 @@ def cuda_q8_matmul_block_dots_device(context, weights, device_activation, tokens
     return stat
 
 
+def cuda_q8_ffn_batch_device(context, gate_weights, up_weights, down_weights, device_activation,
+                             tokens, device_output, output_elements) -> status_t:
+    """Extension: the FFN of `tokens` activations in one call (token-major fp32)."""
+    stat = status_t()
+    if (not context.handle or not gate_weights.handle or not up_weights.handle
+            or not down_weights.handle or not device_activation or not device_output
+            or tokens <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 batched FFN")
+        return stat
+    code = _lib().fortai_cuda_q8_ffn_batch_device(context.handle, gate_weights.handle,
+                                                  up_weights.handle, down_weights.handle,
+                                                  device_activation, int(tokens), device_output,
+                                                  output_elements)
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 batched FFN failed")
+    return stat
+
+
 def cuda_q8_matvec_device_f32_peers(context, weights, device_activation, activation_elements,
                                     peer_outputs, first_row, output_elements) -> status_t:
     stat = status_t()

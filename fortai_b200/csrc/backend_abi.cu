@@ -16,6 +16,7 @@
 #include "q8_common.cuh"
 #include "q8_gemv.cuh"
 #include "q8_mmq.cuh"
+#include "q8_fewtok.cuh"
 #include "qwen35_layers.cuh"
 
 using namespace fortai_b200;
@@ -53,7 +54,13 @@ struct fortai_cuda_q8_context {
     int gemv_balance = 0;      // 1 = trim the grid so that the last round of rows is full
     int ring_stages = 0;
     int ring_rows = 0;
-    int mmq_min_tokens = 0;
+    int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 33)
+    int fewtok_splits = 0;     // K ranges of the few-token kernel (0 = as few as fit)
+    int fewtok_threads = 0;    // its CTA size (0 = 256)
+    int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
+    int fewtok_step = 0;       // bytes of a row per step (0 = chosen from the shape)
+    int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
+    int fewtok_off = 0;        // 1 = small batches run one GEMV per token
     char error[256] = {};
 };
 
@@ -1548,6 +1555,16 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->ring_stages = value;
     else if (!std::strcmp(name, "ring_rows") && value <= 256) context->ring_rows = value;
     else if (!std::strcmp(name, "mmq_min_tokens")) context->mmq_min_tokens = value;
+    else if (!std::strcmp(name, "fewtok_splits") && value >= 0) context->fewtok_splits = value;
+    else if (!std::strcmp(name, "fewtok_threads") && value >= 0 && value <= 512 &&
+             value % 32 == 0) context->fewtok_threads = value;
+    else if (!std::strcmp(name, "fewtok_step") &&
+             (value == 0 || value == 64 || value == 256 || value == 512))
+        context->fewtok_step = value;
+    else if (!std::strcmp(name, "fewtok_stages") && (value == 0 || value == 2 || value == 3))
+        context->fewtok_stages = value;
+    else if (!std::strcmp(name, "fewtok_overlap")) context->fewtok_overlap = value != 0;
+    else if (!std::strcmp(name, "fewtok_off")) context->fewtok_off = value != 0;
     else return FORTAI_CUDA_INVALID;
     return FORTAI_CUDA_OK;
 }
@@ -1660,20 +1677,159 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
 // ---------------------------------------------------------------------------
 namespace {
 
-// Small batches stay on the streaming kernel, one launch per token: the weights
-// of any projection short of the lm_head stay L2-resident between launches.
+// One GEMV launch per token: the fallback for widths the batched kernels do not take.
 cudaError_t enqueue_matmul_streaming(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
-    const void *activation, int act, int tokens, float *output) {
+    const void *activation, int act, int tokens, float *output, int32_t *block_dots) {
     cudaError_t error = cudaSuccess;
     const size_t act_stride = act == kActF32 ? static_cast<size_t>(w->width) * sizeof(float)
                                              : static_cast<size_t>(w->blocks) * kBlockBytes;
     for (int t = 0; t < tokens && error == cudaSuccess; ++t) {
+        float *out = block_dots
+            ? reinterpret_cast<float *>(block_dots + static_cast<size_t>(t) * w->rows * w->blocks)
+            : output + static_cast<size_t>(t) * w->rows;
         const GemvParams p = single_params(c, w,
-            static_cast<const uint8_t *>(activation) + t * act_stride,
-            output + static_cast<size_t>(t) * w->rows);
-        error = launch_gemv(c, p, act, kEpiPlain);
+            static_cast<const uint8_t *>(activation) + t * act_stride, out);
+        error = launch_gemv(c, p, act, block_dots ? kEpiBlockDots : kEpiPlain);
     }
     return error;
+}
+
+template <int NT, int CB, int ST, bool DOTS>
+cudaError_t launch_fewtok_instance(fortai_cuda_q8_context *c, const FewTokParams &p,
+    const FewTokPlan &plan) {
+    cudaError_t error = cudaSuccess;
+    if (plan.smem > 48 * 1024)
+        error = cudaFuncSetAttribute(q8_fewtok_kernel<NT, CB, ST, DOTS>,
+            cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem));
+    int per_sm = 0;
+    if (error == cudaSuccess)
+        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm,
+            q8_fewtok_kernel<NT, CB, ST, DOTS>, plan.threads, plan.smem);
+    if (error != cudaSuccess) return error;
+    if (per_sm < 1) return cudaErrorLaunchOutOfResources;
+    const int grid = fewtok_grid(plan, p.rows, p.width, c->sm_count, per_sm);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(plan.threads);
+    config.dynamicSmemBytes = plan.smem;
+    config.stream = c->stream;
+    cudaLaunchAttribute overlap = {};
+    overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    overlap.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &overlap;
+    config.numAttrs = c->fewtok_overlap ? 1 : 0;
+    error = cudaLaunchKernelEx(&config, q8_fewtok_kernel<NT, CB, ST, DOTS>, p);
+    ++c->launches;
+    return error != cudaSuccess ? error : cudaGetLastError();
+}
+
+template <int NT, int CB>
+cudaError_t launch_fewtok_stages(fortai_cuda_q8_context *c, const FewTokParams &p,
+    const FewTokPlan &plan, bool dots) {
+    if (dots) return launch_fewtok_instance<NT, CB, 2, true>(c, p, plan);
+    return plan.stages == 3 ? launch_fewtok_instance<NT, CB, 3, false>(c, p, plan)
+                            : launch_fewtok_instance<NT, CB, 2, false>(c, p, plan);
+}
+
+template <int NT>
+cudaError_t launch_fewtok(fortai_cuda_q8_context *c, const FewTokParams &p, const FewTokPlan &plan,
+    bool dots) {
+    switch (plan.step_bytes) {
+    case 512: return launch_fewtok_stages<NT, 512>(c, p, plan, dots);
+    case 256: return launch_fewtok_stages<NT, 256>(c, p, plan, dots);
+    default: return launch_fewtok_stages<NT, 64>(c, p, plan, dots);
+    }
+}
+
+// 2..32 tokens: activation image, zeroed output, one pass over the weights.
+cudaError_t enqueue_fewtok(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
+    const void *activation, int act, int tokens, float *output, int32_t *block_dots) {
+    const int padded = fewtok_padded_tokens(tokens);
+    FewTokPlan plan;
+    if (!fewtok_plan(w->rows, w->width, padded, c->sm_count, c->fewtok_splits,
+            c->fewtok_threads, c->fewtok_step, block_dots ? 2 : c->fewtok_stages, &plan))
+        return cudaErrorNotSupported;
+    cudaError_t error = mmq_reserve(reinterpret_cast<void **>(&c->scratch_aux),
+        &c->scratch_aux_bytes, w->rows, w->width, tokens);
+    if (error != cudaSuccess) return error;
+    int8_t *quants = reinterpret_cast<int8_t *>(c->scratch_aux);
+    float *scales = reinterpret_cast<float *>(quants + static_cast<size_t>(padded) * w->width);
+    const long long prep_warps = static_cast<long long>(padded) * w->blocks;
+    const int prep_grid = static_cast<int>(std::max<long long>(1,
+        std::min<long long>((prep_warps + 7) / 8, static_cast<long long>(c->sm_count) * 16)));
+    // the output (cudaMalloc'ed or a 16-byte aligned slice) is zeroed 16 bytes at a time by
+    // the prepare kernel; an unaligned or odd-sized one by a memset node
+    const size_t out_bytes = output ? static_cast<size_t>(tokens) * w->rows * sizeof(float) : 0;
+    const bool zero_in_kernel = output && reinterpret_cast<uintptr_t>(output) % 16 == 0 &&
+        out_bytes % 16 == 0;
+    float4 *zero = zero_in_kernel ? reinterpret_cast<float4 *>(output) : nullptr;
+    const long long zero_count = zero_in_kernel ? static_cast<long long>(out_bytes / 16) : 0;
+    if (output && !zero_in_kernel) {
+        error = cudaMemsetAsync(output, 0, out_bytes, c->stream);
+        if (error != cudaSuccess) return error;
+    }
+    if (act == kActF32)
+        fewtok_prepare_kernel<1><<<prep_grid, 256, 0, c->stream>>>(activation, tokens, padded,
+            w->width, quants, scales, zero, zero_count);
+    else
+        fewtok_prepare_kernel<0><<<prep_grid, 256, 0, c->stream>>>(activation, tokens, padded,
+            w->width, quants, scales, zero, zero_count);
+    ++c->launches;
+    error = cudaGetLastError();
+    if (error != cudaSuccess) return error;
+    FewTokParams p = {};
+    p.weights = w->data;
+    p.rows = w->rows;
+    p.width = w->width;
+    p.blocks = w->blocks;
+    p.row_stride = static_cast<int>(w->row_stride);
+    p.act_quants = quants;
+    p.act_scales = scales;
+    p.tokens = tokens;
+    p.padded_tokens = padded;
+    p.splits = plan.splits;
+    p.blocks_per_split = plan.blocks_per_split;
+    p.output = output;
+    p.block_dots = block_dots;
+    const bool dots = block_dots != nullptr;
+    if (padded == 8) return launch_fewtok<1>(c, p, plan, dots);
+    if (padded == 16) return launch_fewtok<2>(c, p, plan, dots);
+    return launch_fewtok<4>(c, p, plan, dots);
+}
+
+// Batched product, any token count: the tcgen05 kernel above 32 tokens, the few-token
+// kernel below that (in groups of up to 32 where the tcgen05 kernel does not take the
+// width), one GEMV per token as the last resort.  Exactly one of output / block_dots.
+cudaError_t enqueue_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
+    const void *activation, int act, int tokens, float *output, int32_t *block_dots) {
+    if (mmq_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
+        return mmq_enqueue(c->stream, c->sm_count, c->status_device,
+            &const_cast<fortai_cuda_q8_weights *>(w)->mmq, w->data, w->rows, w->width,
+            w->row_stride, activation, act, tokens, output, block_dots,
+            reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes, &c->launches);
+    if (c->fewtok_off || !fewtok_supported(w->rows, w->width, tokens))
+        return enqueue_matmul_streaming(c, w, activation, act, tokens, output, block_dots);
+    const size_t act_stride = act == kActF32 ? static_cast<size_t>(w->width) * sizeof(float)
+                                             : static_cast<size_t>(w->blocks) * kBlockBytes;
+    cudaError_t error = cudaSuccess;
+    for (int first = 0; first < tokens && error == cudaSuccess; first += kFewTokMaxTokens) {
+        const int count = std::min(kFewTokMaxTokens, tokens - first);
+        const void *act_at = static_cast<const uint8_t *>(activation) + first * act_stride;
+        float *out_at = output ? output + static_cast<size_t>(first) * w->rows : nullptr;
+        int32_t *dots_at = block_dots
+            ? block_dots + static_cast<size_t>(first) * w->rows * w->blocks : nullptr;
+        if (count >= 2)
+            error = enqueue_fewtok(c, w, act_at, act, count, out_at, dots_at);
+        else
+            error = enqueue_matmul_streaming(c, w, act_at, act, count, out_at, dots_at);
+    }
+    return error;
+}
+
+// scratch the batched kernels need, grown outside a timed region
+cudaError_t reserve_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w, int tokens) {
+    return mmq_reserve(reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes, w->rows,
+        w->width, tokens);
 }
 
 }  // namespace
@@ -1685,18 +1841,8 @@ extern "C" int fortai_cuda_q8_matmul_device_f32(fortai_cuda_q8_context *context,
         output_elements < static_cast<size_t>(tokens) * weights->rows)
         return FORTAI_CUDA_INVALID;
     cudaSetDevice(context->device);
-    cudaError_t error;
-    if (mmq_supported(weights->rows, weights->width, tokens, context->mmq_min_tokens)) {
-        error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
-            &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data, weights->rows,
-            weights->width, weights->row_stride, device_activation, kActF32, tokens,
-            static_cast<float *>(device_output), nullptr,
-            reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
-            &context->launches);
-    } else {
-        error = enqueue_matmul_streaming(context, weights, device_activation, kActF32, tokens,
-            static_cast<float *>(device_output));
-    }
+    const cudaError_t error = enqueue_matmul(context, weights, device_activation, kActF32, tokens,
+        static_cast<float *>(device_output), nullptr);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device F32 matmul", error);
 }
 
@@ -1706,25 +1852,11 @@ extern "C" int fortai_cuda_q8_matmul_resident(fortai_cuda_q8_context *context,
     if (!owned(context, weights) || !device_activation || !device_output || tokens <= 0 ||
         !kernel_ms) return FORTAI_CUDA_INVALID;
     cudaSetDevice(context->device);
-    cudaError_t error = cudaSuccess;
-    const bool tensor = mmq_supported(weights->rows, weights->width, tokens,
-        context->mmq_min_tokens);
-    if (tensor)   // grow scratch before the timed region
-        error = mmq_reserve(reinterpret_cast<void **>(&context->scratch_aux),
-            &context->scratch_aux_bytes, weights->rows, weights->width, tokens);
+    cudaError_t error = reserve_matmul(context, weights, tokens);   // before the timed region
     if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
-    if (error == cudaSuccess) {
-        if (tensor)
-            error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
-                &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data,
-                weights->rows, weights->width, weights->row_stride, device_activation, kActQ8,
-                tokens, static_cast<float *>(device_output), nullptr,
-                reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
-                &context->launches);
-        else
-            error = enqueue_matmul_streaming(context, weights, device_activation, kActQ8, tokens,
-                static_cast<float *>(device_output));
-    }
+    if (error == cudaSuccess)
+        error = enqueue_matmul(context, weights, device_activation, kActQ8, tokens,
+            static_cast<float *>(device_output), nullptr);
     if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
     if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
     if (error == cudaSuccess)
@@ -1742,28 +1874,15 @@ extern "C" int fortai_cuda_q8_matmul_host_f32(fortai_cuda_q8_context *context,
     cudaSetDevice(context->device);
     const size_t in_bytes = static_cast<size_t>(tokens) * weights->width * sizeof(float);
     const size_t out_bytes = static_cast<size_t>(tokens) * weights->rows * sizeof(float);
-    const bool tensor = mmq_supported(weights->rows, weights->width, tokens,
-        context->mmq_min_tokens);
     cudaError_t error = ensure_scratch(context, in_bytes, out_bytes);
-    if (error == cudaSuccess && tensor)
-        error = mmq_reserve(reinterpret_cast<void **>(&context->scratch_aux),
-            &context->scratch_aux_bytes, weights->rows, weights->width, tokens);
+    if (error == cudaSuccess) error = reserve_matmul(context, weights, tokens);
     if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
     if (error == cudaSuccess)
         error = cudaMemcpyAsync(context->scratch_activation, host_activation, in_bytes,
             cudaMemcpyHostToDevice, context->stream);
-    if (error == cudaSuccess) {
-        if (tensor)
-            error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
-                &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data,
-                weights->rows, weights->width, weights->row_stride, context->scratch_activation,
-                kActF32, tokens, context->scratch_output, nullptr,
-                reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
-                &context->launches);
-        else
-            error = enqueue_matmul_streaming(context, weights, context->scratch_activation,
-                kActF32, tokens, context->scratch_output);
-    }
+    if (error == cudaSuccess)
+        error = enqueue_matmul(context, weights, context->scratch_activation, kActF32, tokens,
+            context->scratch_output, nullptr);
     if (error == cudaSuccess)
         error = cudaMemcpyAsync(host_output, context->scratch_output, out_bytes,
             cudaMemcpyDeviceToHost, context->stream);
@@ -1781,26 +1900,52 @@ extern "C" int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *c
         output_elements < static_cast<size_t>(tokens) * weights->rows * weights->blocks)
         return FORTAI_CUDA_INVALID;
     cudaSetDevice(context->device);
-    cudaError_t error;
-    if (mmq_supported(weights->rows, weights->width, tokens, context->mmq_min_tokens)) {
-        error = mmq_enqueue(context->stream, context->sm_count, context->status_device,
-            &const_cast<fortai_cuda_q8_weights *>(weights)->mmq, weights->data, weights->rows,
-            weights->width, weights->row_stride, device_activation, kActQ8, tokens, nullptr,
-            static_cast<int32_t *>(device_output),
-            reinterpret_cast<void **>(&context->scratch_aux), &context->scratch_aux_bytes,
-            &context->launches);
-    } else {
-        error = cudaSuccess;
-        for (int t = 0; t < tokens && error == cudaSuccess; ++t) {
-            const GemvParams p = single_params(context, weights,
-                static_cast<const uint8_t *>(device_activation) +
-                    static_cast<size_t>(t) * weights->blocks * kBlockBytes,
-                reinterpret_cast<float *>(static_cast<int32_t *>(device_output) +
-                    static_cast<size_t>(t) * weights->rows * weights->blocks));
-            error = launch_gemv(context, p, kActQ8, kEpiBlockDots);
-        }
-    }
+    const cudaError_t error = enqueue_matmul(context, weights, device_activation, kActQ8, tokens,
+        nullptr, static_cast<int32_t *>(device_output));
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "matmul block dots", error);
+}
+
+// h[i] = silu(gate[i]) * up[i], in place over gate
+__global__ void __launch_bounds__(256)
+silu_product_kernel(float *__restrict__ gate, const float *__restrict__ up, long long count) {
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < count;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+        gate[i] = silu_mul(gate[i], up[i]);
+}
+
+extern "C" int fortai_cuda_q8_ffn_batch_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation, int tokens,
+    void *device_output, size_t output_elements) {
+    if (!owned(context, gate_weights) || !owned(context, up_weights) ||
+        !owned(context, down_weights) || !device_activation || !device_output || tokens <= 0)
+        return FORTAI_CUDA_INVALID;
+    // the shape rules of the single-token FFN
+    if (gate_weights->rows != up_weights->rows || gate_weights->blocks != up_weights->blocks ||
+        gate_weights->rows != down_weights->blocks * kBlockElems ||
+        output_elements < static_cast<size_t>(tokens) * down_weights->rows)
+        return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const size_t inner = static_cast<size_t>(tokens) * gate_weights->rows;
+    cudaError_t error = ensure_scratch(context, 0, 2 * inner * sizeof(float));
+    float *gate = context->scratch_output, *up = gate + inner;
+    if (error == cudaSuccess)
+        error = enqueue_matmul(context, gate_weights, device_activation, kActF32, tokens, gate,
+            nullptr);
+    if (error == cudaSuccess)
+        error = enqueue_matmul(context, up_weights, device_activation, kActF32, tokens, up, nullptr);
+    if (error == cudaSuccess) {
+        const int grid = static_cast<int>(std::min<size_t>((inner + 255) / 256,
+            static_cast<size_t>(context->sm_count) * 8));
+        silu_product_kernel<<<grid, 256, 0, context->stream>>>(gate, up,
+            static_cast<long long>(inner));
+        ++context->launches;
+        error = cudaGetLastError();
+    }
+    if (error == cudaSuccess)
+        error = enqueue_matmul(context, down_weights, gate, kActF32, tokens,
+            static_cast<float *>(device_output), nullptr);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "batched FFN", error);
 }
 
 // ---------------------------------------------------------------------------

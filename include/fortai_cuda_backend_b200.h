@@ -234,9 +234,11 @@ int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const float *host_activation,
     size_t activation_elements, float *host_output, size_t output_bytes, float *elapsed_ms);
 
-/* Batched product for multi-token prefill: `tokens` rows of `width` floats in,
- * tokens x rows floats out (token-major: out[t * rows + r]).  Each token row is
- * quantized to Q8_0 exactly as a single activation would be.  Enqueue only. */
+/* Batched product (batched decode, speculative decoding, prefill): `tokens` rows of
+ * `width` floats in, tokens x rows floats out (token-major: out[t * rows + r]).  Each
+ * token row is quantized to Q8_0 exactly as a single activation would be.  2..32 tokens
+ * stream the weights once through a warp-level int8 MMA kernel, more go to the tcgen05
+ * kernel; the reference runs one GEMV per token.  Enqueue only. */
 int fortai_cuda_q8_matmul_device_f32(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
     void *device_output, size_t output_elements);
@@ -253,6 +255,15 @@ int fortai_cuda_q8_matmul_host_f32(fortai_cuda_q8_context *context,
  * out[(t * rows + r) * blocks + b], taken from the tensor-core accumulators. */
 int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
+    void *device_output, size_t output_elements);
+
+/* FFN for `tokens` activations at once: out[t] = down . Q8(silu(gate . x[t]) * (up . x[t])),
+ * x and out token-major fp32 in device memory.  Same shape rules as
+ * fortai_cuda_q8_ffn_device (backend/cuda/fortai_cuda_backend.cu:1247-1296), which it
+ * equals token by token.  Enqueue only. */
+int fortai_cuda_q8_ffn_batch_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation, int tokens,
     void *device_output, size_t output_elements);
 
 /* Row-sharded GEMV whose epilogue stores this rank's slice into every rank's

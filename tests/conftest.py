@@ -119,3 +119,30 @@ def reference_gate(actual, expected):
     err = np.abs(actual.astype(np.float64) - expected.astype(np.float64))
     rel = err / np.maximum(1.0, np.abs(expected.astype(np.float64)))
     return float(err.max()) <= 2e-3 and float(rel.max()) <= 1e-4
+
+
+def ffn_error_beyond_quant_flips(actual, expected, oracle, gate, up, down, inner, hidden, x):
+    """Compare an FFN output with the oracle's, allowing for flipped quants of the hidden vector.
+
+    The FFN re-quantizes h = silu(gate.x) * (up.x) to Q8_0 between its halves.  A last-bit
+    difference in h (another summation order, the IEEE exponential instead of the reference's
+    polynomial) now and then moves one element across a rounding boundary of the quantizer.
+    One flipped quant i changes the output by exactly d_h[block(i)] * W_down[:, i], which is
+    far above the fp32 bound for small layers.  This helper finds the flips that explain the
+    difference (projection of the error on every such column), and returns
+    (number of flips, largest |flip|, max |error| left after removing them).
+    """
+    g, u = oracle.matvec_pair(gate, up, inner, hidden, x)[:2]
+    h = oracle.silu_product(g, u)
+    scales = oracle.quantize(h)[1]
+    rows = expected.size
+    raw = np.ascontiguousarray(down).view(np.uint8).reshape(rows, inner // 32, 34)
+    d = raw[:, :, :2].copy().view(np.float16).astype(np.float64).reshape(rows, inner // 32)
+    q = raw[:, :, 2:].view(np.int8).astype(np.float64)
+    columns = (q * d[:, :, None]).reshape(rows, inner) * np.repeat(scales.astype(np.float64), 32)
+    error = actual.astype(np.float64) - expected.astype(np.float64)
+    norms = (columns * columns).sum(axis=0)
+    projection = np.where(norms > 0, (columns.T @ error) / np.maximum(norms, 1e-300), 0.0)
+    flips = np.where(np.abs(projection) > 0.5, np.rint(projection), 0.0)
+    left = error - columns @ flips
+    return int(np.count_nonzero(flips)), float(np.abs(flips).max()), float(np.abs(left).max())
