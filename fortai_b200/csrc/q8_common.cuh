@@ -99,6 +99,85 @@ __device__ __forceinline__ int quantize_lane(float x, uint16_t *scale_bits) {
     return max(-128, min(127, q));
 }
 
+// ---- activation image of several tokens -----------------------------------------
+// quants[token][width] int8 and scales[block][padded_tokens] float for `padded_tokens`
+// rows (rows >= tokens are zero), from fp32 rows (ACT == 1: eight lanes per Q8_0 block,
+// one 16-byte load and one 32-bit store per lane, same arithmetic and bytes as
+// quantize_lane) or from GGUF Q8_0 rows (ACT == 0: one warp per block).  Called by all
+// threads of a 256-thread CTA of a 1-D grid.
+template <int ACT>
+__device__ __forceinline__ void prepare_token_image(const void *__restrict__ activation, int tokens,
+    int padded_tokens, int width, int8_t *__restrict__ quants, float *__restrict__ scales) {
+    const int blocks = width / kBlockElems;
+    if (ACT == 1) {
+        const float4 *x4 = static_cast<const float4 *>(activation);
+        uint32_t *q32 = reinterpret_cast<uint32_t *>(quants);
+        const int groups = width >> 2;                       // float4 per token, 8 per block
+        const long long total = static_cast<long long>(padded_tokens) * groups;
+        const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+        // warp-uniform trip count: the shuffles below need all 32 lanes
+        for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x; base < total;
+             base += stride) {
+            const long long at = base + threadIdx.x;
+            const bool valid = at < total;
+            const int token = valid ? static_cast<int>(at / groups) : 0;
+            const int g = valid ? static_cast<int>(at - static_cast<long long>(token) * groups) : 0;
+            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (valid && token < tokens) v = x4[static_cast<size_t>(token) * groups + g];
+            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            const float scale = __fdiv_rn(amax, 127.0f);
+            const float inverse = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+            const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v.x, inverse))));
+            const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v.y, inverse))));
+            const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v.z, inverse))));
+            const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v.w, inverse))));
+            if (valid) {
+                q32[static_cast<size_t>(token) * groups + g] = static_cast<uint32_t>(q0 & 0xff) |
+                    (static_cast<uint32_t>(q1 & 0xff) << 8) |
+                    (static_cast<uint32_t>(q2 & 0xff) << 16) |
+                    (static_cast<uint32_t>(q3 & 0xff) << 24);
+                if ((g & 7) == 0)
+                    scales[static_cast<size_t>(g >> 3) * padded_tokens + token] =
+                        half_bits_to_float(__half_as_ushort(__float2half_rn(scale)));
+            }
+        }
+    } else {
+        const int lane = threadIdx.x & 31;
+        const long long total = static_cast<long long>(padded_tokens) * blocks;
+        for (long long i = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); i < total;
+             i += static_cast<long long>(gridDim.x) * 8) {
+            const int token = static_cast<int>(i / blocks);
+            const int b = static_cast<int>(i - static_cast<long long>(token) * blocks);
+            int q = 0;
+            float scale = 0.0f;
+            if (token < tokens) {
+                const uint8_t *block = static_cast<const uint8_t *>(activation) +
+                    (static_cast<size_t>(token) * blocks + b) * kBlockBytes;
+                q = static_cast<int8_t>(block[2 + lane]);
+                scale = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
+            }
+            quants[static_cast<size_t>(token) * width + b * kBlockElems + lane] =
+                static_cast<int8_t>(q);
+            if (lane == 0) scales[static_cast<size_t>(b) * padded_tokens + token] = scale;
+        }
+    }
+}
+
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched with programmatic stream serialization may start while its
+// predecessor in the stream still runs; it calls grid_dependency_wait() before it touches
+// anything the predecessor writes, and the predecessor calls grid_dependents_may_launch()
+// as early as it likes.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void grid_dependency_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependents_may_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---- mbarrier / bulk-copy primitives (sm_90+; used without clusters) -------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -111,50 +111,15 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
-// Programmatic dependent launch: the product kernel is allowed to start while the prepare
-// kernel still runs (its weight requests do not depend on it) and waits here before it
-// touches anything the prepare kernel writes.  Both are no-ops for a plain launch.
-__device__ __forceinline__ void grid_dependency_wait() {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-}
-__device__ __forceinline__ void grid_dependents_may_launch() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-}
-
-// Activation image of a few tokens (one warp per Q8_0 block: fp32 -> quants + scale, or
-// GGUF block -> quants + scale) and the zeroing of the output the product kernel adds into.
+// Activation image of a few tokens and the zeroing of the output the product kernel adds
+// into.
 template <int ACT>
 __global__ void __launch_bounds__(256)
 fewtok_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_tokens, int width,
     int8_t *__restrict__ quants, float *__restrict__ scales, float4 *__restrict__ zero,
     long long zero_count) {
     grid_dependents_may_launch();
-    const int blocks = width / kBlockElems;
-    const int lane = threadIdx.x & 31;
-    const long long total = static_cast<long long>(padded_tokens) * blocks;
-    for (long long i = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); i < total;
-         i += static_cast<long long>(gridDim.x) * 8) {
-        const int token = static_cast<int>(i / blocks);
-        const int b = static_cast<int>(i - static_cast<long long>(token) * blocks);
-        int q = 0;
-        float scale = 0.0f;
-        if (token < tokens) {
-            if (ACT == 1) {
-                const float *x = static_cast<const float *>(activation);
-                uint16_t bits;
-                q = quantize_lane(x[static_cast<size_t>(token) * width + b * kBlockElems + lane],
-                    &bits);
-                scale = half_bits_to_float(bits);
-            } else {
-                const uint8_t *block = static_cast<const uint8_t *>(activation) +
-                    (static_cast<size_t>(token) * blocks + b) * kBlockBytes;
-                q = static_cast<int8_t>(block[2 + lane]);
-                scale = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
-            }
-        }
-        quants[static_cast<size_t>(token) * width + b * kBlockElems + lane] = static_cast<int8_t>(q);
-        if (lane == 0) scales[static_cast<size_t>(b) * padded_tokens + token] = scale;
-    }
+    prepare_token_image<ACT>(activation, tokens, padded_tokens, width, quants, scales);
     for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_count;
          i += static_cast<long long>(gridDim.x) * blockDim.x)
         zero[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);

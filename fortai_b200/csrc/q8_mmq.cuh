@@ -71,39 +71,6 @@ inline bool mmq_supported(int rows, int width, int tokens, int min_tokens) {
     return tokens >= threshold && width % (kMmqStageBlocks * kBlockElems) == 0 && rows >= 1;
 }
 
-// One warp per Q8_0 block of the activation: fp32 -> (quants, scale) or
-// GGUF block -> (quants, scale), into the planar image.
-template <int ACT>
-__global__ void __launch_bounds__(256)
-mmq_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_tokens, int width,
-    int8_t *__restrict__ quants, float *__restrict__ scales) {
-    const int blocks = width / kBlockElems;
-    const int lane = threadIdx.x & 31;
-    const long long total = static_cast<long long>(padded_tokens) * blocks;
-    for (long long i = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); i < total;
-         i += static_cast<long long>(gridDim.x) * 8) {
-        const int t = static_cast<int>(i / blocks);
-        const int b = static_cast<int>(i - static_cast<long long>(t) * blocks);
-        int q = 0;
-        float scale = 0.0f;
-        if (t < tokens) {
-            if (ACT == 1) {
-                const float *x = static_cast<const float *>(activation);
-                uint16_t bits;
-                q = quantize_lane(x[static_cast<size_t>(t) * width + b * kBlockElems + lane], &bits);
-                scale = half_bits_to_float(bits);
-            } else {
-                const uint8_t *block = static_cast<const uint8_t *>(activation) +
-                    (static_cast<size_t>(t) * blocks + b) * kBlockBytes;
-                q = static_cast<int8_t>(block[2 + lane]);
-                scale = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
-            }
-        }
-        quants[static_cast<size_t>(t) * width + b * kBlockElems + lane] = static_cast<int8_t>(q);
-        if (lane == 0) scales[static_cast<size_t>(b) * padded_tokens + t] = scale;
-    }
-}
-
 // ---- tcgen05 / TMA wrappers ---------------------------------------------------
 __device__ __forceinline__ void tma_load_2d(void *smem_dst, const CUtensorMap *map, int x, int y,
     uint64_t *bar) {
@@ -135,6 +102,10 @@ __device__ __forceinline__ void tc_fence_after() {
 }
 
 // D(tmem) = A(smem) * B(smem)^T, int8 x int8 -> int32, fresh accumulator.
+// (Tried and dropped: keeping the bias 0x4B400000 in every accumulator so that the int32
+// result is already the float 12582912 + dot and the convert becomes one exact packed
+// subtraction.  Restoring the bias with tcgen05.st after every drain lengthened the time a
+// buffer is held and the kernel went from 93 us to 113 us at M = 512.)
 __device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
     uint32_t idesc) {
     asm volatile(
@@ -275,6 +246,7 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
     return r;
 }
 
+// 18 warps are allocated registers like 20 (groups of four), so 96 per thread is the cap.
 template <bool DOTS>
 __global__ void __launch_bounds__(kMmqThreads, 1)
 q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
@@ -319,6 +291,9 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
+    // everything above may run under the prepare kernel; the activation image, its scales
+    // and the zeroed split tiles are that kernel's output
+    grid_dependency_wait();
 
     if (warp == 0) {
         // ------------------------------ TMA producer ------------------------------
@@ -558,13 +533,19 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
     }
 }
 
-// Zeroes the output of every split tile (their pieces arrive as atomic adds).
+// Before the product: the planar activation image, and zeros in the output of every
+// split tile (their pieces arrive as atomic adds).
+template <int ACT>
 __global__ void __launch_bounds__(256)
-mmq_zero_split_kernel(float *__restrict__ output, int rows, int tokens, int tiles_n, int tiles,
-    int stages_per_tile, int grid) {
+mmq_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_tokens, int width,
+    int8_t *__restrict__ quants, float *__restrict__ scales, float *__restrict__ output, int rows,
+    int tiles_n, int tiles, int stages_per_tile, int product_grid) {
+    grid_dependents_may_launch();
+    prepare_token_image<ACT>(activation, tokens, padded_tokens, width, quants, scales);
+    if (!output) return;
     const long long total_units = static_cast<long long>(tiles) * stages_per_tile;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        if (!mmq_tile_is_split(total_units, grid, stages_per_tile, tile)) continue;
+        if (!mmq_tile_is_split(total_units, product_grid, stages_per_tile, tile)) continue;
         const int row0 = (tile % tiles_n) * kMmqTileRows;
         const int token0 = (tile / tiles_n) * kMmqTileTokens;
         for (int i = threadIdx.x; i < kMmqTileRows * kMmqTileTokens; i += blockDim.x) {
@@ -659,19 +640,6 @@ inline cudaError_t mmq_enqueue(cudaStream_t stream, int sm_count, int *status,
     if (!mmq_make_map(&act_map, quants, padded, width, width)) return cudaErrorNotSupported;
     if (!mmq_make_scale_map(&scale_map, scales, blocks, padded)) return cudaErrorNotSupported;
 
-    const long long prep_warps = static_cast<long long>(padded) * blocks;
-    const int prep_grid = static_cast<int>(std::max<long long>(1,
-        std::min<long long>((prep_warps + 7) / 8, static_cast<long long>(sm_count) * 16)));
-    if (act == 1)
-        mmq_prepare_kernel<1><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
-            quants, scales);
-    else
-        mmq_prepare_kernel<0><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
-            quants, scales);
-    ++*launches;
-    error = cudaGetLastError();
-    if (error != cudaSuccess) return error;
-
     MmqParams p = {};
     p.weights = weights;
     p.rows = rows;
@@ -689,26 +657,46 @@ inline cudaError_t mmq_enqueue(cudaStream_t stream, int sm_count, int *status,
     const size_t smem = mmq_smem_bytes();
     const long long total_units = static_cast<long long>(p.tiles) * p.stages_per_tile;
     const int grid = static_cast<int>(std::min<long long>(sm_count, total_units));
-    if (output) {
-        mmq_zero_split_kernel<<<std::min(p.tiles, sm_count * 4), 256, 0, stream>>>(output, rows,
-            tokens, p.tiles_n, p.tiles, p.stages_per_tile, grid);
+    {
+        const long long work = act == 1 ? static_cast<long long>(padded) * (width / 4) / 256
+                                        : static_cast<long long>(padded) * blocks / 8;
+        const int prep_grid = static_cast<int>(std::max<long long>(1,
+            std::min<long long>(work + 1, static_cast<long long>(sm_count) * 8)));
+        if (act == 1)
+            mmq_prepare_kernel<1><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
+                quants, scales, output, rows, p.tiles_n, p.tiles, p.stages_per_tile, grid);
+        else
+            mmq_prepare_kernel<0><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
+                quants, scales, output, rows, p.tiles_n, p.tiles, p.stages_per_tile, grid);
         ++*launches;
         error = cudaGetLastError();
         if (error != cudaSuccess) return error;
     }
+    // the product kernel may start (barriers, TMEM, descriptors) under the prepare kernel
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(kMmqThreads);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute overlap = {};
+    overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    overlap.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &overlap;
+    config.numAttrs = 1;
     if (block_dots) {
         error = cudaFuncSetAttribute(q8_mmq_kernel<true>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (error != cudaSuccess) return error;
-        q8_mmq_kernel<true><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map,
+        error = cudaLaunchKernelEx(&config, q8_mmq_kernel<true>, plan->weights_map, act_map,
             scale_map, p);
     } else {
         error = cudaFuncSetAttribute(q8_mmq_kernel<false>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (error != cudaSuccess) return error;
-        q8_mmq_kernel<false><<<grid, kMmqThreads, smem, stream>>>(plan->weights_map, act_map,
+        error = cudaLaunchKernelEx(&config, q8_mmq_kernel<false>, plan->weights_map, act_map,
             scale_map, p);
     }
+    if (error != cudaSuccess) return error;
     ++*launches;
     return cudaGetLastError();
 }
