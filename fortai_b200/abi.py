@@ -6,7 +6,8 @@ built or loaded this module raises: the package never computes on the CPU.
 from __future__ import annotations
 
 import ctypes
-from ctypes import POINTER, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint64, c_void_p
+from ctypes import (POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64,
+                    c_void_p)
 
 from . import build as _build
 
@@ -90,6 +91,33 @@ SIGNATURES = {
 
 REFERENCE_SYMBOLS = [name for name in SIGNATURES][:35]
 
+# include/fortai_gguf_b200.h
+_I64P = POINTER(c_int64)
+GGUF_SIGNATURES = {
+    "fortai_gguf_open": (c_int, [c_char_p, _PP, c_char_p, c_size_t]),
+    "fortai_gguf_close": (None, [_P]),
+    "fortai_gguf_version": (c_int32, [_P]),
+    "fortai_gguf_tensor_count": (c_int64, [_P]),
+    "fortai_gguf_metadata_count": (c_int64, [_P]),
+    "fortai_gguf_alignment": (c_int64, [_P]),
+    "fortai_gguf_data_start": (c_int64, [_P]),
+    "fortai_gguf_find_meta": (c_int64, [_P, c_char_p]),
+    "fortai_gguf_find_tensor": (c_int64, [_P, c_char_p]),
+    "fortai_gguf_meta_key": (c_char_p, [_P, c_int64]),
+    "fortai_gguf_meta_type": (c_int32, [_P, c_int64]),
+    "fortai_gguf_meta_int": (c_int64, [_P, c_char_p, c_int64]),
+    "fortai_gguf_meta_real": (c_float, [_P, c_char_p, c_float]),
+    "fortai_gguf_meta_string": (c_void_p, [_P, c_char_p, _I64P]),
+    "fortai_gguf_meta_bool": (c_int, [_P, c_char_p, c_int]),
+    "fortai_gguf_meta_int_array": (c_int64, [_P, c_char_p, _I64P, c_int64]),
+    "fortai_gguf_tensor_info": (c_int, [_P, c_int64, POINTER(c_char_p), POINTER(c_int32),
+                                        POINTER(c_int32), _I64P, _I64P, _I64P]),
+    "fortai_gguf_tensor_data": (c_void_p, [_P, c_int64]),
+    "fortai_gguf_tensor_value": (c_float, [_P, c_int64, c_int64]),
+    "fortai_gguf_tensor_get_row": (c_int, [_P, c_int64, c_int64, _F, c_int64]),
+    "fortai_gguf_upload_q8": (c_int, [_P, c_int64, _P, c_int64, c_int64, _PP]),
+}
+
 _LIB = None
 
 
@@ -104,7 +132,7 @@ def load() -> ctypes.CDLL:
         return _LIB
     path = _build.build()
     lib = ctypes.CDLL(path)
-    for name, (restype, argtypes) in SIGNATURES.items():
+    for name, (restype, argtypes) in {**SIGNATURES, **GGUF_SIGNATURES}.items():
         fn = getattr(lib, name)      # AttributeError if the symbol is not exported
         fn.restype = restype
         fn.argtypes = argtypes

@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libfortai_cuda_b200.so")
-SOURCES = ["backend_abi.cu"]
+SOURCES = ["backend_abi.cu", "gguf_reader.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -27,7 +27,7 @@ def _newest_source_mtime() -> float:
     newest = 0.0
     for root in (CSRC, os.path.join(HERE, "..", "include")):
         for name in os.listdir(root):
-            if name.endswith((".cu", ".cuh", ".h")):
+            if name.endswith((".cu", ".cuh", ".h", ".cpp")):
                 newest = max(newest, os.path.getmtime(os.path.join(root, name)))
     return newest
 

@@ -477,15 +477,16 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                     const float dw = half_bits_to_float(
                         static_cast<uint16_t>((j & 1) ? (word >> 16) : (word & 0xffffu)));
                     const unsigned long long dw2 = pack2(dw, dw);
-                    const float4 *da = reinterpret_cast<const float4 *>(da_stage +
+                    // four activation scales per 16-byte load, read as two packed pairs
+                    const ulonglong2 *da = reinterpret_cast<const ulonglong2 *>(da_stage +
                         j * kMmqTileTokens + col0);
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        const float4 a = da[q];
-                        acc[2 * q] = fma2(cvt2(v[4 * q], v[4 * q + 1]),
-                            mul2(dw2, pack2(a.x, a.y)), acc[2 * q]);
-                        acc[2 * q + 1] = fma2(cvt2(v[4 * q + 2], v[4 * q + 3]),
-                            mul2(dw2, pack2(a.z, a.w)), acc[2 * q + 1]);
+                        const ulonglong2 a = da[q];
+                        acc[2 * q] = fma2(cvt2(v[4 * q], v[4 * q + 1]), mul2(dw2, a.x),
+                            acc[2 * q]);
+                        acc[2 * q + 1] = fma2(cvt2(v[4 * q + 2], v[4 * q + 3]), mul2(dw2, a.y),
+                            acc[2 * q + 1]);
                     }
                     if (DOTS && row_ok) {
                         const int kb = st * kMmqStageBlocks + j;

@@ -16,13 +16,21 @@ def header_symbols():
     return sorted(set(re.findall(r"\b(fortai_cuda_\w+)\s*\(", text)))
 
 
+def gguf_header_symbols():
+    text = open(os.path.join(ROOT, "include", "fortai_gguf_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fortai_gguf_\w+)\s*\(", text)))
+
+
 def test_library_builds_and_exports_every_declared_symbol():
     from fortai_b200 import abi
     lib = abi.load()
     names = header_symbols()
     assert len(names) >= 35
     assert set(names) == set(abi.SIGNATURES)
-    for name in names:
+    gguf_names = gguf_header_symbols()
+    assert set(gguf_names) == set(abi.GGUF_SIGNATURES)
+    for name in names + gguf_names:
         assert getattr(lib, name) is not None
 
 
