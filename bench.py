@@ -753,6 +753,61 @@ def run_sweep(args):
     return 0
 
 
+def run_decode(args):
+    """Whole decode steps through the device pipeline of the model object (embedding, layer
+    objects, FFN, lm_head: every call of one token of the reference's fortai_cuda_run), with
+    random-init weights of a Qwen3.5-like shape.  Tokens per second, eager launches and CUDA
+    graph replay; an auxiliary number, not the headline metric."""
+    import torch
+    from fortai_b200 import backend_cuda as backend
+    from fortai_b200.qwen35_device import qwen35_device_model_t, synthetic_model
+    helper = backend.cuda_q8_context_t()
+    if not helper.create(0).is_ok():
+        raise SystemExit("context creation failed")
+    shapes = {"0.8B-like": dict(hidden=1024, inner=3840, layer_count=24),
+              "2B-like": dict(hidden=2048, inner=7680, layer_count=24),
+              "4B-like": dict(hidden=2560, inner=9728, layer_count=32)}
+    for label, shape in shapes.items():
+        if args.only and args.only not in label:
+            continue
+        spec = synthetic_model(
+            lambda rows, width, seed, sigma: make_device_weights(torch, backend, helper, 0, rows,
+                                                                 width, seed),
+            vocabulary=151936, max_context=256, **shape)
+        weight_bytes = sum(v.size for v in [spec["output"]] +
+                           [l[k] for l in spec["layers"] for k in ("ffn_gate", "ffn_up", "ffn_down")] +
+                           [v for l in spec["layers"] for v in l["mixer"].values()
+                            if isinstance(v, np.ndarray) and v.dtype == np.int8])
+        result = {"shape": label, **shape, "vocabulary": 151936,
+                  "weight_bytes_per_token": int(weight_bytes)}
+        for mode in ("eager", "graph"):
+            model = qwen35_device_model_t()
+            stat = model.open(spec, cuda_graph=(mode == "graph"))
+            if not stat.is_ok():
+                raise SystemExit(f"model setup failed: {stat}")
+            apply_options(model.cuda, args.options)
+            token, steps = 1, max(8, min(args.steps, 200))
+            for position in range(4):                       # warm-up (and graph capture)
+                logits, stat = model.forward(token, position)
+                assert stat.is_ok(), stat
+                token = int(np.argmax(logits))
+            before = model.cuda.launch_count()
+            t0 = time.perf_counter()
+            for position in range(4, 4 + steps):
+                logits, stat = model.forward(token, position)
+                token = int(np.argmax(logits))
+            seconds = time.perf_counter() - t0
+            result[mode + "_tokens_per_s"] = steps / seconds
+            result[mode + "_ms_per_token"] = seconds / steps * 1e3
+            result[mode + "_weight_gbs"] = weight_bytes * steps / seconds / 1e9
+            if mode == "eager":
+                result["launches_per_token"] = (model.cuda.launch_count() - before) // steps
+            model.close()
+        print(json.dumps(result), flush=True)
+    helper.destroy()
+    return 0
+
+
 def ctx_cleanup(weights, ctx, dist):
     weights.destroy()
     ctx.destroy()
@@ -780,6 +835,8 @@ def main():
     parser.add_argument("--only", default="", help="--sweep: only shapes whose label contains this")
     parser.add_argument("--sweep", action="store_true",
                         help="time every named batch-1 shape and the fused FFN (one JSON line each)")
+    parser.add_argument("--decode", action="store_true",
+                        help="whole decode steps of a random-init Qwen3.5-like model (tokens/s)")
     parser.add_argument("--kernel-only", action="store_true",
                         help="skip the e2e, prefill and CPU legs (profiler captures)")
     args = parser.parse_args()
@@ -790,6 +847,8 @@ def main():
         return run_mmq_only(args)
     if args.sweep:
         return run_sweep(args)
+    if args.decode:
+        return run_decode(args)
     return run_gpu_arm(args)
 
 
