@@ -780,9 +780,10 @@ def run_decode(args):
                             if isinstance(v, np.ndarray) and v.dtype == np.int8])
         result = {"shape": label, **shape, "vocabulary": 151936,
                   "weight_bytes_per_token": int(weight_bytes)}
-        for mode in ("eager", "graph"):
+        for mode in ("eager", "graph", "fused_eager", "fused_graph"):
             model = qwen35_device_model_t()
-            stat = model.open(spec, cuda_graph=(mode == "graph"))
+            stat = model.open(spec, cuda_graph=mode.endswith("graph"),
+                              fused=mode.startswith("fused"))
             if not stat.is_ok():
                 raise SystemExit(f"model setup failed: {stat}")
             apply_options(model.cuda, args.options)
@@ -800,8 +801,9 @@ def run_decode(args):
             result[mode + "_tokens_per_s"] = steps / seconds
             result[mode + "_ms_per_token"] = seconds / steps * 1e3
             result[mode + "_weight_gbs"] = weight_bytes * steps / seconds / 1e9
-            if mode == "eager":
-                result["launches_per_token"] = (model.cuda.launch_count() - before) // steps
+            if mode.endswith("eager"):
+                result[mode.replace("eager", "launches_per_token")] = \
+                    (model.cuda.launch_count() - before) // steps
             model.close()
         print(json.dumps(result), flush=True)
     helper.destroy()

@@ -87,6 +87,11 @@ SIGNATURES = {
                                                            c_int, c_size_t, c_size_t]),
     "fortai_cuda_q8_ffn_device_noalloc": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_size_t]),
     "fortai_cuda_q8_ffn_batch_device": (c_int, [_P, _P, _P, _P, _P, c_int, _P, c_size_t]),
+    "fortai_cuda_qwen35_recurrent_step_device": (c_int, [_P, _P, c_size_t, _P, c_float]),
+    "fortai_cuda_qwen35_attention_step_device": (c_int, [_P, _P, c_size_t, c_int, _P, c_float]),
+    "fortai_cuda_q8_ffn_step_device": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_float]),
+    "fortai_cuda_q8_matvec_norm_device_f32": (c_int, [_P, _P, _P, c_size_t, _P, c_float, _P,
+                                                      c_size_t]),
 }
 
 REFERENCE_SYMBOLS = [name for name in SIGNATURES][:35]

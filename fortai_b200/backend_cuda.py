@@ -598,6 +598,38 @@ def cuda_q8_ffn_batch_device(context, gate_weights, up_weights, down_weights, de
     return stat
 
 
+def cuda_q8_ffn_step_device(context, gate_weights, up_weights, down_weights, device_x, elements,
+                            device_norm_weights, epsilon) -> status_t:
+    """Extension: x <- x + FFN(rms_norm(x) * norm_weights), in place on the residual stream."""
+    stat = status_t()
+    if (not context.handle or not gate_weights.handle or not up_weights.handle
+            or not down_weights.handle or not device_x or not device_norm_weights):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 FFN step")
+        return stat
+    code = _lib().fortai_cuda_q8_ffn_step_device(context.handle, gate_weights.handle,
+                                                 up_weights.handle, down_weights.handle, device_x,
+                                                 elements, device_norm_weights, c_float(epsilon))
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 FFN step failed")
+    return stat
+
+
+def cuda_q8_matvec_norm_device_f32(context, weights, device_x, elements, device_norm_weights,
+                                   epsilon, device_output, output_elements) -> status_t:
+    """Extension: output = weights . Q8(rms_norm(x) * norm_weights) in one launch."""
+    stat = status_t()
+    if not context.handle or not weights.handle or not device_x or not device_output:
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 normalised matvec")
+        return stat
+    code = _lib().fortai_cuda_q8_matvec_norm_device_f32(context.handle, weights.handle, device_x,
+                                                        elements, device_norm_weights,
+                                                        c_float(epsilon), device_output,
+                                                        output_elements)
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 normalised matvec failed")
+    return stat
+
+
 def cuda_q8_matvec_device_f32_peers(context, weights, device_activation, activation_elements,
                                     peer_outputs, first_row, output_elements) -> status_t:
     stat = status_t()
@@ -704,6 +736,26 @@ class cuda_qwen35_recurrent_t:
         return stat
 
 
+def _step(self, call, message, *args) -> status_t:
+    stat = status_t()
+    if not self.handle or not args[0]:
+        stat.set(FORTAI_INVALID, "invalid " + message)
+        return stat
+    if call(self.handle, *args) != FORTAI_CUDA_OK:
+        return _failed(stat, self.context, message + " failed")
+    return stat
+
+
+def _recurrent_step_device(self, device_x, elements, device_norm_weights, epsilon) -> status_t:
+    """Extension: x <- x + layer(rms_norm(x) * norm_weights), in place."""
+    return _step(self, _lib().fortai_cuda_qwen35_recurrent_step_device,
+                 "CUDA Qwen recurrent step", device_x, elements, device_norm_weights,
+                 c_float(epsilon))
+
+
+cuda_qwen35_recurrent_t.step_device = _recurrent_step_device
+
+
 class cuda_qwen35_attention_t:
     """fortai_backend_cuda.f90:45-52 (gated attention layer; binary16 KV cache on the device)."""
 
@@ -758,3 +810,14 @@ class cuda_qwen35_attention_t:
         if code != FORTAI_CUDA_OK:
             return _failed(stat, self.context, "CUDA Qwen attention device run failed")
         return stat
+
+
+def _attention_step_device(self, device_x, elements, position, device_norm_weights,
+                           epsilon) -> status_t:
+    """Extension: x <- x + layer(rms_norm(x) * norm_weights), in place."""
+    return _step(self, _lib().fortai_cuda_qwen35_attention_step_device,
+                 "CUDA Qwen attention step", device_x, elements, int(position),
+                 device_norm_weights, c_float(epsilon))
+
+
+cuda_qwen35_attention_t.step_device = _attention_step_device

@@ -59,6 +59,7 @@ struct fortai_cuda_q8_context {
     int fewtok_threads = 0;    // its CTA size (0 = 256)
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
     int fewtok_step = 0;       // bytes of a row per step (0 = chosen from the shape)
+    int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
     int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
     int fewtok_off = 0;        // 1 = small batches run one GEMV per token
     char error[256] = {};
@@ -166,6 +167,27 @@ cudaError_t ensure_scratch(fortai_cuda_q8_context *c, size_t activation_bytes,
 // ---------------------------------------------------------------------------
 // GEMV launch policy
 // ---------------------------------------------------------------------------
+// A GEMV may start while its predecessor in the stream drains (programmatic stream
+// serialization): the kernel waits by itself before it reads anything but weights.  Kept
+// off for the multi-GPU epilogues, whose peers know nothing of this stream's order.
+template <typename Kernel>
+cudaError_t launch_gemv_kernel(fortai_cuda_q8_context *c, Kernel kernel, int grid, int threads,
+    size_t smem, const GemvParams &p) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(threads);
+    config.dynamicSmemBytes = smem;
+    config.stream = c->stream;
+    cudaLaunchAttribute overlap = {};
+    overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    overlap.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &overlap;
+    config.numAttrs = c->gemv_overlap && p.peers == 0 && p.sequence == 0 ? 1 : 0;
+    const cudaError_t error = cudaLaunchKernelEx(&config, kernel, p);
+    ++c->launches;
+    return error != cudaSuccess ? error : cudaGetLastError();
+}
+
 template <int U, int NR, int ACT, int EPI>
 cudaError_t launch_direct_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
     auto kernel = q8_gemv_direct_kernel<U, NR, ACT, EPI>;
@@ -195,9 +217,7 @@ cudaError_t launch_direct_instance(fortai_cuda_q8_context *c, const GemvParams &
     const int rows_per_cta = kGemvWarps * (EPI == kEpiSiluPair ? 1 : NR);
     const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
     const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
-    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
-    ++c->launches;
-    return cudaGetLastError();
+    return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem, p);
 }
 
 template <int ACT, int EPI>
@@ -270,13 +290,9 @@ cudaError_t launch_pipelined_depth(fortai_cuda_q8_context *c, const GemvParams &
                 static_cast<int>(smem + staged));
             if (error != cudaSuccess) return error;
         }
-        kernel<<<grid, kGemvThreads, smem + staged, c->stream>>>(p);
-        ++c->launches;
-        return cudaGetLastError();
+        return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem + staged, p);
     }
-    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
-    ++c->launches;
-    return cudaGetLastError();
+    return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem, p);
 }
 
 template <int CPL, int ACT, int EPI>
@@ -443,6 +459,17 @@ bool want_ring(const fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
 
 template <int ACT>
 cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
+    if (p.norm_weights || p.residual) {
+        // the fused norm / residual live in the pipelined and the half-block kernel only
+        cudaError_t error = cudaSuccess;
+        if (epi == kEpiSiluPair) {
+            if (launch_pipelined<ACT, kEpiSiluPair>(c, p, &error)) return error;
+            return launch_direct<ACT, kEpiSiluPair>(c, p);
+        }
+        if (epi != kEpiPlain) return cudaErrorNotSupported;
+        if (launch_pipelined<ACT, kEpiPlain>(c, p, &error)) return error;
+        return launch_direct<ACT, kEpiPlain>(c, p);
+    }
     RingConfig cfg;
     const bool ring = want_ring(c, p, epi) && ring_plan(c, p, epi, &cfg);
     // automatic: the pipelined kernel where the shape allows, else the half-block kernel
@@ -507,7 +534,9 @@ cudaError_t launch_planar_prepare(fortai_cuda_q8_context *c, const void *activat
 // Long activation vectors are quantized / unpacked once into the context's prepared image
 // instead of in every CTA's prologue (K = 17408 is 68 KB of fp32 per CTA otherwise).
 cudaError_t launch_gemv(fortai_cuda_q8_context *c, const GemvParams &p, int act, int epi) {
-    if (act == kActPlanar || epi == kEpiBlockDots || p.width < c->planar_min_width)
+    // (a fused norm is computed in the GEMV prologue, not by the preparation pass)
+    if (act == kActPlanar || epi == kEpiBlockDots || p.width < c->planar_min_width ||
+        p.norm_weights)
         return launch_gemv_raw(c, p, act, epi);
     const uintptr_t address = reinterpret_cast<uintptr_t>(p.activation);
     if ((act == kActF32 && (address & 3)) || (act == kActQ8 && (address & 1)))
@@ -720,13 +749,24 @@ bool ffn_shapes_ok(const fortai_cuda_q8_context *c, const fortai_cuda_q8_weights
 
 // quantize(x) is folded into the gate/up kernel when x is fp32; then
 // h = silu(gate.x) * (up.x) -> scratch_output, Q8(h) -> scratch_activation, down.
+// The caller's glue around a projection chain, fused into its first and last GEMV:
+// the input is RMS-normalised with `norm_weights` in the first prologue, and the last
+// epilogue adds `residual` (which may be the output vector itself).  All null = plain.
+struct Glue {
+    const float *norm_weights = nullptr;
+    float epsilon = 0.0f;
+    const float *residual = nullptr;
+};
+
 cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *gate,
     const fortai_cuda_q8_weights *up, const fortai_cuda_q8_weights *down, const void *activation,
-    int act, float *output) {
+    int act, float *output, const Glue &glue = Glue()) {
     GemvParams p = single_params(c, gate, activation, c->scratch_output);
     p.weights[1] = up->data;
     p.rows[1] = up->rows;
     p.segments = 2;
+    p.norm_weights = glue.norm_weights;
+    p.norm_epsilon = glue.epsilon;
     // size the prepared-image scratch for both halves before anything is enqueued, so that
     // it is never reallocated between the two GEMVs
     const int widest = std::max(gate->width, down->width);
@@ -745,6 +785,7 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
                 down->blocks, c->scratch_planar);
         if (error == cudaSuccess) {
             GemvParams d = single_params(c, down, c->scratch_planar, output);
+            d.residual = glue.residual;
             error = launch_gemv_raw(c, d, kActPlanar, kEpiPlain);
         }
         return error;
@@ -753,6 +794,7 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
         static_cast<size_t>(down->blocks));
     if (error == cudaSuccess) {
         GemvParams d = single_params(c, down, c->scratch_activation, output);
+        d.residual = glue.residual;
         error = launch_gemv(c, d, kActQ8, kEpiPlain);
     }
     return error;
@@ -1178,7 +1220,7 @@ cudaError_t clear_recurrent_state(fortai_cuda_qwen35_recurrent *layer) {
 // convolution, the normalisations, the state update and the output projection
 // (whose prologue quantizes the fp32 layer output, so no scratch is touched).
 cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *activation,
-    int act, float *output) {
+    int act, float *output, const Glue &glue = Glue()) {
     fortai_cuda_q8_context *c = layer->context;
     float *qkv = layer->projections;
     float *gate = qkv + layer->conv_size;
@@ -1195,6 +1237,8 @@ cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *a
         p.total_rows += mats[i]->rows;
     }
     p.segments = 4;
+    p.norm_weights = glue.norm_weights;
+    p.norm_epsilon = glue.epsilon;
     cudaError_t error = launch_gemv(c, p, act, kEpiPlain);
     if (error != cudaSuccess) return error;
     gdn_conv_silu_kernel<<<(layer->conv_size + 255) / 256, 256, 0, c->stream>>>(qkv,
@@ -1208,7 +1252,8 @@ cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *a
     c->launches += 3;
     error = cudaGetLastError();
     if (error != cudaSuccess) return error;
-    const GemvParams o = single_params(c, layer->out, layer->gdn_output, output);
+    GemvParams o = single_params(c, layer->out, layer->gdn_output, output);
+    o.residual = glue.residual;
     return launch_gemv(c, o, kActF32, kEpiPlain);
 }
 
@@ -1467,9 +1512,11 @@ extern "C" int fortai_cuda_qwen35_attention_reset(fortai_cuda_qwen35_attention *
 
 // The position used by the kernels is the context's device-side position word
 // (fortai_cuda_q8_context_set_position), as in the reference; `position` only bounds it.
-extern "C" int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attention *layer,
-    const void *device_activation, size_t activation_elements, int position,
-    void *device_output, size_t output_elements) {
+namespace {
+
+int attention_run(fortai_cuda_qwen35_attention *layer, const void *device_activation,
+    size_t activation_elements, int position, void *device_output, size_t output_elements,
+    const Glue &glue) {
     if (!layer || !layer->context || !device_activation || !device_output || position < 0 ||
         position >= layer->max_context) return FORTAI_CUDA_INVALID;
     fortai_cuda_q8_context *c = layer->context;
@@ -1490,6 +1537,8 @@ extern "C" int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attent
     p.rows[2] = layer->v->rows;
     p.segments = 3;
     p.total_rows = layer->q->rows + layer->k->rows + layer->v->rows;
+    p.norm_weights = glue.norm_weights;
+    p.norm_epsilon = glue.epsilon;
     cudaError_t error = launch_gemv(c, p, kActF32, kEpiPlain);
     if (error == cudaSuccess) {
         attention_prepare_kernel<<<layer->heads + layer->kv_heads, 256, 0, c->stream>>>(query, key,
@@ -1508,12 +1557,22 @@ extern "C" int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attent
         if (error == cudaSuccess) error = cudaGetLastError();
     }
     if (error == cudaSuccess) {
-        const GemvParams o = single_params(c, layer->out, layer->attention,
+        GemvParams o = single_params(c, layer->out, layer->attention,
             static_cast<float *>(device_output));
+        o.residual = glue.residual;
         error = launch_gemv(c, o, kActF32, kEpiPlain);
     }
     return error == cudaSuccess ? FORTAI_CUDA_OK
                                 : fail(c, "Qwen attention device run", error);
+}
+
+}  // namespace
+
+extern "C" int fortai_cuda_qwen35_attention_run_device(fortai_cuda_qwen35_attention *layer,
+    const void *device_activation, size_t activation_elements, int position,
+    void *device_output, size_t output_elements) {
+    return attention_run(layer, device_activation, activation_elements, position, device_output,
+        output_elements, Glue());
 }
 
 extern "C" const char *fortai_cuda_q8_last_error(const fortai_cuda_q8_context *context) {
@@ -1563,6 +1622,7 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->fewtok_step = value;
     else if (!std::strcmp(name, "fewtok_stages") && (value == 0 || value == 2 || value == 3))
         context->fewtok_stages = value;
+    else if (!std::strcmp(name, "gemv_overlap")) context->gemv_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_overlap")) context->fewtok_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_off")) context->fewtok_off = value != 0;
     else return FORTAI_CUDA_INVALID;
@@ -1946,6 +2006,94 @@ extern "C" int fortai_cuda_q8_ffn_batch_device(fortai_cuda_q8_context *context,
         error = enqueue_matmul(context, down_weights, gate, kActF32, tokens,
             static_cast<float *>(device_output), nullptr);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "batched FFN", error);
+}
+
+// ---------------------------------------------------------------------------
+// Residual-stream steps: the caller's copy / RMS norm / add folded into the GEMVs
+// ---------------------------------------------------------------------------
+// The reference's caller surrounds every layer object and FFN with copy -> rms_norm ->
+// ... -> add (src/models/qwen35/fortai_qwen35_cpu.f90:713-747): four extra kernels and
+// two copies per layer half on a step that is latency-bound.  These entry points take
+// the residual stream x itself: the first GEMV normalises it in its prologue, the last
+// one adds it back in its epilogue, in place.
+namespace {
+
+bool glue_arguments_ok(const void *x, const void *norm_weights, float epsilon) {
+    return x && norm_weights && epsilon > 0.0f &&
+        reinterpret_cast<uintptr_t>(norm_weights) % 16 == 0;
+}
+
+}  // namespace
+
+extern "C" int fortai_cuda_qwen35_recurrent_step_device(fortai_cuda_qwen35_recurrent *layer,
+    void *device_x, size_t elements, const void *device_norm_weights, float epsilon) {
+    if (!layer || !layer->context || !glue_arguments_ok(device_x, device_norm_weights, epsilon))
+        return FORTAI_CUDA_INVALID;
+    if (elements != static_cast<size_t>(layer->qkv->blocks) * kBlockElems ||
+        elements != static_cast<size_t>(layer->out->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(layer->context->device);
+    Glue glue;
+    glue.norm_weights = static_cast<const float *>(device_norm_weights);
+    glue.epsilon = epsilon;
+    glue.residual = static_cast<const float *>(device_x);
+    const cudaError_t error = enqueue_recurrent(layer, device_x, kActF32,
+        static_cast<float *>(device_x), glue);
+    return error == cudaSuccess ? FORTAI_CUDA_OK
+                                : fail(layer->context, "Qwen recurrent step", error);
+}
+
+extern "C" int fortai_cuda_qwen35_attention_step_device(fortai_cuda_qwen35_attention *layer,
+    void *device_x, size_t elements, int position, const void *device_norm_weights,
+    float epsilon) {
+    if (!layer || !layer->context || !glue_arguments_ok(device_x, device_norm_weights, epsilon))
+        return FORTAI_CUDA_INVALID;
+    if (elements != static_cast<size_t>(layer->out->rows)) return FORTAI_CUDA_INVALID;
+    Glue glue;
+    glue.norm_weights = static_cast<const float *>(device_norm_weights);
+    glue.epsilon = epsilon;
+    glue.residual = static_cast<const float *>(device_x);
+    return attention_run(layer, device_x, elements, position, device_x, elements, glue);
+}
+
+extern "C" int fortai_cuda_q8_ffn_step_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, void *device_x, size_t elements,
+    const void *device_norm_weights, float epsilon) {
+    if (!owned(context, gate_weights) || !owned(context, up_weights) ||
+        !owned(context, down_weights) || !glue_arguments_ok(device_x, device_norm_weights, epsilon))
+        return FORTAI_CUDA_INVALID;
+    if (gate_weights->rows != up_weights->rows || gate_weights->blocks != up_weights->blocks ||
+        gate_weights->rows != down_weights->blocks * kBlockElems ||
+        elements != static_cast<size_t>(gate_weights->blocks) * kBlockElems ||
+        elements != static_cast<size_t>(down_weights->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const size_t inner = static_cast<size_t>(gate_weights->rows);
+    cudaError_t error = ensure_scratch(context, inner / kBlockElems * kBlockBytes,
+        inner * sizeof(float));
+    Glue glue;
+    glue.norm_weights = static_cast<const float *>(device_norm_weights);
+    glue.epsilon = epsilon;
+    glue.residual = static_cast<const float *>(device_x);
+    if (error == cudaSuccess)
+        error = enqueue_ffn(context, gate_weights, up_weights, down_weights, device_x, kActF32,
+            static_cast<float *>(device_x), glue);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "FFN step", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_norm_device_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_x, size_t elements,
+    const void *device_norm_weights, float epsilon, void *device_output,
+    size_t output_elements) {
+    if (!owned(context, weights) || !device_output ||
+        !glue_arguments_ok(device_x, device_norm_weights, epsilon)) return FORTAI_CUDA_INVALID;
+    if (elements != static_cast<size_t>(weights->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(weights->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    GemvParams p = single_params(context, weights, device_x, static_cast<float *>(device_output));
+    p.norm_weights = static_cast<const float *>(device_norm_weights);
+    p.norm_epsilon = epsilon;
+    const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPlain);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "normalised matvec", error);
 }
 
 // ---------------------------------------------------------------------------

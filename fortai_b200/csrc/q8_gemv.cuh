@@ -66,6 +66,12 @@ struct GemvParams {
     unsigned *cta_counter;             // device word, zero between launches
     unsigned sequence;
     int my_rank;
+    // optional fusions of the caller's glue (null = off): an RMS norm of the fp32
+    // activation with learned scale in the prologue, and out[row] = dot + residual[row]
+    // in the plain epilogue (residual may be the output vector itself)
+    const float *norm_weights;
+    float norm_epsilon;
+    const float *residual;
 };
 
 // Tail of a peer-output GEMV: turns "every rank stored its slice everywhere" into "this
@@ -115,9 +121,32 @@ __host__ __device__ inline size_t activation_smem_bytes(int width, int blocks) {
     return (static_cast<size_t>(width) + static_cast<size_t>(blocks) * 4 + 15) & ~size_t(15);
 }
 
+// 1 / sqrt(mean(x^2) + epsilon) over `width` floats, by all threads of the CTA.  Sum of
+// squares in double and the rest in float, as the reference's RMS norm does it
+// (src/models/qwen35/fortai_qwen35_cpu.f90:1422-1427, backend/cuda/fortai_cuda_backend.cu:518-537).
+__device__ __forceinline__ float rms_inverse_scale(const float *x, int width, float epsilon, int tid,
+    int threads) {
+    __shared__ double rms_partial[32];
+    double sum = 0.0;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    for (int g = tid; g < (width >> 2); g += threads) {
+        const float4 v = x4[g];
+        sum += static_cast<double>(v.x) * v.x + static_cast<double>(v.y) * v.y +
+            static_cast<double>(v.z) * v.z + static_cast<double>(v.w) * v.w;
+    }
+#pragma unroll
+    for (int offset = 16; offset; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    if ((tid & 31) == 0) rms_partial[tid >> 5] = sum;
+    __syncthreads();
+    double total = 0.0;
+    for (int w = 0; w < (threads + 31) / 32; ++w) total += rms_partial[w];
+    return 1.0f / sqrtf(static_cast<float>(total / static_cast<double>(width)) + epsilon);
+}
+
 template <int ACT>
 __device__ __forceinline__ void stage_activation(const void *activation, int width, int blocks,
-    uint8_t *smem, int tid, int threads) {
+    uint8_t *smem, int tid, int threads, const float *norm_weights = nullptr,
+    float norm_epsilon = 0.0f) {
     int8_t *act_q = reinterpret_cast<int8_t *>(smem);
     float *act_s = reinterpret_cast<float *>(smem + width);
     if (ACT == kActPlanar) {
@@ -148,6 +177,11 @@ __device__ __forceinline__ void stage_activation(const void *activation, int wid
         const float4 *x4 = static_cast<const float4 *>(activation);
         uint32_t *act_q32 = reinterpret_cast<uint32_t *>(act_q);
         const int groups = width >> 2;              // float4 count; 8 per block
+        const float4 *w4 = reinterpret_cast<const float4 *>(norm_weights);
+        const float inverse_rms = norm_weights
+            ? rms_inverse_scale(static_cast<const float *>(activation), width, norm_epsilon, tid,
+                  threads)
+            : 1.0f;
         constexpr int kPasses = 4;
         for (int g0 = tid; g0 - tid < groups; g0 += threads * kPasses) {
             float4 v[kPasses];
@@ -155,6 +189,14 @@ __device__ __forceinline__ void stage_activation(const void *activation, int wid
             for (int k = 0; k < kPasses; ++k) {
                 const int g = g0 + k * threads;
                 v[k] = g < groups ? x4[g] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (norm_weights && g < groups) {
+                    // (x * inverse) * weight, each product rounded, as the norm kernel does
+                    const float4 w = w4[g];
+                    v[k].x = __fmul_rn(__fmul_rn(v[k].x, inverse_rms), w.x);
+                    v[k].y = __fmul_rn(__fmul_rn(v[k].y, inverse_rms), w.y);
+                    v[k].z = __fmul_rn(__fmul_rn(v[k].z, inverse_rms), w.z);
+                    v[k].w = __fmul_rn(__fmul_rn(v[k].w, inverse_rms), w.w);
+                }
             }
 #pragma unroll
             for (int k = 0; k < kPasses; ++k) {
@@ -234,7 +276,10 @@ template <int U, int NR, int ACT, int EPI>
 __global__ void __launch_bounds__(kGemvThreads)
 q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(16) uint8_t gemv_smem[];
-    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
+    grid_dependents_may_launch();
+    grid_dependency_wait();      // the activation is the previous kernel's output
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads,
+        p.norm_weights, p.norm_epsilon);
     __syncthreads();
     const int4 *act_q = reinterpret_cast<const int4 *>(gemv_smem);
     const float *act_s = reinterpret_cast<const float *>(gemv_smem + p.width);
@@ -291,7 +336,7 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
             const int row = first + r;
             if (lane == 0 && row < p.total_rows) {
                 if (EPI == kEpiPlain) {
-                    *out[r] = total;
+                    *out[r] = p.residual ? total + p.residual[row] : total;
                 } else if (EPI == kEpiPeers) {
                     for (int peer = 0; peer < p.peers; ++peer)
                         p.peer_outputs[peer][p.first_row + row] = total;
@@ -443,6 +488,7 @@ __host__ __device__ inline size_t pipelined_smem_bytes(int width, int blocks, in
 template <int CPL, int ACT, int EPI, int DEPTH>
 __global__ void __launch_bounds__(kGemvThreads)
 q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
+    grid_dependents_may_launch();
     extern __shared__ __align__(16) uint8_t gemv_smem[];
     constexpr int ROWS = EPI == kEpiSiluPair ? 2 : 1;
     const int lane = threadIdx.x & 31;
@@ -486,7 +532,10 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         for (int r = 0; r < ROWS; ++r) row_issue<CPL>(next[r], base[r] + step, lane, p.width);
     }
 
-    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
+    // the weight requests above do not depend on the previous kernel; everything below does
+    grid_dependency_wait();
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads,
+        p.norm_weights, p.norm_epsilon);
     __syncthreads();
     const int4 *act_lane = reinterpret_cast<const int4 *>(gemv_smem) + lane;
     const float *scale_lane = reinterpret_cast<const float *>(gemv_smem + p.width) + (lane >> 1);
@@ -517,7 +566,7 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
             } else if (EPI == kEpiPeers) {
                 staged[finished - cta_first] = total[0];
             } else {
-                p.outputs[0][finished] = total[0];
+                p.outputs[0][finished] = p.residual ? total[0] + p.residual[finished] : total[0];
             }
         }
         if (DEPTH == 2) {
@@ -896,6 +945,7 @@ q8_gemv_ring_kernel(const __grid_constant__ GemvParams p, const __grid_constant_
 // --------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 q8_quantize_kernel(const float *__restrict__ input, uint8_t *__restrict__ output, long long blocks) {
+    grid_dependents_may_launch();
     const int lane = threadIdx.x & 31;
     const long long warp = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const long long warps = static_cast<long long>(gridDim.x) * 8;
@@ -917,6 +967,7 @@ template <int ACT>
 __global__ void __launch_bounds__(256)
 q8_planar_prepare_kernel(const void *__restrict__ activation, int width, int blocks,
     uint8_t *__restrict__ image) {
+    grid_dependents_may_launch();
     int8_t *act_q = reinterpret_cast<int8_t *>(image);
     float *act_s = reinterpret_cast<float *>(image + width);
     const int lane = threadIdx.x & 31;

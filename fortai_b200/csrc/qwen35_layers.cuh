@@ -98,6 +98,7 @@ gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     const float *__restrict__ ssm_a, const float *__restrict__ ssm_dt,
     const float *__restrict__ ssm_norm, float *__restrict__ state, float *__restrict__ output,
     int state_size, int key_heads, int value_heads, int head_size, float epsilon) {
+    grid_dependents_may_launch();
     extern __shared__ float gdn_shared[];     // head_size outputs
     __shared__ double reduce[32];
     const int head = blockIdx.x;
@@ -193,6 +194,7 @@ __global__ void __launch_bounds__(256)
 attention_apply_kernel(const float *__restrict__ query, const __half *__restrict__ key_cache,
     const __half *__restrict__ value_cache, float *__restrict__ attention, int heads, int kv_heads,
     int head_size, int value_size, const int *__restrict__ position_ptr) {
+    grid_dependents_may_launch();
     extern __shared__ float scores[];        // position + 1 entries
     __shared__ float reduce[32];
     const int head = blockIdx.x;

@@ -73,19 +73,22 @@ class qwen35_device_model_t:
         self.spec = None
         self.cuda_graph_enabled = False
         self.cuda_graph_ready = False
+        self.fused = False
         self._weights = []
         self._layers = []
         self._buffers = []
 
     # -- enable_cuda + setup_cuda_device_pipeline
-    def open(self, spec, device=0, cuda_graph=False) -> b.status_t:
+    def open(self, spec, device=0, cuda_graph=False, fused=False) -> b.status_t:
+        """`fused`: use the residual-stream entry points (norm and add inside the GEMVs)
+        instead of the reference's copy / rms_norm / add calls around every layer half."""
         self.close()
         stat = b.status_t()
         self.cuda = b.cuda_q8_context_t()
         stat = self.cuda.create(device)
         if not stat.is_ok():
             return stat
-        self.spec, self.cuda_graph_enabled = spec, cuda_graph
+        self.spec, self.cuda_graph_enabled, self.fused = spec, cuda_graph, fused
         hidden, vocabulary = spec["hidden"], spec["vocabulary"]
 
         def upload(host, rows, width):
@@ -179,6 +182,17 @@ class qwen35_device_model_t:
     def _mix_and_ffn(self, entry, position) -> b.status_t:
         c, hidden = self.cuda, self.spec["hidden"]
         eps = self.spec["epsilon"]
+        if self.fused:
+            if entry["recurrent"]:
+                stat = entry["mixer"].step_device(self.cuda_x, hidden, entry["attn_norm"], eps)
+            else:
+                stat = entry["mixer"].step_device(self.cuda_x, hidden, position,
+                                                  entry["attn_norm"], eps)
+            if stat.is_ok():
+                stat = b.cuda_q8_ffn_step_device(c, entry["ffn_gate"], entry["ffn_up"],
+                                                 entry["ffn_down"], self.cuda_x, hidden,
+                                                 entry["post_norm"], eps)
+            return stat
         stat = b.cuda_qwen35_copy_device(c, self.cuda_x, self.cuda_residual, 4 * hidden)
         if stat.is_ok():
             stat = b.cuda_qwen35_rms_norm_device(c, self.cuda_x, entry["attn_norm"],
@@ -208,6 +222,10 @@ class qwen35_device_model_t:
 
     def _output(self) -> b.status_t:
         hidden = self.spec["hidden"]
+        if self.fused:
+            return b.cuda_q8_matvec_norm_device_f32(self.cuda, self.output, self.cuda_x, hidden,
+                                                    self.cuda_output_norm, self.spec["epsilon"],
+                                                    self.cuda_logits, self.spec["vocabulary"])
         stat = b.cuda_qwen35_rms_norm_device(self.cuda, self.cuda_x, self.cuda_output_norm,
                                              self.cuda_normalized, hidden, self.spec["epsilon"])
         if stat.is_ok():

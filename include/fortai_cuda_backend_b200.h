@@ -266,6 +266,26 @@ int fortai_cuda_q8_ffn_batch_device(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *down_weights, const void *device_activation, int tokens,
     void *device_output, size_t output_elements);
 
+/* Residual-stream steps.  The reference's caller wraps every layer object and FFN in
+ * copy -> rms_norm -> ... -> add (src/models/qwen35/fortai_qwen35_cpu.f90:713-747, 764-800);
+ * these take the residual stream x itself (fp32, device, 16-byte aligned, `elements` =
+ * hidden size) and do x <- x + f(rms_norm(x) * norm_weights) in place: the norm runs in the
+ * first GEMV's prologue, the add in the last GEMV's epilogue.  norm_weights: `elements`
+ * floats in device memory, 16-byte aligned; epsilon > 0.  Enqueue only. */
+int fortai_cuda_qwen35_recurrent_step_device(fortai_cuda_qwen35_recurrent *layer, void *device_x,
+    size_t elements, const void *device_norm_weights, float epsilon);
+int fortai_cuda_qwen35_attention_step_device(fortai_cuda_qwen35_attention *layer, void *device_x,
+    size_t elements, int position, const void *device_norm_weights, float epsilon);
+int fortai_cuda_q8_ffn_step_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, void *device_x, size_t elements,
+    const void *device_norm_weights, float epsilon);
+/* out = weights . Q8(rms_norm(x) * norm_weights): the output head (:749-762) in one launch. */
+int fortai_cuda_q8_matvec_norm_device_f32(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_x, size_t elements,
+    const void *device_norm_weights, float epsilon, void *device_output,
+    size_t output_elements);
+
 /* Row-sharded GEMV whose epilogue stores this rank's slice into every rank's
  * output vector: peer_outputs[p] is rank p's full-length output buffer (device
  * pointers valid on this device, e.g. from symmetric memory); the slice is

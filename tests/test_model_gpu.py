@@ -61,3 +61,40 @@ def test_decode_steps_match_the_cpu_model_and_the_graph_replays_them(oracle):
     close_enough(again, cpu2.forward(17, 0))
     eager.close()
     graphed.close()
+
+
+def test_fused_residual_steps_match_the_unfused_pipeline(oracle):
+    """x <- x + f(rms_norm(x)) inside the GEMVs: same logits as the call-by-call pipeline up
+    to the rounding of the norm sum (another summation order in double), fewer launches."""
+    from fortai_b200.qwen35_device import qwen35_device_model_t
+    spec = make_spec(oracle, hidden=512, inner=1024, vocabulary=2048, layer_count=4, max_context=16)
+    cpu = mo.Model(spec)
+    plain, fused = qwen35_device_model_t(), qwen35_device_model_t()
+    assert plain.open(spec).is_ok()
+    assert fused.open(spec, cuda_graph=True, fused=True).is_ok()
+    token = 5
+    for position in range(5):
+        expected, stat = plain.forward(token, position)
+        assert stat.is_ok(), stat
+        logits, stat = fused.forward(token, position)
+        assert stat.is_ok(), stat
+        close_enough(logits, cpu.forward(token, position))
+        close_enough(logits, expected)
+        token = int(np.argmax(expected))
+    eager_fused = qwen35_device_model_t()
+    assert eager_fused.open(spec, fused=True).is_ok()
+    eager_fused.forward(1, 0)
+    before = eager_fused.cuda.launch_count()
+    eager_fused.forward(1, 1)
+    # 5 / 4 kernels per layer object, 3 per FFN, embedding and the output head
+    assert eager_fused.cuda.launch_count() - before == 3 * (5 + 3) + (4 + 3) + 2
+    # argument checks
+    c = eager_fused.cuda
+    layer = eager_fused._layers[0]
+    from fortai_b200 import backend_cuda as b
+    assert not layer["mixer"].step_device(eager_fused.cuda_x, 512 + 32, layer["attn_norm"], 1e-6).is_ok()
+    assert not layer["mixer"].step_device(eager_fused.cuda_x, 512, layer["attn_norm"], 0.0).is_ok()
+    assert not b.cuda_q8_ffn_step_device(c, layer["ffn_gate"], layer["ffn_up"], layer["ffn_gate"],
+                                         eager_fused.cuda_x, 512, layer["post_norm"], 1e-6).is_ok()
+    for model in (plain, fused, eager_fused):
+        model.close()
