@@ -188,6 +188,26 @@ cudaError_t launch_gemv_kernel(fortai_cuda_q8_context *c, Kernel kernel, int gri
     return error != cudaSuccess ? error : cudaGetLastError();
 }
 
+// The small kernels between the GEMVs of a layer, launched the same way: each begins with
+// grid_dependency_wait(), so only its launch latency overlaps the predecessor.
+template <typename... Params, typename... Args>
+cudaError_t launch_overlapped(fortai_cuda_q8_context *c, void (*kernel)(Params...), int grid,
+    int threads, size_t smem, Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(grid);
+    config.blockDim = dim3(threads);
+    config.dynamicSmemBytes = smem;
+    config.stream = c->stream;
+    cudaLaunchAttribute overlap = {};
+    overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    overlap.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &overlap;
+    config.numAttrs = c->gemv_overlap ? 1 : 0;
+    const cudaError_t error = cudaLaunchKernelEx(&config, kernel, args...);
+    ++c->launches;
+    return error != cudaSuccess ? error : cudaGetLastError();
+}
+
 template <int U, int NR, int ACT, int EPI>
 cudaError_t launch_direct_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
     auto kernel = q8_gemv_direct_kernel<U, NR, ACT, EPI>;
@@ -522,13 +542,10 @@ cudaError_t launch_planar_prepare(fortai_cuda_q8_context *c, const void *activat
     int width, int blocks, uint8_t *image) {
     const int grid = std::max(1, std::min((blocks + 7) / 8, c->sm_count * 4));
     if (act == kActF32)
-        q8_planar_prepare_kernel<kActF32><<<grid, 256, 0, c->stream>>>(activation, width, blocks,
-            image);
-    else
-        q8_planar_prepare_kernel<kActQ8><<<grid, 256, 0, c->stream>>>(activation, width, blocks,
-            image);
-    ++c->launches;
-    return cudaGetLastError();
+        return launch_overlapped(c, q8_planar_prepare_kernel<kActF32>, grid, 256, 0, activation,
+            width, blocks, image);
+    return launch_overlapped(c, q8_planar_prepare_kernel<kActQ8>, grid, 256, 0, activation, width,
+        blocks, image);
 }
 
 // Long activation vectors are quantized / unpacked once into the context's prepared image
@@ -572,10 +589,8 @@ cudaError_t launch_quantize(fortai_cuda_q8_context *c, const float *input, uint8
     const long long want = static_cast<long long>((blocks + 7) / 8);
     const int grid = static_cast<int>(std::max<long long>(1,
         std::min<long long>(want, static_cast<long long>(c->sm_count) * 16)));
-    q8_quantize_kernel<<<grid, 256, 0, c->stream>>>(input, output,
+    return launch_overlapped(c, q8_quantize_kernel, grid, 256, 0, input, output,
         static_cast<long long>(blocks));
-    ++c->launches;
-    return cudaGetLastError();
 }
 
 bool owned(const fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w) {
@@ -1241,16 +1256,16 @@ cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *a
     p.norm_epsilon = glue.epsilon;
     cudaError_t error = launch_gemv(c, p, act, kEpiPlain);
     if (error != cudaSuccess) return error;
-    gdn_conv_silu_kernel<<<(layer->conv_size + 255) / 256, 256, 0, c->stream>>>(qkv,
+    error = launch_overlapped(c, gdn_conv_silu_kernel, (layer->conv_size + 255) / 256, 256, 0, qkv,
         layer->conv_weights, layer->conv_state, layer->conv_size, layer->conv_kernel);
-    gdn_l2_normalize_kernel<<<(2 * layer->key_heads + 7) / 8, 256, 0, c->stream>>>(qkv,
-        layer->key_heads, layer->head_size, layer->state_size, layer->epsilon);
-    gdn_step_kernel<<<layer->value_heads, 256, layer->head_size * sizeof(float), c->stream>>>(qkv,
-        gate, alpha, beta, layer->ssm_a, layer->ssm_dt, layer->ssm_norm, layer->gdn_state,
-        layer->gdn_output, layer->state_size, layer->key_heads, layer->value_heads,
-        layer->head_size, layer->epsilon);
-    c->launches += 3;
-    error = cudaGetLastError();
+    if (error == cudaSuccess)
+        error = launch_overlapped(c, gdn_l2_normalize_kernel, (2 * layer->key_heads + 7) / 8, 256, 0,
+            qkv, layer->key_heads, layer->head_size, layer->state_size, layer->epsilon);
+    if (error == cudaSuccess)
+        error = launch_overlapped(c, gdn_step_kernel, layer->value_heads, 256,
+            layer->head_size * sizeof(float), qkv, gate, alpha, beta, layer->ssm_a, layer->ssm_dt,
+            layer->ssm_norm, layer->gdn_state, layer->gdn_output, layer->state_size,
+            layer->key_heads, layer->value_heads, layer->head_size, layer->epsilon);
     if (error != cudaSuccess) return error;
     GemvParams o = single_params(c, layer->out, layer->gdn_output, output);
     o.residual = glue.residual;
@@ -1541,20 +1556,18 @@ int attention_run(fortai_cuda_qwen35_attention *layer, const void *device_activa
     p.norm_epsilon = glue.epsilon;
     cudaError_t error = launch_gemv(c, p, kActF32, kEpiPlain);
     if (error == cudaSuccess) {
-        attention_prepare_kernel<<<layer->heads + layer->kv_heads, 256, 0, c->stream>>>(query, key,
-            value, layer->q_norm, layer->k_norm, layer->key_cache, layer->value_cache,
-            layer->heads, layer->kv_heads, layer->head_size, layer->value_size, c->position,
-            layer->rope_dimension, layer->rope_base, layer->epsilon);
+        error = launch_overlapped(c, attention_prepare_kernel, layer->heads + layer->kv_heads, 256,
+            0, query, key, value, layer->q_norm, layer->k_norm, layer->key_cache,
+            layer->value_cache, layer->heads, layer->kv_heads, layer->head_size, layer->value_size,
+            c->position, layer->rope_dimension, layer->rope_base, layer->epsilon);
         const size_t shared = static_cast<size_t>(layer->max_context) * sizeof(float);
-        if (shared > 48 * 1024)
+        if (error == cudaSuccess && shared > 48 * 1024)
             error = cudaFuncSetAttribute(attention_apply_kernel,
                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         if (error == cudaSuccess)
-            attention_apply_kernel<<<layer->heads, 256, shared, c->stream>>>(query,
+            error = launch_overlapped(c, attention_apply_kernel, layer->heads, 256, shared, query,
                 layer->key_cache, layer->value_cache, layer->attention, layer->heads,
                 layer->kv_heads, layer->head_size, layer->value_size, c->position);
-        c->launches += 2;
-        if (error == cudaSuccess) error = cudaGetLastError();
     }
     if (error == cudaSuccess) {
         GemvParams o = single_params(c, layer->out, layer->attention,

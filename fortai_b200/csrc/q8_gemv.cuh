@@ -946,6 +946,7 @@ q8_gemv_ring_kernel(const __grid_constant__ GemvParams p, const __grid_constant_
 __global__ void __launch_bounds__(256)
 q8_quantize_kernel(const float *__restrict__ input, uint8_t *__restrict__ output, long long blocks) {
     grid_dependents_may_launch();
+    grid_dependency_wait();
     const int lane = threadIdx.x & 31;
     const long long warp = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
     const long long warps = static_cast<long long>(gridDim.x) * 8;
@@ -968,6 +969,7 @@ __global__ void __launch_bounds__(256)
 q8_planar_prepare_kernel(const void *__restrict__ activation, int width, int blocks,
     uint8_t *__restrict__ image) {
     grid_dependents_may_launch();
+    grid_dependency_wait();
     int8_t *act_q = reinterpret_cast<int8_t *>(image);
     float *act_s = reinterpret_cast<float *>(image + width);
     const int lane = threadIdx.x & 31;

@@ -57,6 +57,8 @@ __device__ __forceinline__ double cta_sum_double(double v, double *scratch32) {
 __global__ void __launch_bounds__(256)
 gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_weights,
     float *__restrict__ conv_state, int conv_size, int kernel) {
+    grid_dependents_may_launch();
+    grid_dependency_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= conv_size) return;
     const float now = qkv[c];
@@ -77,6 +79,8 @@ gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_wei
 __global__ void __launch_bounds__(256)
 gdn_l2_normalize_kernel(float *__restrict__ values, int key_heads, int head_size, int state_size,
     float epsilon) {
+    grid_dependents_may_launch();
+    grid_dependency_wait();
     const int slice = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (slice >= 2 * key_heads) return;
@@ -99,6 +103,7 @@ gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     const float *__restrict__ ssm_norm, float *__restrict__ state, float *__restrict__ output,
     int state_size, int key_heads, int value_heads, int head_size, float epsilon) {
     grid_dependents_may_launch();
+    grid_dependency_wait();
     extern __shared__ float gdn_shared[];     // head_size outputs
     __shared__ double reduce[32];
     const int head = blockIdx.x;
@@ -162,6 +167,8 @@ attention_prepare_kernel(float *__restrict__ query, float *__restrict__ key,
     const float *__restrict__ key_norm, __half *__restrict__ key_cache,
     __half *__restrict__ value_cache, int heads, int kv_heads, int head_size, int value_size,
     const int *__restrict__ position_ptr, int rope_dimension, float rope_base, float epsilon) {
+    grid_dependents_may_launch();
+    grid_dependency_wait();
     __shared__ double reduce[32];
     const int position = *position_ptr;
     const bool is_query = static_cast<int>(blockIdx.x) < heads;
@@ -195,6 +202,7 @@ attention_apply_kernel(const float *__restrict__ query, const __half *__restrict
     const __half *__restrict__ value_cache, float *__restrict__ attention, int heads, int kv_heads,
     int head_size, int value_size, const int *__restrict__ position_ptr) {
     grid_dependents_may_launch();
+    grid_dependency_wait();
     extern __shared__ float scores[];        // position + 1 entries
     __shared__ float reduce[32];
     const int head = blockIdx.x;
