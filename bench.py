@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-Headline workload (BASELINE.json configs[2], the shape the target is quoted on):
+Headline workload (the lm_head shape the bandwidth target is quoted on):
 the lm_head GEMV, 151936 rows x K=2560, Q8_0 weights ~N(0, 0.02), fp32
 activation ~N(0, 1), batch 1.  A step is one full matvec.  The metric is
 weight-GB/s: rows * (K/32) * 34 bytes per step, over the device time of the
@@ -195,7 +195,7 @@ def run_reference_arm(args):
 
 def workload_config(n_gpus):
     return {
-        "workload": f"lm_head Q8_0 GEMV {ROWS}x{WIDTH} batch 1 (BASELINE configs[2])",
+        "workload": f"lm_head Q8_0 GEMV {ROWS}x{WIDTH} batch 1 (headline configuration)",
         "rows": ROWS, "width": WIDTH, "weight_bytes": WEIGHT_BYTES,
         "sharding": "none" if n_gpus == 1 else f"rows/{n_gpus} per rank, fp32 logits reassembled on every rank",
         "cache": "inputs larger than L2 (413 MB of weights per step, L2 is 126 MB)",
@@ -483,7 +483,7 @@ def run_mmq_only(args):
 
 
 def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3, rows=MMQ_N, width=MMQ_K):
-    """Batched product; by default M=512 x K=2560 x N=9728 (BASELINE configs[3])."""
+    """Batched product; by default M=512 x K=2560 x N=9728 (the prefill configuration)."""
     MMQ_M, MMQ_N, MMQ_K = tokens, rows, width
     host_weights = make_device_weights(torch, backend, ctx, 0, MMQ_N, MMQ_K, seed=2)
     w = backend.cuda_q8_weights_t()
@@ -530,7 +530,7 @@ def apply_options(ctx, spec):
 
 
 def decode_shapes():
-    """BASELINE configs[0], [1] and [4]: (label, rows, width)."""
+    """Every named decode-step projection shape: (label, rows, width)."""
     shapes = [("config0 3072x1024", 3072, 1024)]
     for hidden in (1024, 2048, 2560):
         inner = int(round(3.8 * hidden / 256.0)) * 256
@@ -566,8 +566,8 @@ def graph_time_us(torch, ctx, enqueue, per_graph=20, replays=25, warm=3):
 
 
 def sweep_batched(torch, backend, args):
-    """Batched product at the token counts of BASELINE configs[3] and the batch-8 decode of
-    configs[4]; weights rotate over copies that together exceed twice the L2 size."""
+    """Batched product at the token counts of the prefill configuration and the batch-8 decode of
+    the 27B-class projections; weights rotate over copies that together exceed twice the L2 size."""
     l2_bytes = 126 * 1024 * 1024
     cases = [("prefill 9728x2560", 9728, 2560, (2, 4, 8, 16, 32, 64, 128, 512)),
              ("27B gate/up 17408x5120", 17408, 5120, (8,)),
@@ -609,7 +609,7 @@ def sweep_batched(torch, backend, args):
 
 
 def sweep_batched_ffn(torch, backend, args):
-    """BASELINE configs[4] at batch 8: the 27B-class FFN for eight activations per call."""
+    """The 27B-class FFN at batch 8: the FFN for eight activations per call."""
     for hidden, inner, tokens in ((5120, 17408, 8), (2560, 9728, 8)):
         label = f"FFN H{hidden} F{inner} M={tokens}"
         if args.only and args.only not in label and args.only not in "batched":

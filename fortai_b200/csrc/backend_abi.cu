@@ -59,6 +59,7 @@ struct fortai_cuda_q8_context {
     int fewtok_threads = 0;    // its CTA size (0 = 256)
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
     int fewtok_step = 0;       // bytes of a row per step (0 = chosen from the shape)
+    int ffn_quantize_in_gemv = 4096;   // FFN inner sizes up to this skip the quantize kernel
     int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
     int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
     int fewtok_off = 0;        // 1 = small batches run one GEMV per token
@@ -805,6 +806,14 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
         }
         return error;
     }
+    if (down->width <= c->ffn_quantize_in_gemv) {
+        // short hidden vectors: the down projection quantizes them in its own prologue (same
+        // bytes, one launch less; from about 4096 elements on every CTA redoing the work
+        // costs more than the separate kernel)
+        GemvParams d = single_params(c, down, c->scratch_output, output);
+        d.residual = glue.residual;
+        return launch_gemv_raw(c, d, kActF32, kEpiPlain);
+    }
     error = launch_quantize(c, c->scratch_output, c->scratch_activation,
         static_cast<size_t>(down->blocks));
     if (error == cudaSuccess) {
@@ -1259,11 +1268,8 @@ cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *a
     error = launch_overlapped(c, gdn_conv_silu_kernel, (layer->conv_size + 255) / 256, 256, 0, qkv,
         layer->conv_weights, layer->conv_state, layer->conv_size, layer->conv_kernel);
     if (error == cudaSuccess)
-        error = launch_overlapped(c, gdn_l2_normalize_kernel, (2 * layer->key_heads + 7) / 8, 256, 0,
-            qkv, layer->key_heads, layer->head_size, layer->state_size, layer->epsilon);
-    if (error == cudaSuccess)
         error = launch_overlapped(c, gdn_step_kernel, layer->value_heads, 256,
-            layer->head_size * sizeof(float), qkv, gate, alpha, beta, layer->ssm_a, layer->ssm_dt,
+            3 * layer->head_size * sizeof(float), qkv, gate, alpha, beta, layer->ssm_a, layer->ssm_dt,
             layer->ssm_norm, layer->gdn_state, layer->gdn_output, layer->state_size,
             layer->key_heads, layer->value_heads, layer->head_size, layer->epsilon);
     if (error != cudaSuccess) return error;
@@ -1635,6 +1641,8 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->fewtok_step = value;
     else if (!std::strcmp(name, "fewtok_stages") && (value == 0 || value == 2 || value == 3))
         context->fewtok_stages = value;
+    else if (!std::strcmp(name, "ffn_quantize_in_gemv") && value >= 0)
+        context->ffn_quantize_in_gemv = value;
     else if (!std::strcmp(name, "gemv_overlap")) context->gemv_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_overlap")) context->fewtok_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_off")) context->fewtok_off = value != 0;

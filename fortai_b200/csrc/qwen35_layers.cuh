@@ -73,29 +73,12 @@ gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_wei
     qkv[c] = silu_ieee(acc);
 }
 
-// L2 normalisation of the query heads and the key heads of the convolved vector: one
-// warp per head.  Queries start at head * head_size, keys at state_size * key_heads +
-// head * head_size.
-__global__ void __launch_bounds__(256)
-gdn_l2_normalize_kernel(float *__restrict__ values, int key_heads, int head_size, int state_size,
-    float epsilon) {
-    grid_dependents_may_launch();
-    grid_dependency_wait();
-    const int slice = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    if (slice >= 2 * key_heads) return;
-    float *v = values + (slice < key_heads ? slice * head_size
-                                           : state_size * key_heads + (slice - key_heads) * head_size);
-    double sum = 0.0;
-    for (int i = lane; i < head_size; i += 32) sum += static_cast<double>(v[i]) * v[i];
-    sum = warp_sum_double(sum);
-    const float inverse = 1.0f / fmaxf(sqrtf(static_cast<float>(sum)), epsilon);
-    for (int i = lane; i < head_size; i += 32) v[i] *= inverse;
-}
-
-// One gated-delta-net step for one value head per CTA: every warp owns rows of the
-// head_size x head_size state (decay, key dot, delta update, query dot), then the
-// head's output is RMS-normalised, scaled by ssm_norm and gated by silu(gate).
+// One gated-delta-net step for one value head per CTA.  Warps 0 and 1 first L2-normalise
+// the head's query and key (sum of squares in double, 1 / max(sqrt(sum), epsilon), as
+// l2_normalize_slice of the reference does; the convolved vector itself is left as it
+// is), then every warp owns
+// rows of the head_size x head_size state (decay, key dot, delta update, query dot), then
+// the head's output is RMS-normalised, scaled by ssm_norm and gated by silu(gate).
 __global__ void __launch_bounds__(256)
 gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     const float *__restrict__ alpha, const float *__restrict__ beta,
@@ -104,14 +87,25 @@ gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     int state_size, int key_heads, int value_heads, int head_size, float epsilon) {
     grid_dependents_may_launch();
     grid_dependency_wait();
-    extern __shared__ float gdn_shared[];     // head_size outputs
+    extern __shared__ float gdn_shared[];     // head_size outputs, then query, then key
     __shared__ double reduce[32];
     const int head = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int key_head = head / (value_heads / key_heads);
-    const float *query = conv + key_head * head_size;
-    const float *key = conv + state_size * key_heads + key_head * head_size;
+    float *query = gdn_shared + head_size;
+    float *key = query + head_size;
     const float *value = conv + 2 * state_size * key_heads + head * head_size;
+    if (warp < 2) {
+        const float *raw = warp == 0 ? conv + key_head * head_size
+                                     : conv + state_size * key_heads + key_head * head_size;
+        float *normalized = warp == 0 ? query : key;
+        double sum = 0.0;
+        for (int i = lane; i < head_size; i += 32) sum += static_cast<double>(raw[i]) * raw[i];
+        sum = warp_sum_double(sum);
+        const float inverse = 1.0f / fmaxf(sqrtf(static_cast<float>(sum)), epsilon);
+        for (int i = lane; i < head_size; i += 32) normalized[i] = raw[i] * inverse;
+    }
+    __syncthreads();
     const float decay = expf(ssm_a[head] * softplus_clamped(alpha[head] + ssm_dt[head]));
     const float b = sigmoid_stable(beta[head]);
     const float scale = 1.0f / sqrtf(static_cast<float>(head_size));

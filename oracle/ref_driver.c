@@ -1,5 +1,5 @@
 /* Row-loop driver around the REFERENCE's own compiled arithmetic.
- * TEST / BASELINE INFRASTRUCTURE ONLY - never linked into the shipped library.
+ * TEST AND CPU-BASELINE INFRASTRUCTURE ONLY - never linked into the shipped library.
  *
  * The reference's Q8_0 arithmetic is C (src/backend/cpu/fortai_q8_dot.c) and is
  * compiled unchanged, from where it lies, by oracle/Makefile.  The loop that

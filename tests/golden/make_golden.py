@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures in this directory FROM THE REFERENCE ITSELF.
 
-Needs the reference checkout (default /root/reference): its C arithmetic is
+Needs the reference checkout (path in FORTAI_REFERENCE): its C arithmetic is
 compiled in place by oracle/Makefile into oracle/_ref, and its bench-spec header
 is compiled into a helper under oracle/_ref.  Nothing from the restated oracle
 (oracle/q8_oracle.c) is used to produce an expected value here, with one

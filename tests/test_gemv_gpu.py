@@ -95,7 +95,7 @@ def decode_shapes():
 @pytest.mark.parametrize("variant", VARIANTS)
 @pytest.mark.parametrize("rows,width", [(3072, 1024)] + decode_shapes())
 def test_decode_projection_sweep(backend, context, dev, oracle, rows, width, variant):
-    """BASELINE configs 0 and 1: every decode-step projection at batch 1."""
+    """Every named decode-step projection at batch 1."""
     context.set_option("gemv_variant", variant)
     weights = oracle.make_weights(rows, width, seed=0)
     x = oracle.normal(width, seed=1)
@@ -124,7 +124,7 @@ def test_config0_against_golden(backend, context, dev, oracle):
 
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_lm_head_full_size(backend, context, dev, oracle, variant):
-    """BASELINE config 2 at full size: 151936 x 2560, every row against the oracle."""
+    """The lm_head at full size: 151936 x 2560, every row against the oracle."""
     rows, width = 151936, 2560
     context.set_option("gemv_variant", variant)
     weights = oracle.make_weights(rows, width, seed=0)

@@ -21,7 +21,7 @@ def check_rows(actual, expected):
 
 @pytest.mark.parametrize("tokens", [16, 64, 128, 512])
 def test_prefill_config_shapes(backend, context, dev, oracle, tokens):
-    """BASELINE config 3: M in {16, 64, 128, 512} x K=2560 x N=9728."""
+    """The prefill configuration: M in {16, 64, 128, 512} x K=2560 x N=9728."""
     rows, width = 9728, 2560
     weights = oracle.make_weights(rows, width, seed=2)
     x = oracle.normal(tokens * width, seed=3).reshape(tokens, width)
