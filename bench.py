@@ -453,7 +453,7 @@ def run_gpu_arm(args):
         "e2e": {"value": WEIGHT_BYTES * e2e_steps / e2e_s / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": WIDTH * 4, "d2h_bytes_per_step": my_rows * 4,
                 "ms_per_step": e2e_s / e2e_steps * 1e3,
-                "api": "fortai_cuda_q8_matvec_host_f32 (pinned host buffers)"},
+                "api": "fortai_cuda_q8_matvec_host_f32 (pinned host buffers; the activation is copied up, the kernel stores the results into the pinned output)"},
         "gpu_launches": int(launches),
         "clocks": sampler.summary(t0, t1),
     }

@@ -60,6 +60,7 @@ struct fortai_cuda_q8_context {
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
     int fewtok_step = 0;       // bytes of a row per step (0 = chosen from the shape)
     int ffn_quantize_in_gemv = 4096;   // FFN inner sizes up to this skip the quantize kernel
+    int host_direct_output = 1;    // *_host_f32: store straight into page-locked output
     int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
     int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
     int fewtok_off = 0;        // 1 = small batches run one GEMV per token
@@ -567,6 +568,20 @@ cudaError_t launch_gemv(fortai_cuda_q8_context *c, const GemvParams &p, int act,
     GemvParams prepared = p;
     prepared.activation = c->scratch_planar;
     return launch_gemv_raw(c, prepared, kActPlanar, epi);
+}
+
+// The device-side alias of a host pointer when that memory is page-locked and mapped into
+// the device's address space (16-byte aligned), else null.  Never fails: unknown pointers
+// are pageable memory.
+float *mapped_host_pointer(const void *host) {
+    cudaPointerAttributes attributes = {};
+    if (cudaPointerGetAttributes(&attributes, host) != cudaSuccess) {
+        cudaGetLastError();                       // not an error for the caller
+        return nullptr;
+    }
+    if (attributes.type != cudaMemoryTypeHost || !attributes.devicePointer) return nullptr;
+    if (reinterpret_cast<uintptr_t>(attributes.devicePointer) % 16 != 0) return nullptr;
+    return static_cast<float *>(attributes.devicePointer);
 }
 
 GemvParams single_params(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
@@ -1643,6 +1658,7 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->fewtok_stages = value;
     else if (!std::strcmp(name, "ffn_quantize_in_gemv") && value >= 0)
         context->ffn_quantize_in_gemv = value;
+    else if (!std::strcmp(name, "host_direct_output")) context->host_direct_output = value != 0;
     else if (!std::strcmp(name, "gemv_overlap")) context->gemv_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_overlap")) context->fewtok_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_off")) context->fewtok_off = value != 0;
@@ -1686,16 +1702,31 @@ extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
     const size_t out_bytes = static_cast<size_t>(weights->rows) * sizeof(float);
     // the fp32 activation is parked in the activation scratch (4 bytes per element)
     cudaError_t error = ensure_scratch(context, in_bytes, out_bytes);
+    // Page-locked, device-mapped output (cudaHostAlloc / cudaHostRegister memory): the GEMV
+    // stores its results there itself, a CTA's block of rows at a time in full lines, while
+    // it is still streaming weights; the separate device-to-host copy (607 KB and a second
+    // trip through the copy engine for the lm_head) disappears.  Pageable memory keeps the
+    // copy.
+    float *mapped_output = nullptr;
+    if (error == cudaSuccess && context->host_direct_output && weights->width % 512 == 0)
+        mapped_output = mapped_host_pointer(host_output);
     if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
     if (error == cudaSuccess)
         error = cudaMemcpyAsync(context->scratch_activation, host_activation, in_bytes,
             cudaMemcpyHostToDevice, context->stream);
     if (error == cudaSuccess) {
-        const GemvParams p = single_params(context, weights, context->scratch_activation,
+        GemvParams p = single_params(context, weights, context->scratch_activation,
             context->scratch_output);
-        error = launch_gemv(context, p, kActF32, kEpiPlain);
+        if (mapped_output) {
+            p.peers = 1;
+            p.peer_outputs[0] = mapped_output;
+            p.first_row = 0;
+            error = launch_gemv(context, p, kActF32, kEpiPeers);
+        } else {
+            error = launch_gemv(context, p, kActF32, kEpiPlain);
+        }
     }
-    if (error == cudaSuccess)
+    if (error == cudaSuccess && !mapped_output)
         error = cudaMemcpyAsync(host_output, context->scratch_output, out_bytes,
             cudaMemcpyDeviceToHost, context->stream);
     if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);

@@ -325,3 +325,31 @@ def test_small_device_ops(backend, context, dev, oracle):
     assert np.allclose(dev.floats(dout, width), a * np.float32(inv) * b, rtol=2e-6, atol=1e-7)
     assert backend.cuda_qwen35_copy_device(context, da, dout, 4 * width).is_ok()
     assert np.array_equal(dev.floats(dout, width), a)
+
+
+def test_host_f32_stores_straight_into_page_locked_output(backend, context, dev, oracle):
+    """With a page-locked (device-mapped) output buffer the GEMV writes the results to host
+    memory itself; with pageable memory they come back through a copy.  Same bits."""
+    import torch
+    rows, width = 5000, 2560
+    weights = oracle.make_weights(rows, width, seed=21)
+    x = oracle.normal(width, seed=22)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    w = dev.weights(weights, rows, width)
+    pageable = np.zeros(rows, np.float32)
+    _, stat = backend.cuda_q8_matvec_host_f32(context, w, x, pageable)
+    assert stat.is_ok(), stat
+    assert np.abs(pageable - expected).max() <= l2_tolerance(expected)
+    locked = torch.zeros(rows + 3, dtype=torch.float32).pin_memory()
+    before = context.launch_count()
+    ms, stat = backend.cuda_q8_matvec_host_f32(context, w, x, locked.numpy()[:rows])
+    assert stat.is_ok(), stat
+    assert context.launch_count() - before == 1
+    assert np.array_equal(locked.numpy()[:rows], pageable)
+    assert float(locked[rows:].abs().max()) == 0.0        # nothing past the last row
+    # switched off: back to the copy
+    assert context.set_option("host_direct_output", 0).is_ok()
+    again = torch.zeros(rows, dtype=torch.float32).pin_memory()
+    _, stat = backend.cuda_q8_matvec_host_f32(context, w, x, again.numpy())
+    assert stat.is_ok(), stat
+    assert np.array_equal(again.numpy(), pageable)
