@@ -730,11 +730,21 @@ int matvec_host_many(fortai_cuda_q8_context *c, const HostRequest *requests, int
     }
     cudaSetDevice(c->device);
     cudaError_t error = ensure_scratch(c, expected_activation, total_rows * sizeof(float));
+    // a single product into page-locked, device-mapped memory: the kernel stores there itself
+    float *mapped_output = nullptr;
+    if (error == cudaSuccess && count == 1 && !combined_output && c->host_direct_output &&
+        first->width % 512 == 0)
+        mapped_output = mapped_host_pointer(requests[0].output);
     if (error == cudaSuccess) error = cudaEventRecord(c->start, c->stream);
     if (error == cudaSuccess)
         error = cudaMemcpyAsync(c->scratch_activation, host_activation, expected_activation,
             cudaMemcpyHostToDevice, c->stream);
-    if (error == cudaSuccess) {
+    if (error == cudaSuccess && mapped_output) {
+        GemvParams p = single_params(c, first, c->scratch_activation, c->scratch_output);
+        p.peers = 1;
+        p.peer_outputs[0] = mapped_output;
+        error = launch_gemv(c, p, kActQ8, kEpiPeers);
+    } else if (error == cudaSuccess) {
         GemvParams p = {};
         size_t offset = 0;
         for (int i = 0; i < count; ++i) {
@@ -752,7 +762,7 @@ int matvec_host_many(fortai_cuda_q8_context *c, const HostRequest *requests, int
         p.status = c->status_device;
         error = launch_gemv(c, p, kActQ8, kEpiPlain);
     }
-    if (error == cudaSuccess) {
+    if (error == cudaSuccess && !mapped_output) {
         if (combined_output) {
             error = cudaMemcpyAsync(combined_output, c->scratch_output,
                 total_rows * sizeof(float), cudaMemcpyDeviceToHost, c->stream);

@@ -353,3 +353,23 @@ def test_host_f32_stores_straight_into_page_locked_output(backend, context, dev,
     _, stat = backend.cuda_q8_matvec_host_f32(context, w, x, again.numpy())
     assert stat.is_ok(), stat
     assert np.array_equal(again.numpy(), pageable)
+
+
+def test_reference_host_call_into_page_locked_output(backend, context, dev, oracle):
+    """fortai_cuda_q8_matvec_host (Q8_0 activation from the host) with a page-locked output."""
+    import torch
+    rows, width = 3000, 1024
+    weights = oracle.make_weights(rows, width, seed=31)
+    x = oracle.normal(width, seed=32)
+    expected, quantized, _ = oracle.matvec(weights, rows, width, x)
+    w = dev.weights(weights, rows, width)
+    pageable = np.zeros(rows, np.float32)
+    _, stat = backend.cuda_q8_matvec_host(context, w, quantized, quantized.size, pageable,
+                                          pageable.nbytes)
+    assert stat.is_ok(), stat
+    locked = torch.zeros(rows, dtype=torch.float32).pin_memory()
+    _, stat = backend.cuda_q8_matvec_host(context, w, quantized, quantized.size, locked.numpy(),
+                                          locked.numpy().nbytes)
+    assert stat.is_ok(), stat
+    assert np.array_equal(locked.numpy(), pageable)
+    assert np.abs(pageable - expected).max() <= l2_tolerance(expected)
