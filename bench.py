@@ -753,6 +753,87 @@ def run_sweep(args):
     return 0
 
 
+def run_ffn(args):
+    """The 27B-class FFN (hidden 5120, inner 17408, 284 MB of Q8_0 weights) sharded over the
+    ranks: gate/up by rows, down by columns (each rank feeds its own slice of the hidden
+    vector), partial outputs all-reduced over NCCL.  One JSON line from rank 0 with the step
+    time with and without the collective; an auxiliary number, not the headline metric."""
+    import torch
+    from fortai_b200 import backend_cuda as backend, sharded
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world,
+                                device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(local_rank)
+    stream = torch.cuda.current_stream()
+    ctx = backend.cuda_q8_context_t()
+    if not ctx.create(local_rank, stream=stream.cuda_stream).is_ok():
+        raise SystemExit("context creation failed")
+    apply_options(ctx, args.options)
+    hidden, inner = 5120, 17408
+    gate = make_device_weights(torch, backend, ctx, 0, inner, hidden, seed=40)
+    up = make_device_weights(torch, backend, ctx, 0, inner, hidden, seed=41)
+    down = make_device_weights(torch, backend, ctx, 0, hidden, inner, seed=42)
+    ffn = sharded.ShardedFfn(backend, ctx, gate, up, down, hidden, inner, rank, world)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(2)
+    x = torch.randn(hidden, generator=gen, device="cuda", dtype=torch.float32)
+    out = torch.empty(hidden, device="cuda", dtype=torch.float32)
+
+    def local_only():
+        stat = backend.cuda_q8_ffn_device(ctx, ffn.gate, ffn.up, ffn.down, x.data_ptr(), hidden,
+                                          out.data_ptr(), hidden)
+        if not stat.is_ok():
+            raise RuntimeError(f"FFN failed: {stat}")
+
+    def timed(fn, steps):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(steps):
+            fn()
+        b.record(stream)
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    steps = max(10, min(args.steps, 5000))
+    with_collective = timed(lambda: ffn.forward(dist, x, out), steps)
+    without = timed(local_only, steps)
+    if rank == 0:
+        nbytes = 3 * inner * (hidden // 32) * 34
+        print(json.dumps({"metric": "q8_0_ffn_weight_bandwidth", "unit": "GB/s", "n_gpus": world,
+                          "value": nbytes / with_collective / 1e6,
+                          "ms_per_step": with_collective, "ms_per_step_without_all_reduce": without,
+                          "scaling": "strong", "steps": steps,
+                          "config": {"workload": "FFN hidden 5120 inner 17408 batch 1",
+                                     "weight_bytes": nbytes,
+                                     "sharding": f"gate/up rows/{world}, down columns/{world}, "
+                                                 "fp32 all-reduce of 5120 floats",
+                                     "cache": "284 MB of weights per step in total"}}),
+              flush=True)
+    ffn.destroy()
+    ctx.destroy()
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
 def run_decode(args):
     """Whole decode steps through the device pipeline of the model object (embedding, layer
     objects, FFN, lm_head: every call of one token of the reference's fortai_cuda_run), with
@@ -837,6 +918,8 @@ def main():
     parser.add_argument("--only", default="", help="--sweep: only shapes whose label contains this")
     parser.add_argument("--sweep", action="store_true",
                         help="time every named batch-1 shape and the fused FFN (one JSON line each)")
+    parser.add_argument("--ffn", action="store_true",
+                        help="the 27B-class FFN sharded over --gpus ranks (rows + columns, all-reduce)")
     parser.add_argument("--decode", action="store_true",
                         help="whole decode steps of a random-init Qwen3.5-like model (tokens/s)")
     parser.add_argument("--kernel-only", action="store_true",
@@ -851,6 +934,8 @@ def main():
         return run_sweep(args)
     if args.decode:
         return run_decode(args)
+    if args.ffn:
+        return run_ffn(args)
     return run_gpu_arm(args)
 
 

@@ -60,6 +60,7 @@ struct fortai_cuda_q8_context {
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
     int fewtok_step = 0;       // bytes of a row per step (0 = chosen from the shape)
     int ffn_quantize_in_gemv = 4096;   // FFN inner sizes up to this skip the quantize kernel
+    int gemv_even_rounds = 1;      // half-block kernel: equal rows per warp when rounds are few
     int host_direct_output = 1;    // *_host_f32: store straight into page-locked output
     int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
     int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
@@ -238,7 +239,15 @@ cudaError_t launch_direct_instance(fortai_cuda_q8_context *c, const GemvParams &
     }
     const int rows_per_cta = kGemvWarps * (EPI == kEpiSiluPair ? 1 : NR);
     const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
-    const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
+    const int limit = c->sm_count * per_sm;
+    int grid = std::max(1, std::min(needed, limit));
+    if (c->gemv_even_rounds && needed > limit && needed < 4 * limit) {
+        // a few rounds of rows per warp: size the grid so that every warp gets the same
+        // number (5120 long rows on 592 CTAs are 1.08 rounds - most warps would wait for
+        // the few that have a second row; 320 CTAs with two rows each finish sooner)
+        const int rounds = (needed + limit - 1) / limit;
+        grid = (needed + rounds - 1) / rounds;
+    }
     return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem, p);
 }
 
@@ -1668,6 +1677,7 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->fewtok_stages = value;
     else if (!std::strcmp(name, "ffn_quantize_in_gemv") && value >= 0)
         context->ffn_quantize_in_gemv = value;
+    else if (!std::strcmp(name, "gemv_even_rounds")) context->gemv_even_rounds = value != 0;
     else if (!std::strcmp(name, "host_direct_output")) context->host_direct_output = value != 0;
     else if (!std::strcmp(name, "gemv_overlap")) context->gemv_overlap = value != 0;
     else if (!std::strcmp(name, "fewtok_overlap")) context->fewtok_overlap = value != 0;
