@@ -14,7 +14,9 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
-LIB_PATH = os.path.join(LIB_DIR, "libfortai_cuda_b200.so")
+# FORTAI_B200_LIB names another build of the same sources (e.g. with other -D tuning
+# constants); it must exist, it is never rebuilt
+LIB_PATH = os.environ.get("FORTAI_B200_LIB") or os.path.join(LIB_DIR, "libfortai_cuda_b200.so")
 SOURCES = ["backend_abi.cu", "gguf_reader.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
@@ -33,6 +35,10 @@ def _newest_source_mtime() -> float:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
+    if os.environ.get("FORTAI_B200_LIB"):
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"FORTAI_B200_LIB={LIB_PATH} does not exist")
+        return LIB_PATH
     os.makedirs(LIB_DIR, exist_ok=True)
     if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= _newest_source_mtime():
         return LIB_PATH

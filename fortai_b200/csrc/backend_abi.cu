@@ -2249,3 +2249,10 @@ extern "C" int fortai_cuda_q8_ffn_device_noalloc(fortai_cuda_q8_context *context
     return error == cudaSuccess ? FORTAI_CUDA_OK
                                 : fail(context, "allocation-free Qwen FFN device", error);
 }
+
+#ifdef FORTAI_MMQ_TRACE
+// debug builds only (never declared in the public header)
+extern "C" int fortai_cuda_mmq_trace_read(long long *host) {
+    return fortai_b200::mmq_trace_read(host) == cudaSuccess ? 0 : 2;
+}
+#endif

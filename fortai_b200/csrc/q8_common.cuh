@@ -224,6 +224,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
     return false;
 }
 
+// The same with non-suspending probes (mbarrier.test_wait): the waiter notices a completed
+// phase within a few cycles instead of at the end of a suspension slice.  For the hot
+// hand-offs of a pipeline whose stages take well under a microsecond; the bound is 2^26
+// probes (tens of milliseconds).
+__device__ __forceinline__ bool mbar_wait_spin_bounded(uint64_t *bar, uint32_t parity,
+    uint32_t limit = 1u << 26) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // 1-D bulk asynchronous copy global -> shared, completion counted in bytes on an
 // mbarrier.  Both addresses 16-byte aligned, size a multiple of 16.  Always the
 // plain one-destination form: the copy lands in the issuing CTA's own shared memory.

@@ -19,8 +19,8 @@
 //                 K-bytes of weights and of activations per stage (= 4 blocks), and
 //                 one 2-D load of activation scales per 16 blocks
 //   warp 1        TMEM allocation, MMA issue (one elected thread), commits
-//   warps 2..17   epilogue: warp w owns TMEM lanes 32*(w%4).. and 32 of the 128
-//                 token columns; 32 fp32 accumulators per thread, updated with
+//   warps 2..9    epilogue: warp w owns TMEM lanes 32*(w%4).. and 64 of the 128
+//                 token columns; 64 fp32 accumulators per thread, updated with
 //                 packed f32x2 multiply and fused multiply-add
 //
 // The grid is persistent (one CTA per SM); work is split in units of one stage of
@@ -35,16 +35,48 @@
 
 #include <cuda.h>
 
+#ifndef FORTAI_MMQ_SPIN_WAITS
+#define FORTAI_MMQ_SPIN_WAITS 0
+#endif
+
 #include "q8_common.cuh"
 
 namespace fortai_b200 {
+
+#ifdef FORTAI_MMQ_TRACE
+// Debug builds only: clock64 stamps of CTA 0's three roles, for the first kTraceEvents
+// hand-offs of each kind (role, event, slot).
+constexpr int kTraceEvents = 96;
+__device__ long long g_mmq_trace[3][kTraceEvents][6];
+#define MMQ_STAMP(role, n, slot) \
+    do { if (blockIdx.x == 0 && (n) < kTraceEvents) g_mmq_trace[role][n][slot] = clock64(); } while (0)
+#else
+#define MMQ_STAMP(role, n, slot) do { } while (0)
+#endif
+
+// Hand-offs between the roles of the kernel (see FORTAI_MMQ_SPIN_WAITS above).
+__device__ __forceinline__ bool mmq_wait(uint64_t *bar, uint32_t parity) {
+#if FORTAI_MMQ_SPIN_WAITS
+    return mbar_wait_spin_bounded(bar, parity);
+#else
+    return mbar_wait_bounded(bar, parity);
+#endif
+}
 
 constexpr int kMmqTileRows = 128;     // weight rows per CTA (MMA M)
 constexpr int kMmqTileTokens = 128;   // tokens per CTA (MMA N)
 constexpr int kMmqStageBlocks = 4;    // Q8_0 blocks per pipeline stage (128 K-bytes)
 constexpr int kMmqStages = 4;
 constexpr int kMmqTmemBuffers = 4;
-constexpr int kMmqEpilogueWarps = 16;
+#ifndef FORTAI_MMQ_EPILOGUE_WARPS
+#define FORTAI_MMQ_EPILOGUE_WARPS 8
+#endif
+// Four TMEM lane quadrants x (128 / kMmqWarpColumns) column groups.  Eight warps of 64
+// columns rather than sixteen of 32: the fixed cost of a drain step (barrier wait, fences,
+// the load itself, the weight scale) is paid per warp and buffer, and ten warps may use
+// 168 registers each where eighteen are held to 96.
+constexpr int kMmqEpilogueWarps = FORTAI_MMQ_EPILOGUE_WARPS;
+constexpr int kMmqWarpColumns = kMmqTileTokens / (kMmqEpilogueWarps / 4);
 constexpr int kMmqThreads = (2 + kMmqEpilogueWarps) * 32;
 constexpr int kMmqStageBytes = (kMmqTileRows + kMmqTileTokens) * 128;
 
@@ -315,7 +347,7 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                         // activation scales of the next 16 blocks of this piece
                         const int c = chunks % kMmqScaleChunks;
                         const int use = chunks / kMmqScaleChunks;
-                        if (use > 0 && !mbar_wait_bounded(&sh->scale_empty[c], (use - 1) & 1)) {
+                        if (use > 0 && !mmq_wait(&sh->scale_empty[c], (use - 1) & 1)) {
                             atomicExch(p.status, kStatusMmqLoadTimeout);
                             *abort_flag = 1;
                             failed = true;
@@ -328,7 +360,8 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                     }
                     const int s = armed % kMmqStages;
                     const int use = armed / kMmqStages;
-                    if (use > 0 && !mbar_wait_bounded(&sh->smem_empty[s], (use - 1) & 1)) {
+                    MMQ_STAMP(0, armed, 0);
+                    if (use > 0 && !mmq_wait(&sh->smem_empty[s], (use - 1) & 1)) {
                         atomicExch(p.status, kStatusMmqLoadTimeout);
                         *abort_flag = 1;
                         failed = true;
@@ -343,6 +376,7 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                     tma_load_2d(dst, &weights_map, st * 128, row0, &sh->smem_full[s]);
                     tma_load_2d(dst + kMmqTileRows * 128, &act_map, st * 128, token0,
                         &sh->smem_full[s]);
+                    MMQ_STAMP(0, armed, 1);
                     ++armed;
                 }
                 u += count;
@@ -372,20 +406,23 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
             int issued = 0;         // MMAs issued (TMEM ring position)
             for (long long u = unit_begin; u < unit_end && !failed; ++u, ++consumed) {
                 const int s = consumed % kMmqStages;
-                if (!mbar_wait_bounded(&sh->smem_full[s], (consumed / kMmqStages) & 1)) {
+                MMQ_STAMP(1, consumed, 0);
+                if (!mmq_wait(&sh->smem_full[s], (consumed / kMmqStages) & 1)) {
                     atomicExch(p.status, kStatusMmqLoadTimeout);
                     *abort_flag = 1;
                     break;
                 }
                 tc_fence_after();
+                MMQ_STAMP(1, consumed, 1);
                 const uint8_t *tile = stage_base + s * kMmqStageBytes;
                 const uint64_t desc_a = smem_desc_k_major_sw128(tile);
                 const uint64_t desc_b = smem_desc_k_major_sw128(tile + kMmqTileRows * 128);
                 for (int j = 0; j < kMmqStageBlocks; ++j, ++issued) {
                     const int buf = issued % kMmqTmemBuffers;
                     const int use = issued / kMmqTmemBuffers;
+                    if (j == 0) MMQ_STAMP(1, consumed, 2);
                     if (use > 0) {
-                        if (!mbar_wait_bounded(&sh->tmem_empty[buf], (use - 1) & 1)) {
+                        if (!mmq_wait(&sh->tmem_empty[buf], (use - 1) & 1)) {
                             atomicExch(p.status, kStatusMmqDrainTimeout);
                             *abort_flag = 1;
                             failed = true;
@@ -402,16 +439,19 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                     mma_i8(tmem_base + buf * kMmqTileTokens, desc_a + 2 * j, desc_b + 2 * j,
                         idesc);
                     mma_commit(&sh->tmem_full[buf]);
+                    if (j == 0) MMQ_STAMP(1, consumed, 3);
                 }
                 if (!failed) mma_commit(&sh->smem_empty[s]);
+                MMQ_STAMP(1, consumed, 4);
             }
         }
     } else {
         // ------------------------------ epilogue ----------------------------------
         const int ew = warp - 2;
         const int quadrant = warp & 3;              // TMEM lanes this warp may touch
-        const int col0 = (ew >> 2) * 32;            // token columns of this warp
-        unsigned long long acc[16];                 // 32 fp32 accumulators, packed in pairs
+        const int col0 = (ew >> 2) * kMmqWarpColumns;   // token columns of this warp
+        constexpr int kPairs = kMmqWarpColumns / 2;
+        unsigned long long acc[kPairs];             // fp32 accumulators, packed in pairs
         bool failed = false;
         int drained = 0;        // accumulators drained (TMEM ring position)
         int chunks = 0;         // scale chunks consumed
@@ -428,7 +468,7 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
             const uint8_t *scale_plane = p.weights +
                 static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) acc[i] = 0ull;
+            for (int i = 0; i < kPairs; ++i) acc[i] = 0ull;
             // The four fp16 weight scales of a stage are 8 aligned bytes of the row's
             // scale plane; they are fetched one stage ahead so that the L2 latency
             // hides behind a whole stage of drain work.
@@ -440,7 +480,7 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const int chunk = (chunks + (i >> 2)) % kMmqScaleChunks;
                 if ((i & 3) == 0) {
                     const int n = chunks + (i >> 2);
-                    if (!mbar_wait_bounded(&sh->scale_full[chunk], (n / kMmqScaleChunks) & 1)) {
+                    if (!mmq_wait(&sh->scale_full[chunk], (n / kMmqScaleChunks) & 1)) {
                         if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
                         *abort_flag = 1;
                         failed = true;
@@ -457,21 +497,34 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                 for (int j = 0; j < kMmqStageBlocks; ++j, ++drained) {
                     const int buf = drained % kMmqTmemBuffers;
                     const uint32_t parity = (drained / kMmqTmemBuffers) & 1;
-                    if (!mbar_wait_bounded(&sh->tmem_full[buf], parity)) {
+                    const uint32_t taddr = tmem_base +
+                        (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kMmqTileTokens + col0;
+                    if (warp == 2 && lane == 0) MMQ_STAMP(2, drained, 0);
+                    if (!mmq_wait(&sh->tmem_full[buf], parity)) {
                         if (lane == 0) atomicExch(p.status, kStatusMmqMmaTimeout);
                         *abort_flag = 1;
                         failed = true;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t taddr = tmem_base +
-                        (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kMmqTileTokens + col0;
-                    uint32_t v[32];
-                    tmem_load_32(taddr, v);
+                    if (warp == 2 && lane == 0) MMQ_STAMP(2, drained, 1);
+                    // All of the warp's columns leave TMEM at once and the buffer is handed
+                    // back before any arithmetic.  (Tried and dropped: draining in slabs of 32
+                    // columns with the next slab in flight, and requesting the next
+                    // accumulator's first slab before the last slab of this one is worked on -
+                    // both were 5 % slower.  A clock64 trace (-DFORTAI_MMQ_TRACE) shows why: of
+                    // the ~770 cycles a warp spends per block, the load and its wait are 37, the
+                    // barrier wait ~130 and the arithmetic below ~520.)
+                    constexpr int kSlabs = kMmqWarpColumns / 32;
+                    uint32_t v[kSlabs][32];
+#pragma unroll
+                    for (int h = 0; h < kSlabs; ++h) tmem_load_32(taddr + 32 * h, v[h]);
                     tmem_load_wait();
+                    if (warp == 2 && lane == 0) MMQ_STAMP(2, drained, 2);
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+                    if (warp == 2 && lane == 0) MMQ_STAMP(2, drained, 3);
 
                     const uint32_t word = j < 2 ? dw4.x : dw4.y;
                     const float dw = half_bits_to_float(
@@ -481,21 +534,25 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
                     const ulonglong2 *da = reinterpret_cast<const ulonglong2 *>(da_stage +
                         j * kMmqTileTokens + col0);
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) {
-                        const ulonglong2 a = da[q];
-                        acc[2 * q] = fma2(cvt2(v[4 * q], v[4 * q + 1]), mul2(dw2, a.x),
-                            acc[2 * q]);
-                        acc[2 * q + 1] = fma2(cvt2(v[4 * q + 2], v[4 * q + 3]), mul2(dw2, a.y),
-                            acc[2 * q + 1]);
+                    for (int h = 0; h < kSlabs; ++h) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const ulonglong2 a = da[8 * h + q];
+                            acc[16 * h + 2 * q] = fma2(cvt2(v[h][4 * q], v[h][4 * q + 1]),
+                                mul2(dw2, a.x), acc[16 * h + 2 * q]);
+                            acc[16 * h + 2 * q + 1] = fma2(cvt2(v[h][4 * q + 2], v[h][4 * q + 3]),
+                                mul2(dw2, a.y), acc[16 * h + 2 * q + 1]);
+                        }
                     }
+                    if (warp == 2 && lane == 0) MMQ_STAMP(2, drained, 4);
                     if (DOTS && row_ok) {
                         const int kb = st * kMmqStageBlocks + j;
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
+                        for (int e = 0; e < kMmqWarpColumns; ++e) {
                             const int t0 = token0 + col0 + e;
                             if (t0 < p.tokens)
                                 p.block_dots[(static_cast<size_t>(t0) * p.rows + row) * p.blocks +
-                                    kb] = static_cast<int>(v[e]);
+                                    kb] = static_cast<int>(v[e >> 5][e & 31]);
                         }
                     }
                 }
@@ -508,7 +565,7 @@ q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,
             if (!failed && row_ok && p.output) {
                 const bool split = count != p.stages_per_tile;
 #pragma unroll
-                for (int e = 0; e < 16; ++e) {
+                for (int e = 0; e < kPairs; ++e) {
                     const int t = token0 + col0 + 2 * e;
                     float lo, hi;
                     unpack2(acc[e], lo, hi);
@@ -701,5 +758,11 @@ inline cudaError_t mmq_enqueue(cudaStream_t stream, int sm_count, int *status,
     ++*launches;
     return cudaGetLastError();
 }
+
+#ifdef FORTAI_MMQ_TRACE
+inline cudaError_t mmq_trace_read(long long *host) {
+    return cudaMemcpyFromSymbol(host, g_mmq_trace, sizeof(g_mmq_trace));
+}
+#endif
 
 }  // namespace fortai_b200
