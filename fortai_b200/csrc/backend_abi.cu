@@ -60,6 +60,7 @@ struct fortai_cuda_q8_context {
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
     int fewtok_step = 0;       // bytes of a row per step (0 = chosen from the shape)
     int ffn_quantize_in_gemv = 4096;   // FFN inner sizes up to this skip the quantize kernel
+    int gdn_conv_in_gemv = 1;      // recurrent layer: convolution in the projection's epilogue
     int gemv_even_rounds = 1;      // half-block kernel: equal rows per warp when rounds are few
     int host_direct_output = 1;    // *_host_f32: store straight into page-locked output
     int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
@@ -490,7 +491,7 @@ bool want_ring(const fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
 
 template <int ACT>
 cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
-    if (p.norm_weights || p.residual) {
+    if (p.norm_weights || p.residual || p.conv_weights) {
         // the fused norm / residual live in the pipelined and the half-block kernel only
         cudaError_t error = cudaSuccess;
         if (epi == kEpiSiluPair) {
@@ -1297,10 +1298,19 @@ cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *a
     p.segments = 4;
     p.norm_weights = glue.norm_weights;
     p.norm_epsilon = glue.epsilon;
+    // the convolution + SiLU over the qkv channels rides in this launch's epilogue
+    const bool conv_in_gemv = c->gdn_conv_in_gemv != 0;
+    if (conv_in_gemv) {
+        p.conv_weights = layer->conv_weights;
+        p.conv_state = layer->conv_state;
+        p.conv_rows = layer->conv_size;
+        p.conv_kernel = layer->conv_kernel;
+    }
     cudaError_t error = launch_gemv(c, p, act, kEpiPlain);
     if (error != cudaSuccess) return error;
-    error = launch_overlapped(c, gdn_conv_silu_kernel, (layer->conv_size + 255) / 256, 256, 0, qkv,
-        layer->conv_weights, layer->conv_state, layer->conv_size, layer->conv_kernel);
+    if (!conv_in_gemv)
+        error = launch_overlapped(c, gdn_conv_silu_kernel, (layer->conv_size + 255) / 256, 256, 0,
+            qkv, layer->conv_weights, layer->conv_state, layer->conv_size, layer->conv_kernel);
     if (error == cudaSuccess)
         error = launch_overlapped(c, gdn_step_kernel, layer->value_heads, 256,
             3 * layer->head_size * sizeof(float), qkv, gate, alpha, beta, layer->ssm_a, layer->ssm_dt,
@@ -1677,6 +1687,7 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->fewtok_stages = value;
     else if (!std::strcmp(name, "ffn_quantize_in_gemv") && value >= 0)
         context->ffn_quantize_in_gemv = value;
+    else if (!std::strcmp(name, "gdn_conv_in_gemv")) context->gdn_conv_in_gemv = value != 0;
     else if (!std::strcmp(name, "gemv_even_rounds")) context->gemv_even_rounds = value != 0;
     else if (!std::strcmp(name, "host_direct_output")) context->host_direct_output = value != 0;
     else if (!std::strcmp(name, "gemv_overlap")) context->gemv_overlap = value != 0;

@@ -81,6 +81,11 @@ __device__ __forceinline__ float silu_mul(float gate, float up) {
     return __fdiv_rn(gate, 1.0f + expf(-gate)) * up;
 }
 
+// silu(x) with the IEEE exponential and division.
+__device__ __forceinline__ float silu_ieee(float x) {
+    return __fdiv_rn(x, 1.0f + expf(-x));
+}
+
 // ---- Q8_0 quantization of 32 floats held one per lane ----------------------
 // Bit-for-bit the arithmetic of the reference's AVX2 quantizer
 // (src/backend/cpu/fortai_q8_dot.c:153-198): amax over the block, scale =

@@ -72,7 +72,31 @@ struct GemvParams {
     const float *norm_weights;
     float norm_epsilon;
     const float *residual;
+    // optional, half-block kernel only: the first `conv_rows` output rows are channels of a
+    // causal depthwise convolution (window conv_kernel, history in conv_state) followed by
+    // SiLU - the gated-delta-net layer's step between its input projections and its state
+    // update, done by the lane that holds the finished dot product
+    const float *conv_weights;
+    float *conv_state;
+    int conv_rows;
+    int conv_kernel;
 };
+
+// One channel of the causal depthwise convolution over the last `kernel` inputs, SiLU, and
+// the shift of that channel's history (conv_state is (kernel - 1) x channels, oldest first).
+// Same arithmetic as the reference's CPU layer (src/models/qwen35/fortai_qwen35_cpu.f90:856-879).
+__device__ __forceinline__ float conv_silu_channel(const float *__restrict__ conv_weights,
+    float *__restrict__ conv_state, int channels, int kernel, int c, float now) {
+    float acc = 0.0f;
+    for (int slot = 0; slot < kernel - 1; ++slot) {
+        const float held = conv_state[slot * channels + c];
+        acc += conv_weights[c * kernel + slot] * held;
+        if (slot > 0) conv_state[(slot - 1) * channels + c] = held;
+    }
+    acc += conv_weights[c * kernel + kernel - 1] * now;
+    conv_state[(kernel - 2) * channels + c] = now;
+    return silu_ieee(acc);
+}
 
 // Tail of a peer-output GEMV: turns "every rank stored its slice everywhere" into "this
 // launch is complete only when every rank's slice has arrived here", without a second
@@ -336,7 +360,11 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
             const int row = first + r;
             if (lane == 0 && row < p.total_rows) {
                 if (EPI == kEpiPlain) {
-                    *out[r] = p.residual ? total + p.residual[row] : total;
+                    float value = p.residual ? total + p.residual[row] : total;
+                    if (p.conv_weights && row < p.conv_rows)
+                        value = conv_silu_channel(p.conv_weights, p.conv_state, p.conv_rows,
+                            p.conv_kernel, row, value);
+                    *out[r] = value;
                 } else if (EPI == kEpiPeers) {
                     for (int peer = 0; peer < p.peers; ++peer)
                         p.peer_outputs[peer][p.first_row + row] = total;

@@ -13,12 +13,9 @@
 #include <cuda_fp16.h>
 
 #include "q8_common.cuh"
+#include "q8_gemv.cuh"
 
 namespace fortai_b200 {
-
-__device__ __forceinline__ float silu_ieee(float x) {
-    return __fdiv_rn(x, 1.0f + expf(-x));
-}
 
 __device__ __forceinline__ float sigmoid_stable(float x) {
     if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
@@ -61,16 +58,7 @@ gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_wei
     grid_dependency_wait();
     const int c = blockIdx.x * blockDim.x + threadIdx.x;
     if (c >= conv_size) return;
-    const float now = qkv[c];
-    float acc = 0.0f;
-    for (int slot = 0; slot < kernel - 1; ++slot) {
-        const float held = conv_state[slot * conv_size + c];
-        acc += conv_weights[c * kernel + slot] * held;
-        if (slot > 0) conv_state[(slot - 1) * conv_size + c] = held;
-    }
-    acc += conv_weights[c * kernel + kernel - 1] * now;
-    conv_state[(kernel - 2) * conv_size + c] = now;
-    qkv[c] = silu_ieee(acc);
+    qkv[c] = conv_silu_channel(conv_weights, conv_state, conv_size, kernel, c, qkv[c]);
 }
 
 // One gated-delta-net step for one value head per CTA.  Warps 0 and 1 first L2-normalise

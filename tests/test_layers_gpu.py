@@ -194,3 +194,28 @@ def test_attention_last_cache_slot(oracle, backend, context, dev):
     context.synchronize()
     layer_close(dev.floats(out_dev, hidden), expected)
     assert layer.destroy().is_ok()
+
+
+def test_recurrent_with_the_convolution_as_its_own_kernel(oracle, backend, context, dev):
+    """The convolution normally rides in the input projection's epilogue; as a separate
+    kernel it gives the same bits."""
+    shape = RECURRENT_SHAPES[0]
+    hidden = shape[0]
+    fused_layer, _, _ = make_recurrent(oracle, backend, context, dev, shape, seed=40)
+    out_a, out_b = dev.buffer(hidden * 4), dev.buffer(hidden * 4)
+    results = []
+    for separate in (0, 1):
+        assert context.set_option("gdn_conv_in_gemv", 1 - separate).is_ok()
+        layer = fused_layer if separate == 0 else make_recurrent(oracle, backend, context, dev,
+                                                                 shape, seed=40)[0]
+        outs = []
+        for step in range(4):
+            x = oracle.normal(hidden, seed=900 + step, sigma=1.0)
+            before = context.launch_count()
+            assert layer.run_device(dev.to_device(x), hidden, out_a, hidden).is_ok()
+            assert context.launch_count() - before == 3 + separate
+            context.synchronize()
+            outs.append(dev.floats(out_a, hidden))
+        results.append(outs)
+    for a, b in zip(*results):
+        assert np.array_equal(a, b)

@@ -43,14 +43,14 @@ def test_decode_steps_match_the_cpu_model_and_the_graph_replays_them(oracle):
         assert np.array_equal(replayed, logits)
         token = int(np.argmax(logits))
     assert graphed.cuda_graph_ready
-    # 4 kernels per recurrent layer object, 4 per attention layer object, 2 per FFN (inner
+    # 3 kernels per recurrent layer object, 4 per attention layer object, 2 per FFN (inner
     # sizes up to 4096 are quantized inside the down projection, else 3), 2 norms
     # and 2 adds per layer (the copies are memcpy nodes), embedding + norm + lm_head per step:
-    # 43 for this model, where the reference's scheme needs about 17 per layer plus 4
+    # 40 for this model, where the reference's scheme needs about 17 per layer plus 4
     before = eager.cuda.launch_count()
     eager.forward(token, 6)
     per_step = eager.cuda.launch_count() - before
-    assert per_step == 3 * (4 + 2 + 4) + (4 + 2 + 4) + 3, per_step
+    assert per_step == 3 * (3 + 2 + 4) + (4 + 2 + 4) + 3, per_step
     # argument checks of qwen35_cpu_forward
     assert not eager.forward(-1, 0)[1].is_ok()
     assert not eager.forward(1024, 0)[1].is_ok()
@@ -87,8 +87,8 @@ def test_fused_residual_steps_match_the_unfused_pipeline(oracle):
     eager_fused.forward(1, 0)
     before = eager_fused.cuda.launch_count()
     eager_fused.forward(1, 1)
-    # 4 kernels per layer object, 2 per FFN, embedding and the output head
-    assert eager_fused.cuda.launch_count() - before == 3 * (4 + 2) + (4 + 2) + 2
+    # 3 or 4 kernels per layer object, 2 per FFN, embedding and the output head
+    assert eager_fused.cuda.launch_count() - before == 3 * (3 + 2) + (4 + 2) + 2
     # argument checks
     c = eager_fused.cuda
     layer = eager_fused._layers[0]
