@@ -862,6 +862,8 @@ def run_decode(args):
         result = {"shape": label, **shape, "vocabulary": 151936,
                   "weight_bytes_per_token": int(weight_bytes)}
         for mode in ("eager", "graph", "fused_eager", "fused_graph"):
+            if args.modes and mode not in args.modes.split(","):
+                continue
             model = qwen35_device_model_t()
             stat = model.open(spec, cuda_graph=mode.endswith("graph"),
                               fused=mode.startswith("fused"))
@@ -920,6 +922,8 @@ def main():
                         help="time every named batch-1 shape and the fused FFN (one JSON line each)")
     parser.add_argument("--ffn", action="store_true",
                         help="the 27B-class FFN sharded over --gpus ranks (rows + columns, all-reduce)")
+    parser.add_argument("--modes", default="",
+                        help="--decode: comma-separated subset of eager,graph,fused_eager,fused_graph")
     parser.add_argument("--decode", action="store_true",
                         help="whole decode steps of a random-init Qwen3.5-like model (tokens/s)")
     parser.add_argument("--kernel-only", action="store_true",

@@ -1312,7 +1312,9 @@ cudaError_t enqueue_recurrent(fortai_cuda_qwen35_recurrent *layer, const void *a
         error = launch_overlapped(c, gdn_conv_silu_kernel, (layer->conv_size + 255) / 256, 256, 0,
             qkv, layer->conv_weights, layer->conv_state, layer->conv_size, layer->conv_kernel);
     if (error == cudaSuccess)
-        error = launch_overlapped(c, gdn_step_kernel, layer->value_heads, 256,
+        // one CTA per value head; enough warps that each walks one or two pairs of rows
+        error = launch_overlapped(c, gdn_step_kernel, layer->value_heads,
+            std::max(64, std::min(1024, layer->head_size * 8)),
             3 * layer->head_size * sizeof(float), qkv, gate, alpha, beta, layer->ssm_a, layer->ssm_dt,
             layer->ssm_norm, layer->gdn_state, layer->gdn_output, layer->state_size,
             layer->key_heads, layer->value_heads, layer->head_size, layer->epsilon);

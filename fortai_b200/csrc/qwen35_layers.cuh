@@ -67,7 +67,7 @@ gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_wei
 // is), then every warp owns
 // rows of the head_size x head_size state (decay, key dot, delta update, query dot), then
 // the head's output is RMS-normalised, scaled by ssm_norm and gated by silu(gate).
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     const float *__restrict__ alpha, const float *__restrict__ beta,
     const float *__restrict__ ssm_a, const float *__restrict__ ssm_dt,
@@ -98,24 +98,45 @@ gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     const float b = sigmoid_stable(beta[head]);
     const float scale = 1.0f / sqrtf(static_cast<float>(head_size));
     float *head_state = state + static_cast<size_t>(head) * head_size * head_size;
-    for (int row = warp; row < head_size; row += warps) {
-        float *s = head_state + static_cast<size_t>(row) * head_size;
-        float key_dot = 0.0f;
+    // Two state rows per warp at a time: their loads and their two warp reductions each are
+    // independent, which halves the length of the dependent chain a warp walks through.
+    for (int row = warp; row < head_size; row += 2 * warps) {
+        const int other = row + warps;
+        const bool pair = other < head_size;
+        float *s0 = head_state + static_cast<size_t>(row) * head_size;
+        float *s1 = head_state + static_cast<size_t>(pair ? other : row) * head_size;
+        float key_dot0 = 0.0f, key_dot1 = 0.0f;
         for (int c = lane; c < head_size; c += 32) {
-            const float decayed = s[c] * decay;
-            s[c] = decayed;
-            key_dot = fmaf(decayed, key[c], key_dot);
+            const float k = key[c];
+            const float d0 = s0[c] * decay;
+            const float d1 = s1[c] * decay;
+            s0[c] = d0;
+            if (pair) s1[c] = d1;
+            key_dot0 = fmaf(d0, k, key_dot0);
+            key_dot1 = fmaf(d1, k, key_dot1);
         }
-        key_dot = warp_sum(key_dot);
-        const float delta = (value[row] - key_dot) * b;
-        float query_dot = 0.0f;
+        key_dot0 = warp_sum(key_dot0);
+        key_dot1 = warp_sum(key_dot1);
+        const float delta0 = (value[row] - key_dot0) * b;
+        const float delta1 = (value[pair ? other : row] - key_dot1) * b;
+        float query_dot0 = 0.0f, query_dot1 = 0.0f;
         for (int c = lane; c < head_size; c += 32) {
-            const float updated = fmaf(delta, key[c], s[c]);
-            s[c] = updated;
-            query_dot = fmaf(updated, query[c], query_dot);
+            const float k = key[c], q = query[c];
+            const float u0 = fmaf(delta0, k, s0[c]);
+            s0[c] = u0;
+            query_dot0 = fmaf(u0, q, query_dot0);
+            if (pair) {
+                const float u1 = fmaf(delta1, k, s1[c]);
+                s1[c] = u1;
+                query_dot1 = fmaf(u1, q, query_dot1);
+            }
         }
-        query_dot = warp_sum(query_dot);
-        if (lane == 0) gdn_shared[row] = query_dot * scale;
+        query_dot0 = warp_sum(query_dot0);
+        query_dot1 = warp_sum(query_dot1);
+        if (lane == 0) {
+            gdn_shared[row] = query_dot0 * scale;
+            if (pair) gdn_shared[other] = query_dot1 * scale;
+        }
     }
     __syncthreads();
     double sum = 0.0;
