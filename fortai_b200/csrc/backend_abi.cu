@@ -330,7 +330,7 @@ cudaError_t launch_pipelined_depth(fortai_cuda_q8_context *c, const GemvParams &
 template <int CPL, int ACT, int EPI>
 cudaError_t launch_pipelined_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
     // the gate/up pair already has two rows per warp in flight
-    if (EPI != kEpiSiluPair && c->gemv_depth == 2)
+    if (EPI != kEpiSiluPair && EPI != kEpiStacked && c->gemv_depth == 2)
         return launch_pipelined_depth<CPL, ACT, EPI, 2>(c, p);
     return launch_pipelined_depth<CPL, ACT, EPI, 1>(c, p);
 }
@@ -386,7 +386,11 @@ bool launch_splitrow(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t
 template <int ACT, int EPI>
 bool launch_pipelined(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *error) {
     if (p.width % 512 != 0) return false;
-    if (EPI == kEpiPlain && p.segments != 1) return false;
+    // stacked matrices: plain epilogue with one row in flight; a convolution rides along
+    // only there (a single matrix with a convolution has no caller)
+    if (EPI == kEpiStacked && (p.segments < 2 || p.residual)) return false;
+    if (EPI == kEpiPlain && (p.segments != 1 || p.conv_weights)) return false;
+    if (EPI == kEpiPeers && p.segments != 1) return false;
     if (EPI == kEpiSiluPair && p.width / 512 > 5) return false;   // two rows double-buffered
     switch (p.width / 512) {
     case 1: *error = launch_pipelined_instance<1, ACT, EPI>(c, p); return true;
@@ -499,6 +503,7 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
             return launch_direct<ACT, kEpiSiluPair>(c, p);
         }
         if (epi != kEpiPlain) return cudaErrorNotSupported;
+        if (p.segments > 1 && launch_pipelined<ACT, kEpiStacked>(c, p, &error)) return error;
         if (launch_pipelined<ACT, kEpiPlain>(c, p, &error)) return error;
         return launch_direct<ACT, kEpiPlain>(c, p);
     }
@@ -515,7 +520,9 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
     if (c->gemv_variant == 0 || c->gemv_variant == 4) {
         cudaError_t error = cudaSuccess;
         bool done = false;
-        if (epi == kEpiPlain) done = launch_pipelined<ACT, kEpiPlain>(c, p, &error);
+        if (epi == kEpiPlain && p.segments > 1)
+            done = launch_pipelined<ACT, kEpiStacked>(c, p, &error);
+        else if (epi == kEpiPlain) done = launch_pipelined<ACT, kEpiPlain>(c, p, &error);
         else if (epi == kEpiSiluPair) done = launch_pipelined<ACT, kEpiSiluPair>(c, p, &error);
         else if (epi == kEpiPeers) done = launch_pipelined<ACT, kEpiPeers>(c, p, &error);
         if (done) return error;

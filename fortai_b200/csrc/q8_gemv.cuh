@@ -37,7 +37,8 @@ enum GemvEpilogue : int {
     kEpiPlain = 0,      // out[row] = dot
     kEpiSiluPair = 1,   // segments: 0 = gate, 1 = up; out[row] = silu(gate.x) * (up.x)
     kEpiBlockDots = 2,  // int32 out[row * blocks + b] = exact block dot
-    kEpiPeers = 3       // plain, stored into every peer's output vector
+    kEpiPeers = 3,      // plain, stored into every peer's output vector
+    kEpiStacked = 4     // pipelined kernel only: plain over up to four stacked matrices
 };
 
 enum ActivationKind : int {
@@ -509,6 +510,22 @@ __host__ __device__ inline size_t pipelined_smem_bytes(int width, int blocks, in
         static_cast<size_t>(kGemvWarps) * rows * (2 * cpl * 16);
 }
 
+// Row `row` of up to four matrices stacked one after the other (the fused projections of
+// a layer): which matrix, which of its rows, and where that row starts.
+__device__ __forceinline__ const uint8_t *stacked_row(const GemvParams &p, int row, size_t stride,
+    int *segment, int *local) {
+    int seg = 0, at = row;
+#pragma unroll
+    for (int s = 0; s < kMaxSegments - 1; ++s)
+        if (seg == s && s + 1 < p.segments && at >= p.rows[s]) {
+            at -= p.rows[s];
+            seg = s + 1;
+        }
+    *segment = seg;
+    *local = at;
+    return p.weights[seg] + at * stride;
+}
+
 // DEPTH is the number of rows a warp keeps in flight: 1 = the next row is
 // requested right after the current one has been consumed (64 registers, four
 // CTAs per SM for CPL = 5), 2 = it is requested one row earlier (register double
@@ -545,9 +562,14 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
     float *staged = reinterpret_cast<float *>(gemv_smem +
         pipelined_smem_bytes(p.width, p.blocks, CPL, ROWS));
 
+    // several stacked matrices (plain epilogue, one row in flight): the row's matrix and
+    // local index are looked up per row instead of stepping one base pointer
+    constexpr bool stacked = EPI == kEpiStacked;
+    int segment = 0, local = row;
     const uint8_t *base[ROWS];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) base[r] = p.weights[r] + row * stride;
+    if (stacked && row < row_end) base[0] = stacked_row(p, row, stride, &segment, &local);
     RowRegs<CPL> cur[ROWS], next[DEPTH == 2 ? ROWS : 1];
     // the first row(s) are requested before the activation is staged, so the
     // quantize prologue runs under a full memory pipeline
@@ -574,10 +596,11 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         for (int r = 0; r < ROWS; ++r)
             partial[r] = row_consume<CPL>(cur[r], act_lane, scale_lane,
                 slots + r * (2 * CPL * 16), lane);
-        const int finished = row;
+        const int finished = row, finished_segment = segment, finished_local = local;
         row += row_step;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) base[r] += step;
+        if (stacked && row < row_end) base[0] = stacked_row(p, row, stride, &segment, &local);
         if (DEPTH == 1) {
             // registers of `cur` are free again: request the next row before reducing
             if (row < row_end) {
@@ -593,6 +616,12 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
                 p.outputs[0][finished] = silu_mul(total[0], total[ROWS - 1]);
             } else if (EPI == kEpiPeers) {
                 staged[finished - cta_first] = total[0];
+            } else if (stacked) {
+                float value = total[0];
+                if (p.conv_weights && finished < p.conv_rows)
+                    value = conv_silu_channel(p.conv_weights, p.conv_state, p.conv_rows,
+                        p.conv_kernel, finished, value);
+                p.outputs[finished_segment][finished_local] = value;
             } else {
                 p.outputs[0][finished] = p.residual ? total[0] + p.residual[finished] : total[0];
             }
