@@ -1619,14 +1619,17 @@ int attention_run(fortai_cuda_qwen35_attention *layer, const void *device_activa
             0, query, key, value, layer->q_norm, layer->k_norm, layer->key_cache,
             layer->value_cache, layer->heads, layer->kv_heads, layer->head_size, layer->value_size,
             c->position, layer->rope_dimension, layer->rope_base, layer->epsilon);
-        const size_t shared = static_cast<size_t>(layer->max_context) * sizeof(float);
+        // scores of every position, then one row of partial value sums per warp
+        const size_t shared = (static_cast<size_t>(layer->max_context + 3) / 4 * 4 +
+            8 * static_cast<size_t>(layer->value_size)) * sizeof(float);
         if (error == cudaSuccess && shared > 48 * 1024)
             error = cudaFuncSetAttribute(attention_apply_kernel,
                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
         if (error == cudaSuccess)
             error = launch_overlapped(c, attention_apply_kernel, layer->heads, 256, shared, query,
                 layer->key_cache, layer->value_cache, layer->attention, layer->heads,
-                layer->kv_heads, layer->head_size, layer->value_size, c->position);
+                layer->kv_heads, layer->head_size, layer->value_size,
+                (layer->max_context + 3) / 4 * 4, c->position);
     }
     if (error == cudaSuccess) {
         GemvParams o = single_params(c, layer->out, layer->attention,

@@ -198,15 +198,31 @@ attention_prepare_kernel(float *__restrict__ query, float *__restrict__ key,
             __float2half_rn(value[head * value_size + i]);
 }
 
-// One CTA per head: scores against every cached key (one warp per position), softmax
-// over positions, weighted sum of cached values, sigmoid output gate.
+// Eight binary16 values of a cache row as floats (one 16-byte load).
+__device__ __forceinline__ void load_half8(const __half *p, float (&out)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p);
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(h[i]);
+        out[2 * i] = f.x;
+        out[2 * i + 1] = f.y;
+    }
+}
+
+// One CTA per head: scores against every cached key (one warp per position), softmax over
+// positions, weighted sum of cached values (the warps share the positions, every lane owns
+// eight value dimensions and reads them with one 16-byte load per position; the warps'
+// partial sums meet in shared memory in warp order), sigmoid output gate.  Dynamic shared
+// memory: max_context scores, then warps x value_size partial sums.  Head and value sizes
+// that are not multiples of 8, or values wider than 256, take the element-wise path.
 __global__ void __launch_bounds__(256)
 attention_apply_kernel(const float *__restrict__ query, const __half *__restrict__ key_cache,
     const __half *__restrict__ value_cache, float *__restrict__ attention, int heads, int kv_heads,
-    int head_size, int value_size, const int *__restrict__ position_ptr) {
+    int head_size, int value_size, int max_context, const int *__restrict__ position_ptr) {
     grid_dependents_may_launch();
     grid_dependency_wait();
-    extern __shared__ float scores[];        // position + 1 entries
+    extern __shared__ __align__(16) float scores[];      // max_context entries, then partials
     __shared__ float reduce[32];
     const int head = blockIdx.x;
     const int position = *position_ptr;
@@ -215,10 +231,28 @@ attention_apply_kernel(const float *__restrict__ query, const __half *__restrict
     const float *q = query + head * 2 * head_size;
     const float *gate = q + head_size;
     const float scale = 1.0f / sqrtf(static_cast<float>(head_size));
+    const bool wide_keys = (head_size & 7) == 0;
     for (int p = warp; p <= position; p += warps) {
         const __half *k = key_cache + (static_cast<size_t>(p) * kv_heads + kv_head) * head_size;
         float dot = 0.0f;
-        for (int i = lane; i < head_size; i += 32) dot = fmaf(q[i], __half2float(k[i]), dot);
+        if (wide_keys) {
+            for (int c = lane; c < (head_size >> 3); c += 32) {
+                float kv[8];
+                load_half8(k + 8 * c, kv);
+                const float4 q0 = *reinterpret_cast<const float4 *>(q + 8 * c);
+                const float4 q1 = *reinterpret_cast<const float4 *>(q + 8 * c + 4);
+                dot = fmaf(q0.x, kv[0], dot);
+                dot = fmaf(q0.y, kv[1], dot);
+                dot = fmaf(q0.z, kv[2], dot);
+                dot = fmaf(q0.w, kv[3], dot);
+                dot = fmaf(q1.x, kv[4], dot);
+                dot = fmaf(q1.y, kv[5], dot);
+                dot = fmaf(q1.z, kv[6], dot);
+                dot = fmaf(q1.w, kv[7], dot);
+            }
+        } else {
+            for (int i = lane; i < head_size; i += 32) dot = fmaf(q[i], __half2float(k[i]), dot);
+        }
         dot = warp_sum(dot);
         if (lane == 0) scores[p] = dot * scale;
     }
@@ -244,6 +278,31 @@ attention_apply_kernel(const float *__restrict__ query, const __half *__restrict
     __syncthreads();
     float normalizer = 0.0f;
     for (int w = 0; w < warps; ++w) normalizer += reduce[w];
+    if ((value_size & 7) == 0 && value_size <= 256) {
+        float *partials = scores + max_context;          // [warps][value_size]
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        const bool owner = lane < (value_size >> 3);
+        if (owner) {
+            for (int p = warp; p <= position; p += warps) {
+                float vv[8];
+                load_half8(value_cache + (static_cast<size_t>(p) * kv_heads + kv_head) * value_size +
+                    8 * lane, vv);
+                const float weight = scores[p];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] = fmaf(weight, vv[i], acc[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) partials[warp * value_size + 8 * lane + i] = acc[i];
+        }
+        __syncthreads();
+        const float inverse = 1.0f / normalizer;
+        for (int i = threadIdx.x; i < value_size; i += blockDim.x) {
+            float total = 0.0f;
+            for (int w = 0; w < warps; ++w) total += partials[w * value_size + i];
+            attention[head * value_size + i] = total * inverse * sigmoid_stable(gate[i]);
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < value_size; i += blockDim.x) {
         float total = 0.0f;
         for (int p = 0; p <= position; ++p) {

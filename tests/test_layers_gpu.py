@@ -219,3 +219,21 @@ def test_recurrent_with_the_convolution_as_its_own_kernel(oracle, backend, conte
         results.append(outs)
     for a, b in zip(*results):
         assert np.array_equal(a, b)
+
+
+def test_attention_over_several_hundred_positions(oracle, backend, context, dev):
+    """Longer than the warp count and than one pass of the softmax loops: every warp gets
+    many positions in the score and in the value passes."""
+    shape = (256, 4, 2, 64, 64, 700, 32, 0)
+    hidden = shape[0]
+    layer, cpu = make_attention(oracle, backend, context, dev, shape, seed=123)
+    out_dev = dev.buffer(hidden * 4)
+    for position in range(640):
+        x = oracle.normal(hidden, seed=10000 + position, sigma=1.0)
+        assert context.set_position(position).is_ok()
+        assert layer.run_device(dev.to_device(x), hidden, position, out_dev, hidden).is_ok()
+        expected = cpu.run(x, position)
+        if position % 127 == 0 or position == 639:
+            context.synchronize()
+            layer_close(dev.floats(out_dev, hidden), expected)
+    assert layer.destroy().is_ok()
