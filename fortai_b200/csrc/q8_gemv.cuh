@@ -58,6 +58,15 @@ struct GemvParams {
     int row_stride;
     const void *activation;
     int *status;
+    // When the successor in the stream may be scheduled (programmatic dependent launch).
+    // Zero (the default): after the row loop, so its launch overlaps this grid's tail only.
+    // Non-zero: as soon as every CTA of this grid runs.  That lets a successor request its
+    // first weights earlier (the same 9728 x 2560 product back to back: 5.6 us against
+    // 6.7 us), but its CTAs take whatever slots are free at that moment, piled onto the SMs
+    // with room; a successor of few CTAs then runs on part of the machine (1024 x 3840
+    // after 7680 x 1024: 5.1 us against 4.3 us; the 1024-wide FFN 8.4 us against 6.6 us),
+    // and whole decode steps are 1-3 % slower.
+    int trigger_early;
     float *peer_outputs[kMaxPeers];
     int peers;
     int first_row;  // element offset of this shard inside the peers' vectors
@@ -301,7 +310,7 @@ template <int U, int NR, int ACT, int EPI>
 __global__ void __launch_bounds__(kGemvThreads)
 q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ __align__(16) uint8_t gemv_smem[];
-    grid_dependents_may_launch();
+    if (p.trigger_early) grid_dependents_may_launch();
     grid_dependency_wait();      // the activation is the previous kernel's output
     stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads,
         p.norm_weights, p.norm_epsilon);
@@ -373,6 +382,7 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
             }
         }
     }
+    grid_dependents_may_launch();
     if (EPI == kEpiPeers) peer_allgather_tail(p);
 }
 
@@ -533,7 +543,7 @@ __device__ __forceinline__ const uint8_t *stacked_row(const GemvParams &p, int r
 template <int CPL, int ACT, int EPI, int DEPTH>
 __global__ void __launch_bounds__(kGemvThreads)
 q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
-    grid_dependents_may_launch();
+    if (p.trigger_early) grid_dependents_may_launch();
     extern __shared__ __align__(16) uint8_t gemv_smem[];
     constexpr int ROWS = EPI == kEpiSiluPair ? 2 : 1;
     const int lane = threadIdx.x & 31;
@@ -636,6 +646,7 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
             }
         }
     }
+    grid_dependents_may_launch();
     if (EPI == kEpiPeers) {
         __syncthreads();
         const int count = row_end - cta_first;
