@@ -62,7 +62,7 @@ struct fortai_cuda_q8_context {
     int ffn_quantize_in_gemv = 4096;   // FFN inner sizes up to this skip the quantize kernel
     int gdn_conv_in_gemv = 1;      // recurrent layer: convolution in the projection's epilogue
     int gemv_even_rounds = 1;      // half-block kernel: equal rows per warp when rounds are few
-    int gemv_early_trigger = 0;    // successor may be scheduled at once: 0 never, 1 always, 2 when the grid fills the machine
+    int gemv_early_trigger = 3;    // successor may be scheduled at once: 0 never, 1 always, 2 when the grid fills the machine, 3 after a residual epilogue
     int host_direct_output = 1;    // *_host_f32: store straight into page-locked output
     int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
     int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
@@ -179,8 +179,11 @@ template <typename Kernel>
 cudaError_t launch_gemv_kernel(fortai_cuda_q8_context *c, Kernel kernel, int grid, int threads,
     size_t smem, const GemvParams &params, int resident_limit) {
     GemvParams p = params;
-    p.trigger_early = c->gemv_early_trigger < 2 ? c->gemv_early_trigger
-                                                : grid * 8 >= resident_limit * 7;
+    switch (c->gemv_early_trigger) {
+    case 0: case 1: p.trigger_early = c->gemv_early_trigger; break;
+    case 2: p.trigger_early = grid * 8 >= resident_limit * 7; break;
+    default: p.trigger_early = params.residual != nullptr; break;   // last GEMV of a layer step
+    }
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(grid);
     config.blockDim = dim3(threads);
@@ -1705,7 +1708,7 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->ffn_quantize_in_gemv = value;
     else if (!std::strcmp(name, "gdn_conv_in_gemv")) context->gdn_conv_in_gemv = value != 0;
     else if (!std::strcmp(name, "gemv_even_rounds")) context->gemv_even_rounds = value != 0;
-    else if (!std::strcmp(name, "gemv_early_trigger") && value <= 2)
+    else if (!std::strcmp(name, "gemv_early_trigger") && value <= 3)
         context->gemv_early_trigger = value;
     else if (!std::strcmp(name, "host_direct_output")) context->host_direct_output = value != 0;
     else if (!std::strcmp(name, "gemv_overlap")) context->gemv_overlap = value != 0;

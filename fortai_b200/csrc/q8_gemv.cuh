@@ -59,7 +59,8 @@ struct GemvParams {
     const void *activation;
     int *status;
     // When the successor in the stream may be scheduled (programmatic dependent launch).
-    // Zero (the default): after the row loop, so its launch overlaps this grid's tail only.
+    // Zero: after the row loop, so its launch overlaps this grid's tail only (the default for
+    // every GEMV but the one with a residual epilogue, which a many-row projection follows).
     // Non-zero: as soon as every CTA of this grid runs.  That lets a successor request its
     // first weights earlier (the same 9728 x 2560 product back to back: 5.6 us against
     // 6.7 us), but its CTAs take whatever slots are free at that moment, piled onto the SMs

@@ -246,6 +246,39 @@ def test_ffn_host_and_device(backend, context, dev, oracle, hidden, inner, varia
     assert not backend.cuda_q8_ffn_device(context, wg, wu, wg, dx, hidden, dout, hidden).is_ok()
 
 
+def test_dependent_launch_settings_give_identical_results(backend, context, dev, oracle):
+    """Where a GEMV lets its successor be scheduled (after its row loop / at its first
+    instruction / at once when its grid fills the machine) and whether launches overlap at
+    all are scheduling choices: a chain of calls in which each reads what the one before
+    wrote must give the same bits under every setting, and its first link the oracle's."""
+    hidden, inner = 1024, 3840
+    up = oracle.make_weights(inner, hidden, seed=21)
+    down = oracle.make_weights(hidden, inner, seed=22)
+    wu, wd = dev.weights(up, inner, hidden), dev.weights(down, hidden, inner)
+    x = oracle.normal(hidden, seed=23)
+    first_link = oracle.matvec(up, inner, hidden, x)[0]
+    assert not context.set_option("gemv_early_trigger", 4).is_ok()
+    results = []
+    for overlap in (0, 1):
+        for trigger in (0, 1, 2, 3):
+            assert context.set_option("gemv_overlap", overlap).is_ok()
+            assert context.set_option("gemv_early_trigger", trigger).is_ok()
+            dx, dmid = dev.to_device(x), dev.buffer(4 * inner)
+            for link in range(4):   # wide -> narrow -> wide ...: many- and few-CTA successors
+                dout = dev.buffer(4 * hidden)
+                assert backend.cuda_q8_matvec_device_f32(context, wu, dx, hidden, dmid,
+                                                         inner).is_ok()
+                if link == 0:
+                    check_vector(dev.floats(dmid, inner), first_link)
+                assert backend.cuda_q8_matvec_device_f32(context, wd, dmid, inner, dout,
+                                                         hidden).is_ok()
+                dx = dout
+            results.append(dev.floats(dx, hidden).copy())
+    assert np.abs(results[0]).max() > 0
+    for other in results[1:]:
+        assert np.array_equal(results[0], other)
+
+
 # --------------------------------------------------------------------------- ABI behaviour
 def test_argument_validation_and_ownership(backend, context, dev, oracle):
     rows, width = 64, 256
