@@ -51,11 +51,6 @@ __device__ __forceinline__ double cta_sum_double(double v, double *scratch32) {
 // Causal depthwise convolution over the last `kernel` inputs of every channel, SiLU,
 // and the shift of the per-channel history.  conv_state is (kernel - 1) x conv_size,
 // oldest first.
-#ifdef FORTAI_LAYER_TRIGGER_LATE
-constexpr bool kLayerTriggerLate = true;
-#else
-constexpr bool kLayerTriggerLate = false;
-#endif
 __global__ void __launch_bounds__(256)
 gdn_conv_silu_kernel(float *__restrict__ qkv, const float *__restrict__ conv_weights,
     float *__restrict__ conv_state, int conv_size, int kernel) {
@@ -78,7 +73,7 @@ gdn_step_kernel(const float *__restrict__ conv, const float *__restrict__ gate,
     const float *__restrict__ ssm_a, const float *__restrict__ ssm_dt,
     const float *__restrict__ ssm_norm, float *__restrict__ state, float *__restrict__ output,
     int state_size, int key_heads, int value_heads, int head_size, float epsilon) {
-    if (!kLayerTriggerLate) grid_dependents_may_launch();
+    grid_dependents_may_launch();
     grid_dependency_wait();
     extern __shared__ float gdn_shared[];     // head_size outputs, then query, then key
     __shared__ double reduce[32];
@@ -225,7 +220,7 @@ __global__ void __launch_bounds__(256)
 attention_apply_kernel(const float *__restrict__ query, const __half *__restrict__ key_cache,
     const __half *__restrict__ value_cache, float *__restrict__ attention, int heads, int kv_heads,
     int head_size, int value_size, int max_context, const int *__restrict__ position_ptr) {
-    if (!kLayerTriggerLate) grid_dependents_may_launch();
+    grid_dependents_may_launch();
     grid_dependency_wait();
     extern __shared__ __align__(16) float scores[];      // max_context entries, then partials
     __shared__ float reduce[32];
