@@ -16,6 +16,7 @@
 #include "q8_common.cuh"
 #include "q8_gemv.cuh"
 #include "q8_mmq.cuh"
+#include "q8_prefill.cuh"
 #include "q8_fewtok.cuh"
 #include "qwen35_layers.cuh"
 
@@ -55,6 +56,7 @@ struct fortai_cuda_q8_context {
     int ring_stages = 0;
     int ring_rows = 0;
     int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 33)
+    int prefill_kind = 0;      // tcgen05 kernel: 0 = binary16 operands (exact block dots in fp32), 1 = kind::i8
     int fewtok_splits = 0;     // K ranges of the few-token kernel (0 = as few as fit)
     int fewtok_threads = 0;    // its CTA size (0 = 256)
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
@@ -77,7 +79,8 @@ struct fortai_cuda_q8_weights {
     int blocks = 0;
     int row_stride = 0;
     uint8_t *data = nullptr;
-    MmqWeightsPlan mmq;   // tensor maps for the prefill kernel, built lazily
+    MmqWeightsPlan mmq;   // tensor maps for the prefill kernels, built lazily
+    PfWeightsPlan prefill;
 };
 
 // Layer objects borrow their weight handles (the caller keeps them alive and destroys
@@ -1696,6 +1699,7 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->ring_stages = value;
     else if (!std::strcmp(name, "ring_rows") && value <= 256) context->ring_rows = value;
     else if (!std::strcmp(name, "mmq_min_tokens")) context->mmq_min_tokens = value;
+    else if (!std::strcmp(name, "prefill_kind")) context->prefill_kind = value;
     else if (!std::strcmp(name, "fewtok_splits") && value >= 0) context->fewtok_splits = value;
     else if (!std::strcmp(name, "fewtok_threads") && value >= 0 && value <= 512 &&
              value % 32 == 0) context->fewtok_threads = value;
@@ -1966,6 +1970,11 @@ cudaError_t enqueue_fewtok(fortai_cuda_q8_context *c, const fortai_cuda_q8_weigh
 // width), one GEMV per token as the last resort.  Exactly one of output / block_dots.
 cudaError_t enqueue_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
     const void *activation, int act, int tokens, float *output, int32_t *block_dots) {
+    if (c->prefill_kind == 0 && pf_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
+        return pf_enqueue(c->stream, c->sm_count, c->status_device,
+            &const_cast<fortai_cuda_q8_weights *>(w)->prefill, w->data, w->rows, w->width,
+            w->row_stride, activation, act, tokens, output, block_dots,
+            reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes, &c->launches);
     if (mmq_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
         return mmq_enqueue(c->stream, c->sm_count, c->status_device,
             &const_cast<fortai_cuda_q8_weights *>(w)->mmq, w->data, w->rows, w->width,
@@ -1992,6 +2001,9 @@ cudaError_t enqueue_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weigh
 
 // scratch the batched kernels need, grown outside a timed region
 cudaError_t reserve_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w, int tokens) {
+    if (c->prefill_kind == 0 && pf_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
+        return pf_reserve(reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes,
+            w->width, tokens);
     return mmq_reserve(reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes, w->rows,
         w->width, tokens);
 }
