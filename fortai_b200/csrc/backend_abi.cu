@@ -56,7 +56,7 @@ struct fortai_cuda_q8_context {
     int ring_stages = 0;
     int ring_rows = 0;
     int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 33)
-    int prefill_kind = 0;      // tcgen05 kernel: 0 = binary16 operands (exact block dots in fp32), 1 = kind::i8
+    int prefill_kind = 0;      // tcgen05 kernel: 0 = kind::f16, activation scale folded into the operand; 1 = kind::i8, scaled per block
     int fewtok_splits = 0;     // K ranges of the few-token kernel (0 = as few as fit)
     int fewtok_threads = 0;    // its CTA size (0 = 256)
     int fewtok_stages = 0;     // tiles per warp ring (0 = chosen from the shape, else 2 or 3)
@@ -700,7 +700,9 @@ int upload_weights(fortai_cuda_q8_context *context, const void *host_weights,
     cudaSetDevice(context->device);
     uint8_t *staging = nullptr;
     const size_t device_bytes = static_cast<size_t>(rows) * w->row_stride;
-    cudaError_t error = cudaMalloc(reinterpret_cast<void **>(&w->data), device_bytes);
+    // 32 spare bytes: the prefill kernel fetches a row's fp16 scales in aligned 16-byte
+    // pieces, and the last piece of the last row may reach past the row's padding
+    cudaError_t error = cudaMalloc(reinterpret_cast<void **>(&w->data), device_bytes + 32);
     if (error == cudaSuccess) error = cudaMalloc(reinterpret_cast<void **>(&staging), expected);
     if (error == cudaSuccess)
         error = cudaMemcpyAsync(staging, host_weights, expected, cudaMemcpyHostToDevice,
@@ -1970,10 +1972,12 @@ cudaError_t enqueue_fewtok(fortai_cuda_q8_context *c, const fortai_cuda_q8_weigh
 // width), one GEMV per token as the last resort.  Exactly one of output / block_dots.
 cudaError_t enqueue_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
     const void *activation, int act, int tokens, float *output, int32_t *block_dots) {
-    if (c->prefill_kind == 0 && pf_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
+    // the exact int32 block dots come from the kind::i8 kernel (or the few-token kernel)
+    if (c->prefill_kind == 0 && !block_dots &&
+        pf_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
         return pf_enqueue(c->stream, c->sm_count, c->status_device,
             &const_cast<fortai_cuda_q8_weights *>(w)->prefill, w->data, w->rows, w->width,
-            w->row_stride, activation, act, tokens, output, block_dots,
+            w->row_stride, activation, act, tokens, output,
             reinterpret_cast<void **>(&c->scratch_aux), &c->scratch_aux_bytes, &c->launches);
     if (mmq_supported(w->rows, w->width, tokens, c->mmq_min_tokens))
         return mmq_enqueue(c->stream, c->sm_count, c->status_device,

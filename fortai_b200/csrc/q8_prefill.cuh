@@ -1,45 +1,53 @@
-// Batched Q8_0 x Q8_0 product for multi-token prefill: tcgen05 tensor cores fed with the
-// int8 quants widened to binary16, block dots exact in fp32, accumulators in TMEM.
+// Batched Q8_0 x Q8_0 product for multi-token prefill on the sm_100a tensor cores, with the
+// activation scale folded into the tensor-core operand.
 //
 // out[t][r] = sum_b half(dw[r][b]) * half(da[t][b]) * (sum_i qw[r][b][i] * qa[t][b][i])
 //
 // The reference has no batched call (one token per forward,
 // src/models/qwen35/fortai_qwen35_cpu.f90:591); parity is defined as `tokens` independent
-// reference matvecs (src/fortai_gguf_runtime.f90:424-465), and the per-(token, row, block)
-// integer dots are the loop of src/backend/cpu/fortai_q8_dot.c:277-279.
+// reference matvecs (src/fortai_gguf_runtime.f90:424-465).
 //
-// Why binary16 operands for an int8 product.  Every Q8_0 block has its own pair of scales,
-// so a block's 32-element dot has to leave the tensor core before the next block is added
-// to it, and every element of the accumulator tile costs CUDA-core work once per block.
-// With kind::i8 that work is an int32 -> fp32 conversion (a quarter-rate instruction), a
-// multiply and a fused multiply-add; the conversions alone take longer than the MMAs.  The
-// quants are integers in [-127, 127], exact in binary16; their products and the sum of 32
-// of them (|dot| <= 516 128 < 2^24) are exact in the fp32 accumulator of kind::f16.  The
-// accumulator therefore holds the block dot already as a float: no conversion, and the
-// int32 block dots that the parity probe returns are these floats converted back, exact.
-// The tensor core runs at half its int8 rate, which is still twice as fast as the
-// CUDA cores can scale what it produces.
+// Why not kind::i8 with one scaling step per block.  Every Q8_0 block has its own pair of
+// scales, so a block's dot has to be scaled before the next block is added to it.  Doing
+// that on the CUDA cores costs, per accumulator element and block, a conversion (quarter
+// rate), a multiply and an FMA, and - whichever way the tile is laid out - one of the two
+// scales is the same for all lanes of a warp and has to be fetched through the load/store
+// unit, whose return path moves 128 bytes per clock: 1024 cycles per block of 128 x 256
+// elements against 128 cycles of int8 MMA (q8_mmq.cuh is that kernel; it is kept as the
+// exact-int32-block-dot probe).
+//
+// Here the activation scale goes into the operand instead.  da * qa (binary16 scale x 7-bit
+// quant) has at most 18 significant bits, so it is the exact sum of two binary16 numbers,
+// hi = rn16(da * qa) and lo = da * qa - hi; the prepare kernel writes both once per call,
+// scaled per token by a power of two so that neither overflows nor leaves the binary16
+// range.  The int8 weights are widened to binary16 (exact) on their way through shared
+// memory.  Four kind::f16 MMAs per block (K = 16 each: two over hi, two over lo) leave
+// sum_i qw * (da * qa) in a fresh fp32 TMEM accumulator, and what is left for the CUDA cores
+// is one packed FMA per two elements and block with the weight scale, which each thread
+// owns (a thread is a weight row): no conversion, no multiply, no shared-memory traffic.
+// The fp32 results differ from the int32 formulation only by the rounding of the tensor
+// core's fp32 accumulation (about 1e-7 relative per block), far inside the 1e-5 * L2 bound;
+// this path has no int32 block dots.
 //
 // Tile: 128 weight rows (MMA M, TMEM lanes) x TN tokens (MMA N, TMEM columns), TN = 256
 // for long prompts (an MMA takes 128 cycles whatever N is, so N = 256 is the only shape at
-// full rate), 128 or 64 for short ones.  Two K = 16 MMAs per Q8_0 block.
+// full rate), 128 or 64 for short ones.
 //
-//   warp 0        TMA producer: per stage (2 blocks = 64 K) the raw int8 weight tile
-//                 (128 rows x 64 bytes) and the binary16 activation tile (TN x 64, 128-byte
-//                 swizzle); per 8 blocks the activation scales (8 x TN floats)
-//   warp 1        TMEM allocation, MMA issue (one elected thread), commits
-//   warps 2..3    weight converters: int8 -> binary16 into the swizzled K-major operand tile
-//   warps 4..11   epilogue: warp w owns TMEM lanes 32*(w%4).. and half of the token columns;
-//                 TN/2 fp32 accumulators per thread, packed f32x2 multiply and FMA
+//   warp 0        TMA producer: per stage (one block) the activation tile (TN x [32 hi |
+//                 32 lo] binary16, 128-byte swizzle); per four blocks the raw int8 weight
+//                 tile (128 rows x 128 bytes)
+//   warps 1, 2    MMA issue (one elected thread each, even / odd blocks), commits; warp 1
+//                 also owns the TMEM allocation
+//   warps 4..7    int8 -> binary16 of the weight tile into the swizzled K-major operand tile
+//   warps 8..23   the drain: warp w owns TMEM lanes 32*(w%4).. and a quarter of the token
+//                 columns
 //
-// Registers: the first warpgroup gives registers back (setmaxnreg) so that the epilogue
-// warpgroups can hold 128 accumulators and two 32-column slabs of a TMEM load per thread.
-//
-// The grid is persistent (one CTA per SM); work is split in units of one stage of one tile
-// so that every CTA gets the same number of units, and a tile that two CTAs share is
-// completed with atomic adds onto zeroed output.  All waits on mbarriers are bounded; a wait
-// that gives up records a status word, raises the CTA's abort flag, and every role falls
-// through to the common exit, where the TMEM allocation is released.
+// Registers: the first two warpgroups give registers back (setmaxnreg) to the sixteen
+// drain warps.  The grid is persistent (one CTA per SM); work is split in units of one block of
+// one tile so that every CTA gets the same number of units, and a tile that two CTAs share
+// is completed with atomic adds onto zeroed output.  All waits on mbarriers are bounded; a
+// wait that gives up records a status word, raises the CTA's abort flag, and every role
+// falls through to the common exit, where the TMEM allocation is released.
 #pragma once
 
 #include <cuda.h>
@@ -48,39 +56,39 @@
 
 namespace fortai_b200 {
 
-constexpr int kPfTileRows = 128;
-constexpr int kPfStageBlocks = 2;           // 64 K per stage: one 128-byte swizzle row of binary16
-constexpr int kPfStageK = kPfStageBlocks * kBlockElems;
-constexpr int kPfStages = 3;
-constexpr int kPfChunkBlocks = 8;           // activation-scale chunk: 8 blocks x TN tokens
-constexpr int kPfChunks = 3;
-#ifndef FORTAI_PF_EPILOGUE_WARPS
-#define FORTAI_PF_EPILOGUE_WARPS 16
+#ifndef FORTAI_PF_STAGES
+#define FORTAI_PF_STAGES 4
 #endif
-#ifndef FORTAI_PF_SLAB_BUFFERS
-#define FORTAI_PF_SLAB_BUFFERS 1
-#endif
-constexpr int kPfEpilogueWarps = FORTAI_PF_EPILOGUE_WARPS;   // 8 or 16: 4 TMEM lane quadrants x column groups
-constexpr int kPfThreads = (4 + kPfEpilogueWarps) * 32;
 #ifndef FORTAI_PF_PRODUCER_REGS
-#define FORTAI_PF_PRODUCER_REGS 40
+#define FORTAI_PF_PRODUCER_REGS 48
 #endif
 #ifndef FORTAI_PF_EPILOGUE_REGS
-#define FORTAI_PF_EPILOGUE_REGS 104
+#define FORTAI_PF_EPILOGUE_REGS 96
 #endif
 #ifndef FORTAI_PF_SLAB
 #define FORTAI_PF_SLAB 16
 #endif
-constexpr int kPfProducerRegs = FORTAI_PF_PRODUCER_REGS;   // registers per thread of the first warpgroup after the hand-over
-constexpr int kPfEpilogueRegs = FORTAI_PF_EPILOGUE_REGS;   // and of the two epilogue warpgroups
+#ifndef FORTAI_PF_SLAB_BUFFERS
+#define FORTAI_PF_SLAB_BUFFERS 2
+#endif
+
+constexpr int kPfTileRows = 128;
+constexpr int kPfStages = FORTAI_PF_STAGES;
+constexpr int kPfEpilogueWarps = 16;        // 4 TMEM lane quadrants x 4 column groups
+constexpr int kPfFrontWarps = 8;            // producer, two MMA issuers, a spare, four converters
+constexpr int kPfConverterWarps = 4;
+constexpr int kPfThreads = (kPfFrontWarps + kPfEpilogueWarps) * 32;
+constexpr int kPfProducerRegs = FORTAI_PF_PRODUCER_REGS;   // per thread of the first warpgroup after the hand-over
+constexpr int kPfEpilogueRegs = FORTAI_PF_EPILOGUE_REGS;   // and of the drain warpgroups
 constexpr int kPfSlab = FORTAI_PF_SLAB;                    // TMEM columns per tcgen05.ld
-constexpr int kPfRawBytes = kPfTileRows * kPfStageK;            // int8 weight tile as loaded
-constexpr int kPfW16Bytes = kPfTileRows * kPfStageK * 2;        // the same tile in binary16
+constexpr int kPfRawBlocks = 4;                            // blocks per raw weight load (128 bytes of every row)
+constexpr int kPfRawBytes = kPfTileRows * kPfRawBlocks * kBlockElems;
+constexpr int kPfRawBuffers = 2;
+constexpr int kPfW16Bytes = kPfTileRows * 128;             // binary16, each row [w | w]: 128 bytes
 
 __host__ __device__ constexpr int pf_stage_bytes(int tn) {
-    return kPfW16Bytes + tn * kPfStageK * 2 + kPfRawBytes;
+    return kPfW16Bytes + tn * 128;
 }
-__host__ __device__ constexpr int pf_chunk_bytes(int tn) { return kPfChunkBlocks * tn * 4; }
 __host__ __device__ constexpr int pf_tmem_buffers(int tn) { return tn >= 256 ? 2 : 4; }
 
 inline int pf_tile_tokens(int tokens) { return tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256; }
@@ -90,35 +98,42 @@ inline int pf_padded_tokens(int tokens) {
     return (tokens + tn - 1) / tn * tn;
 }
 
-// Planar activation image in scratch:
-//   [ tokens_padded x width binary16 quants ][ blocks x tokens_padded float scales ]
+// Activation image in scratch:
+//   [ tokens_padded x blocks x (32 hi | 32 lo) binary16 ][ tokens_padded float unscale ]
 inline size_t pf_scratch_bytes(int width, int tokens) {
     const size_t padded = static_cast<size_t>(pf_padded_tokens(tokens));
-    return padded * width * 2 + padded * (width / kBlockElems) * sizeof(float);
+    return padded * width * 4 + padded * sizeof(float);
 }
 
 inline bool pf_supported(int rows, int width, int tokens, int min_tokens) {
     const int threshold = min_tokens > 0 ? min_tokens : 33;
-    return tokens >= threshold && width % kPfStageK == 0 && rows >= 1;
+    return tokens >= threshold && width % kBlockElems == 0 && width <= 65536 && rows >= 1;
 }
 
 #ifdef FORTAI_PF_TRACE
-// Debug builds only: clock64 stamps of CTA 0's roles (producer, MMA, converter, epilogue).
+// Debug builds only: clock64 stamps of CTA 0's roles (producer, MMA, converter, drain).
 constexpr int kPfTraceEvents = 96;
 __device__ long long g_pf_trace[4][kPfTraceEvents][6];
 #define PF_STAMP(role, n, slot) \
     do { if (blockIdx.x == 0 && (n) < kPfTraceEvents) g_pf_trace[role][n][slot] = clock64(); } while (0)
+#ifdef FORTAI_PF_TRACE_DRAIN
+#define PF_STAMP_DRAIN(role, n, slot) PF_STAMP(role, n, slot)
+#else
+#define PF_STAMP_DRAIN(role, n, slot) do { } while (0)
+#endif
 #else
 #define PF_STAMP(role, n, slot) do { } while (0)
+#define PF_STAMP_DRAIN(role, n, slot) do { } while (0)
 #endif
 
 struct PfWeightsPlan {
     bool ready = false;
-    CUtensorMap weights_map;    // raw int8 quant plane, boxes of 128 rows x 64 bytes
+    CUtensorMap weights_map;    // raw int8 quant plane, boxes of 128 rows x 128 bytes
 };
 
 struct PfParams {
     const uint8_t *weights;     // row-planar weight rows (for the fp16 scale plane)
+    const float *unscale;       // [padded_tokens] power of two that undoes the token's operand scaling
     int rows;
     int width;
     int blocks;
@@ -127,20 +142,18 @@ struct PfParams {
     int padded_tokens;
     int tiles_n;                // row tiles
     int tiles;                  // row tiles x token tiles
-    int stages_per_tile;        // blocks / 2
     float *output;              // [tokens][rows]
-    int32_t *block_dots;        // optional [tokens][rows][blocks]
     int *status;
 };
 
 struct PfShared {
-    uint64_t full[kPfStages];           // TMA bytes of a stage have landed
+    uint64_t full[kPfStages];           // the stage's activation tile has landed
     uint64_t converted[kPfStages];      // binary16 weight tile written
     uint64_t empty[kPfStages];          // the stage's MMAs have finished reading
+    uint64_t raw_full[kPfRawBuffers];   // four blocks of raw int8 weights have landed
+    uint64_t raw_empty[kPfRawBuffers];  // and have been converted
     uint64_t tmem_full[4];
     uint64_t tmem_empty[4];
-    uint64_t scale_full[kPfChunks];
-    uint64_t scale_empty[kPfChunks];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -194,6 +207,37 @@ __device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&v)[16]) 
 __device__ __forceinline__ void tmem_load_slab(uint32_t taddr, uint32_t (&v)[32]) { tmem_load_32(taddr, v); }
 __device__ __forceinline__ void tmem_load_slab(uint32_t taddr, uint32_t (&v)[16]) { tmem_load_16(taddr, v); }
 
+// Bounded wait on an mbarrier phase, by shared-memory address: one probe and one branch
+// when the phase is already complete (the single-thread roles of this kernel are bound by
+// their own instruction count).  Returns false after 2^22 probes.
+__device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, 0;\n\t"
+        "PF_WAIT_LOOP:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra PF_WAIT_DONE;\n\t"
+        "add.u32 n, n, 1;\n\t"
+        "setp.lt.u32 p, n, 4194304;\n\t"
+        "@p bra PF_WAIT_LOOP;\n\t"
+        "setp.ne.u32 p, n, n;\n\t"
+        "PF_WAIT_DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+__device__ __forceinline__ void pf_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+                 ::"r"(bar) : "memory");
+}
+
 template <int REGS>
 __device__ __forceinline__ void regs_release() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS));
@@ -203,29 +247,38 @@ __device__ __forceinline__ void regs_claim() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS));
 }
 
-template <int TN, bool DOTS>
+// 16 bytes from global memory, issued where it stands (the compiler may not sink it to its
+// first use): the weight scales of the next eight blocks are requested a whole chunk ahead.
+__device__ __forceinline__ uint4 ldg_early_16(const void *address) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(address));
+    return v;
+}
+
+template <int TN>
 __global__ void __launch_bounds__(kPfThreads, 1)
 q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
-    const __grid_constant__ CUtensorMap act_map, const __grid_constant__ CUtensorMap scale_map,
-    const __grid_constant__ PfParams p) {
+    const __grid_constant__ CUtensorMap act_map, const __grid_constant__ PfParams p) {
     constexpr int kStageBytes = pf_stage_bytes(TN);
-    constexpr int kChunkBytes = pf_chunk_bytes(TN);
     constexpr int kBufs = pf_tmem_buffers(TN);
     constexpr int kBufStride = 512 / kBufs;             // TMEM columns per accumulator buffer
-    constexpr uint32_t kStageTx = kPfRawBytes + TN * kPfStageK * 2;
+    constexpr uint32_t kStageTx = TN * 128;
 
     extern __shared__ uint8_t pf_smem_raw[];
-    // [stages x (W16 16 KB | A16 TN*128 | raw 8 KB)] [scale chunks] [barriers]; swizzled
-    // tiles start on 1024-byte boundaries (the launch reserves the slack).
+    // [stages x (W16 16 KB | A TN*128)] [raw weights: 2 x 16 KB] [barriers]; swizzled tiles
+    // start on 1024-byte boundaries (the launch reserves the slack).
     uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
-    uint8_t *scale_base = smem + kPfStages * kStageBytes;
-    PfShared *sh = reinterpret_cast<PfShared *>(scale_base + kPfChunks * kChunkBytes);
+    uint8_t *raw_base = smem + kPfStages * kStageBytes;
+    PfShared *sh = reinterpret_cast<PfShared *>(raw_base + kPfRawBuffers * kPfRawBytes);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     volatile int *abort_flag = &sh->abort_flag;
 
-    const long long total_units = static_cast<long long>(p.tiles) * p.stages_per_tile;
+    // units: one Q8_0 block of one tile, numbered tile-major
+    const long long total_units = static_cast<long long>(p.tiles) * p.blocks;
     const long long unit_begin = mmq_unit_begin(total_units, gridDim.x, blockIdx.x);
     const long long unit_end = mmq_unit_begin(total_units, gridDim.x, blockIdx.x + 1);
     const int unit_count = static_cast<int>(unit_end - unit_begin);
@@ -233,16 +286,16 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPfStages; ++s) {
             mbar_init(&sh->full[s], 1);
-            mbar_init(&sh->converted[s], kPfEpilogueWarps);
+            mbar_init(&sh->converted[s], kPfConverterWarps);
             mbar_init(&sh->empty[s], 1);
+        }
+        for (int b = 0; b < kPfRawBuffers; ++b) {
+            mbar_init(&sh->raw_full[b], 1);
+            mbar_init(&sh->raw_empty[b], kPfConverterWarps);
         }
         for (int b = 0; b < 4; ++b) {
             mbar_init(&sh->tmem_full[b], 1);
             mbar_init(&sh->tmem_empty[b], kPfEpilogueWarps);
-        }
-        for (int c = 0; c < kPfChunks; ++c) {
-            mbar_init(&sh->scale_full[c], 1);
-            mbar_init(&sh->scale_empty[c], kPfEpilogueWarps);
         }
         sh->abort_flag = 0;
         mbar_fence_init();
@@ -252,146 +305,218 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    // everything above may run under the prepare kernel; the activation image, its scales
-    // and the zeroed split tiles are that kernel's output
+    // everything above may run under the prepare kernel; the activation image and the
+    // zeroed split tiles are that kernel's output
     grid_dependency_wait();
 
-    if (warp < 4) {
+    if (warp < kPfFrontWarps) {
         regs_release<kPfProducerRegs>();
         if (warp == 0) {
             // ------------------------------ TMA producer ------------------------------
+            // A tensor-map load costs this SM's copy engine about 500 cycles whatever its
+            // size, so the weights come four blocks at a time (128 rows x 128 bytes) and the
+            // activation tile, 256 rows of 128 bytes, is the one load per block.
             if (lane == 0) {
-                int armed = 0;          // stages armed so far (ring position)
-                int chunks = 0;         // scale chunks armed so far
-                bool failed = false;
-                for (long long u = unit_begin; u < unit_end && !failed;) {
-                    const int tile = static_cast<int>(u / p.stages_per_tile);
-                    const int first_stage = static_cast<int>(u -
-                        static_cast<long long>(tile) * p.stages_per_tile);
-                    const long long tile_end = static_cast<long long>(tile + 1) * p.stages_per_tile;
-                    const int count = static_cast<int>((tile_end < unit_end ? tile_end : unit_end) - u);
+                bool ok = true;
+                int chunks = 0;         // raw weight loads armed so far
+                int tile = static_cast<int>(unit_begin / p.blocks);
+                int kb = static_cast<int>(unit_begin - static_cast<long long>(tile) * p.blocks);
+                const uint32_t empty_bar = smem_u32(&sh->empty[0]);
+                const uint32_t raw_empty_bar = smem_u32(&sh->raw_empty[0]);
+                int armed = 0;
+                for (; armed < unit_count && ok; ++armed) {
                     const int row0 = (tile % p.tiles_n) * kPfTileRows;
                     const int token0 = (tile / p.tiles_n) * TN;
-                    for (int i = 0; i < count; ++i) {
-                        const int st = first_stage + i;
-                        const int kb = st * kPfStageBlocks;
-                        if (i == 0 || (kb & (kPfChunkBlocks - 1)) == 0) {
-                            const int c = chunks % kPfChunks;
-                            const int use = chunks / kPfChunks;
-                            if (use > 0 && !mbar_wait_bounded(&sh->scale_empty[c], (use - 1) & 1)) {
-                                atomicExch(p.status, kStatusMmqLoadTimeout);
-                                *abort_flag = 1;
-                                failed = true;
-                                break;
-                            }
-                            mbar_arrive_expect_tx(&sh->scale_full[c], kChunkBytes);
-                            tma_load_2d(scale_base + c * kChunkBytes, &scale_map, token0,
-                                kb & ~(kPfChunkBlocks - 1), &sh->scale_full[c]);
-                            ++chunks;
-                        }
-                        const int s = armed % kPfStages;
-                        const int use = armed / kPfStages;
-                        PF_STAMP(0, armed, 0);
-                        if (use > 0 && !mbar_wait_bounded(&sh->empty[s], (use - 1) & 1)) {
-                            atomicExch(p.status, kStatusMmqLoadTimeout);
-                            *abort_flag = 1;
-                            failed = true;
-                            break;
-                        }
-                        if (*abort_flag) {
-                            failed = true;
-                            break;
-                        }
-                        uint8_t *stage = smem + s * kStageBytes;
-                        mbar_arrive_expect_tx(&sh->full[s], kStageTx);
-                        tma_load_2d(stage + kPfW16Bytes + TN * kPfStageK * 2, &weights_map,
-                            st * kPfStageK, row0, &sh->full[s]);
-                        tma_load_2d(stage + kPfW16Bytes, &act_map, st * kPfStageK, token0,
-                            &sh->full[s]);
-                        PF_STAMP(0, armed, 1);
-                        ++armed;
+                    if (armed == 0 || (kb & (kPfRawBlocks - 1)) == 0) {
+                        const int rb = chunks % kPfRawBuffers;
+                        const int use = chunks / kPfRawBuffers;
+                        if (use > 0) ok = pf_wait(raw_empty_bar + 8 * rb, (use - 1) & 1);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&sh->raw_full[rb], kPfRawBytes);
+                        tma_load_2d(raw_base + rb * kPfRawBytes, &weights_map,
+                            (kb & ~(kPfRawBlocks - 1)) * kBlockElems, row0, &sh->raw_full[rb]);
+                        ++chunks;
                     }
-                    u += count;
+                    const int s = armed % kPfStages;
+                    const int use = armed / kPfStages;
+                    PF_STAMP(0, armed, 0);
+                    if (use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
+                    if (!ok) break;
+                    mbar_arrive_expect_tx(&sh->full[s], kStageTx);
+                    tma_load_2d(smem + s * kStageBytes + kPfW16Bytes, &act_map, kb * 64, token0,
+                        &sh->full[s]);
+                    PF_STAMP(0, armed, 1);
+                    if (++kb == p.blocks) {
+                        kb = 0;
+                        ++tile;
+                    }
                 }
-                if (failed || *abort_flag) {
+                if (!ok) {
+                    atomicExch(p.status, kStatusMmqLoadTimeout);
+                    *abort_flag = 1;
                     // let the loads that are still in flight land before the CTA ends
                     const int lap = armed < kPfStages ? armed : kPfStages;
                     for (int k = 0; k < lap; ++k) {
                         const int n = armed - 1 - k;
                         mbar_wait_bounded(&sh->full[n % kPfStages], (n / kPfStages) & 1, 1u << 16);
                     }
-                    const int clap = chunks < kPfChunks ? chunks : kPfChunks;
+                    const int clap = chunks < kPfRawBuffers ? chunks : kPfRawBuffers;
                     for (int k = 0; k < clap; ++k) {
                         const int n = chunks - 1 - k;
-                        mbar_wait_bounded(&sh->scale_full[n % kPfChunks], (n / kPfChunks) & 1,
-                            1u << 16);
+                        mbar_wait_bounded(&sh->raw_full[n % kPfRawBuffers],
+                            (n / kPfRawBuffers) & 1, 1u << 16);
                     }
                 }
             }
-        } else if (warp == 1) {
-            // ------------------------------ MMA issuer --------------------------------
+        } else if (warp == 1 || warp == 2) {
+            // ------------------------------ MMA issuers -------------------------------
+            // Two threads, one for the even and one for the odd blocks (they use disjoint
+            // stages and TMEM buffers): a single issuer needs about 850 cycles per block for
+            // its two waits, the fence, four MMAs and two commits, more than the 512 cycles
+            // the MMAs themselves take.  The stage ring is unrolled so that barrier addresses
+            // and operand descriptors are loop constants.
             if (lane == 0) {
-                const uint32_t idesc = pf_instr_desc(kPfTileRows, TN);
-                bool failed = false;
-                int issued = 0;         // blocks issued (TMEM ring position)
-                for (int consumed = 0; consumed < unit_count && !failed; ++consumed) {
-                    const int s = consumed % kPfStages;
-                    const uint32_t parity = (consumed / kPfStages) & 1;
-                    PF_STAMP(1, consumed, 0);
-                    if (!mbar_wait_bounded(&sh->full[s], parity)) {
-                        atomicExch(p.status, kStatusMmqLoadTimeout);
-                        *abort_flag = 1;
-                        break;
-                    }
-                    PF_STAMP(1, consumed, 1);
-                    if (!mbar_wait_bounded(&sh->converted[s], parity)) {
-                        atomicExch(p.status, kStatusMmqLoadTimeout);
-                        *abort_flag = 1;
-                        break;
-                    }
-                    tc_fence_after();
-                    PF_STAMP(1, consumed, 2);
-                    const uint8_t *stage = smem + s * kStageBytes;
-                    const uint64_t desc_w = smem_desc_k_major_sw128(stage);
-                    const uint64_t desc_a = smem_desc_k_major_sw128(stage + kPfW16Bytes);
+                constexpr uint32_t idesc = pf_instr_desc(kPfTileRows, TN);
+                static_assert(kPfStages % 2 == 0 && kBufs % 2 == 0 && kPfStages % kBufs == 0,
+                    "two issuers share the stage ring and the TMEM ring evenly");
+                const int issuer = warp - 1;
+                const uint32_t full_bar = smem_u32(&sh->full[0]);
+                const uint32_t converted_bar = smem_u32(&sh->converted[0]);
+                const uint32_t empty_bar = smem_u32(&sh->empty[0]);
+                const uint32_t tmem_full_bar = smem_u32(&sh->tmem_full[0]);
+                const uint32_t tmem_empty_bar = smem_u32(&sh->tmem_empty[0]);
+                const uint64_t desc_w0 = smem_desc_k_major_sw128(smem);
+                const uint64_t desc_a0 = smem_desc_k_major_sw128(smem + kPfW16Bytes);
+                bool ok = true;
+                for (int n0 = 0; n0 < unit_count && ok; n0 += kPfStages) {
+                    const uint32_t lap = static_cast<uint32_t>(n0 / kPfStages);
 #pragma unroll
-                    for (int j = 0; j < kPfStageBlocks; ++j, ++issued) {
-                        const int buf = issued % kBufs;
-                        const int use = issued / kBufs;
-                        if (use > 0) {
-                            if (!mbar_wait_bounded(&sh->tmem_empty[buf], (use - 1) & 1)) {
-                                atomicExch(p.status, kStatusMmqDrainTimeout);
-                                *abort_flag = 1;
-                                failed = true;
-                                break;
-                            }
-                            tc_fence_after();
-                        }
-                        if (*abort_flag) {
-                            failed = true;
+                    for (int j = 0; j < kPfStages / 2; ++j) {
+                        const int s = 2 * j + issuer;
+                        if (n0 + s >= unit_count || !ok) break;
+                        if (issuer == 0) PF_STAMP(1, (n0 + s) >> 1, 0);
+                        ok = pf_wait(full_bar + 8 * s, lap & 1) &&
+                            pf_wait(converted_bar + 8 * s, lap & 1);
+                        if (!ok) {
+                            atomicExch(p.status, kStatusMmqLoadTimeout);
                             break;
                         }
-                        // a block is 64 bytes of the 128-byte swizzled row: two K = 16 steps
-                        // of 32 bytes, +2 each in the descriptor's 16-byte units
+                        if (issuer == 0) PF_STAMP(1, (n0 + s) >> 1, 2);
+                        constexpr int kLapBufs = kPfStages / kBufs;     // uses of a buffer per lap
+                        const int buf = s % kBufs;
+                        const uint32_t use = lap * kLapBufs + s / kBufs;
+                        if (use > 0) {
+                            ok = pf_wait(tmem_empty_bar + 8 * buf, (use - 1) & 1);
+                            if (!ok) {
+                                atomicExch(p.status, kStatusMmqDrainTimeout);
+                                break;
+                            }
+                        }
+                        tc_fence_after();
+                        if (issuer == 0) PF_STAMP(1, (n0 + s) >> 1, 3);
+                        // stage s is s * kStageBytes further: the descriptor counts 16 bytes
+                        const uint64_t desc_w = desc_w0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
+                        const uint64_t desc_a = desc_a0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
                         const uint32_t d = tmem_base + buf * kBufStride;
-                        if (j == 0) PF_STAMP(1, consumed, 3);
-                        mma_f16(d, desc_w + 4 * j, desc_a + 4 * j, idesc, 0u);
-                        mma_f16(d, desc_w + 4 * j + 2, desc_a + 4 * j + 2, idesc, 1u);
-                        mma_commit(&sh->tmem_full[buf]);
+                        // the 128-byte operand rows are [w | w] and [hi | lo]: four K = 16 steps
+                        // of 32 bytes, +2 each in the descriptor's 16-byte units
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            mma_f16(d, desc_w + 2 * k, desc_a + 2 * k, idesc, k > 0 ? 1u : 0u);
+                        pf_commit(tmem_full_bar + 8 * buf);
+                        pf_commit(empty_bar + 8 * s);
+                        if (issuer == 0) PF_STAMP(1, (n0 + s) >> 1, 4);
                     }
-                    if (!failed) mma_commit(&sh->empty[s]);
-                    PF_STAMP(1, consumed, 4);
+                }
+                if (!ok) *abort_flag = 1;
+            }
+        } else if (warp >= kPfFrontWarps - kPfConverterWarps) {
+            // ------------------------------ weight converters -------------------------
+            // int8 -> binary16 of one block's weight tile (128 rows x 32 quants): 128 threads,
+            // two pieces of 16 raw bytes (half a row) each, every piece written twice, as
+            // the first and the second half of the row's 128 bytes ([w | w]: the tensor core
+            // multiplies the same weights with hi and with lo), in the 128-byte swizzled
+            // K-major layout.  The raw bytes sit in the same swizzle (four blocks per row).
+            constexpr int kConverters = kPfConverterWarps * 32;
+            constexpr int kPieces = kPfTileRows * 2 / kConverters;
+            const int ct = threadIdx.x - (kPfFrontWarps - kPfConverterWarps) * 32;
+            const uint32_t raw_full_bar = smem_u32(&sh->raw_full[0]);
+            const uint32_t empty_bar = smem_u32(&sh->empty[0]);
+            int tile = static_cast<int>(unit_begin / p.blocks);
+            int kb = static_cast<int>(unit_begin - static_cast<long long>(tile) * p.blocks);
+            int chunks = 0;         // raw weight loads taken so far
+            const uint8_t *raw = raw_base;
+            bool ok = true;
+            for (int n = 0; n < unit_count && ok; ++n) {
+                if (ct == 0) PF_STAMP(2, n, 0);
+                if (n == 0 || (kb & (kPfRawBlocks - 1)) == 0) {
+                    const int rb = chunks % kPfRawBuffers;
+                    ok = pf_wait(raw_full_bar + 8 * rb, (chunks / kPfRawBuffers) & 1);
+                    raw = raw_base + rb * kPfRawBytes;
+                    ++chunks;
+                }
+                const int s = n % kPfStages;
+                const int use = n / kPfStages;
+                // the stage's previous binary16 tile has been read by its MMAs
+                if (ok && use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
+                if (!ok) {
+                    if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                if (ct == 0) PF_STAMP(2, n, 1);
+                uint8_t *stage = smem + s * kStageBytes;
+                const int j = kb & (kPfRawBlocks - 1);
+                uint4 x[kPieces];
+#pragma unroll
+                for (int q = 0; q < kPieces; ++q) {
+                    const int piece = ct + kConverters * q;
+                    const int r = piece >> 1;
+                    const int c = piece & 1;        // which 16 of the block's 32 quants
+                    x[q] = *reinterpret_cast<const uint4 *>(raw + r * 128 +
+                        (((2 * j + c) ^ (r & 7)) << 4));
+                }
+#pragma unroll
+                for (int q = 0; q < kPieces; ++q) {
+                    const int piece = ct + kConverters * q;
+                    const int r = piece >> 1;
+                    const int c = piece & 1;
+                    uint4 h0, h1;
+                    widen4(x[q].x, h0.x, h0.y);
+                    widen4(x[q].y, h0.z, h0.w);
+                    widen4(x[q].z, h1.x, h1.y);
+                    widen4(x[q].w, h1.z, h1.w);
+                    // 128-byte swizzle: 16-byte chunk k of row r lives at chunk k ^ (r & 7)
+                    uint8_t *row = stage + r * 128;
+                    const int x7 = r & 7;
+                    *reinterpret_cast<uint4 *>(row + (((2 * c) ^ x7) << 4)) = h0;
+                    *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ x7) << 4)) = h1;
+                    *reinterpret_cast<uint4 *>(row + (((2 * c + 4) ^ x7) << 4)) = h0;
+                    *reinterpret_cast<uint4 *>(row + (((2 * c + 5) ^ x7) << 4)) = h1;
+                }
+                // generic-proxy writes must be visible to the tensor core's async-proxy reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&sh->converted[s]);
+                    // last block taken from this raw load: hand the buffer back
+                    if (j == kPfRawBlocks - 1 || kb == p.blocks - 1 || n == unit_count - 1)
+                        mbar_arrive(&sh->raw_empty[(chunks - 1) % kPfRawBuffers]);
+                }
+                if (ct == 0) PF_STAMP(2, n, 2);
+                if (++kb == p.blocks) {
+                    kb = 0;
+                    ++tile;
                 }
             }
         }
     } else {
-        // ---------------- weight conversion + epilogue (warps 4..) -------------------
+        // ------------------------------ drain ------------------------------------------
         regs_claim<kPfEpilogueRegs>();
-        const int ew = warp - 4;
-        const int et = threadIdx.x - 128;           // 0 .. 32 * kPfEpilogueWarps - 1
+        const int ew = warp - kPfFrontWarps;
+        const int et = threadIdx.x - kPfFrontWarps * 32;    // 0 .. 511
         const int quadrant = warp & 3;              // TMEM lanes this warp may touch
-        constexpr int kGroups = kPfEpilogueWarps / 4;
-        constexpr int kCols = TN / kGroups;         // token columns of this warp
+        constexpr int kCols = TN / 4;               // token columns of this warp
         constexpr int kSlab = kCols < kPfSlab ? kCols : kPfSlab;
         const int col0 = (ew >> 2) * kCols;
         constexpr int kPairs = kCols / 2;
@@ -399,58 +524,12 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
         constexpr int kP = kSlab / 2;
         unsigned long long acc[kPairs];             // fp32 accumulators, packed in pairs
         bool failed = false;
-        int drained = 0;        // accumulators drained (TMEM ring position)
-        int chunks = 0;         // scale chunks taken so far
-        int converted = 0;      // stages converted so far
 
-        // int8 -> binary16 of one stage's weight tile: 16 raw bytes (16 K of one row) per
-        // thread and step, into the 128-byte swizzled K-major tile the MMA reads.
-        auto convert_stage = [&]() -> bool {
-            const int s = converted % kPfStages;
-            if (et == 0) PF_STAMP(2, converted, 0);
-            if (!mbar_wait_bounded(&sh->full[s], (converted / kPfStages) & 1)) {
-                if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
-                *abort_flag = 1;
-                return false;
-            }
-            if (et == 0) PF_STAMP(2, converted, 1);
-            uint8_t *stage = smem + s * kStageBytes;
-            const uint8_t *raw = stage + kPfW16Bytes + TN * kPfStageK * 2;
-            constexpr int kUnits = kPfRawBytes / 16;
-            constexpr int kThreads = kPfEpilogueWarps * 32;
-#pragma unroll
-            for (int q = 0; q < kUnits / kThreads; ++q) {
-                const int unit = et + kThreads * q;
-                const int r = unit >> 2;
-                const int c16 = unit & 3;
-                const uint4 x = *reinterpret_cast<const uint4 *>(raw + r * kPfStageK + c16 * 16);
-                uint4 h0, h1;
-                widen4(x.x, h0.x, h0.y);
-                widen4(x.y, h0.z, h0.w);
-                widen4(x.z, h1.x, h1.y);
-                widen4(x.w, h1.z, h1.w);
-                // 128-byte swizzle: 16-byte chunk c of row r lives at chunk c ^ (r & 7)
-                uint8_t *row = stage + r * 128;
-                *reinterpret_cast<uint4 *>(row + (((2 * c16) ^ (r & 7)) << 4)) = h0;
-                *reinterpret_cast<uint4 *>(row + (((2 * c16 + 1) ^ (r & 7)) << 4)) = h1;
-            }
-            // generic-proxy writes must be visible to the tensor core's async-proxy reads
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sh->converted[s]);
-            if (et == 0) PF_STAMP(2, converted, 2);
-            ++converted;
-            return true;
-        };
-
-        // conversion runs two stages ahead of the drain
-        for (int k = 0; k < 2 && k < unit_count && !failed; ++k) failed = !convert_stage();
-
+        int drained = 0;        // blocks drained (TMEM ring position)
         for (long long u = unit_begin; u < unit_end && !failed;) {
-            const int tile = static_cast<int>(u / p.stages_per_tile);
-            const int first_stage = static_cast<int>(u - static_cast<long long>(tile) *
-                p.stages_per_tile);
-            const long long tile_end = static_cast<long long>(tile + 1) * p.stages_per_tile;
+            const int tile = static_cast<int>(u / p.blocks);
+            const int first_block = static_cast<int>(u - static_cast<long long>(tile) * p.blocks);
+            const long long tile_end = static_cast<long long>(tile + 1) * p.blocks;
             const int count = static_cast<int>((tile_end < unit_end ? tile_end : unit_end) - u);
             const int row0 = (tile % p.tiles_n) * kPfTileRows;
             const int token0 = (tile / p.tiles_n) * TN;
@@ -460,128 +539,92 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
 #pragma unroll
             for (int i = 0; i < kPairs; ++i) acc[i] = 0ull;
-            // the two fp16 weight scales of a stage are 4 aligned bytes of the row's scale
-            // plane, fetched one stage ahead
-            uint32_t dw_next = *reinterpret_cast<const uint32_t *>(scale_plane +
-                first_stage * kPfStageBlocks * 2);
-            int chunk = 0;
+            // the row's fp16 weight scales, eight blocks (16 aligned bytes) at a time and one
+            // chunk ahead; the scale plane is padded to a multiple of 32 bytes per row
+            uint4 dw_chunk = ldg_early_16(scale_plane + (first_block & ~7) * 2);
+            uint4 dw_ahead = dw_chunk;
 
-            for (int i = 0; i < count && !failed; ++i) {
-                const int st = first_stage + i;
-                const int kb = st * kPfStageBlocks;
-                if (i == 0 || (kb & (kPfChunkBlocks - 1)) == 0) {
-                    chunk = chunks % kPfChunks;
-                    if (!mbar_wait_bounded(&sh->scale_full[chunk], (chunks / kPfChunks) & 1)) {
-                        if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
-                        *abort_flag = 1;
-                        failed = true;
-                        break;
-                    }
-                    ++chunks;
+            for (int i = 0; i < count && !failed; ++i, ++drained) {
+                const int kb = first_block + i;
+                if ((kb & 7) == 0 || i == 0) {
+                    if (i > 0) dw_chunk = dw_ahead;
+                    const int next = (kb & ~7) + 8;
+                    if (next < p.blocks) dw_ahead = ldg_early_16(scale_plane + next * 2);
                 }
-                const uint32_t dw_pair = dw_next;
-                if (i + 1 < count)
-                    dw_next = *reinterpret_cast<const uint32_t *>(scale_plane +
-                        (st + 1) * kPfStageBlocks * 2);
-#pragma unroll
-                for (int j = 0; j < kPfStageBlocks; ++j, ++drained) {
-                    const int buf = drained % kBufs;
-                    const uint32_t parity = (drained / kBufs) & 1;
-                    const uint32_t taddr = tmem_base +
-                        (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kBufStride + col0;
-                    if (et == 0) PF_STAMP(3, drained, 0);
-                    if (!mbar_wait_bounded(&sh->tmem_full[buf], parity)) {
-                        if (lane == 0) atomicExch(p.status, kStatusMmqMmaTimeout);
-                        *abort_flag = 1;
-                        failed = true;
-                        break;
-                    }
-                    tc_fence_after();
-                    if (et == 0) PF_STAMP(3, drained, 1);
-                    const float dw = half_bits_to_float(
-                        static_cast<uint16_t>(j ? (dw_pair >> 16) : (dw_pair & 0xffffu)));
-                    const unsigned long long dw2 = pack2(dw, dw);
-                    const float *da_row = reinterpret_cast<const float *>(scale_base +
-                        chunk * kChunkBytes) + ((kb + j) & (kPfChunkBlocks - 1)) * TN + col0;
-                    // Slabs of kSlab columns; with two buffers the next slab is requested
-                    // before this one is worked on.  The accumulator buffer goes back to the
-                    // MMA warp as soon as the last slab has left TMEM.
-                    constexpr int kDepth = FORTAI_PF_SLAB_BUFFERS;
-                    uint32_t v[kDepth][kSlab];
-                    if (kDepth == 2) tmem_load_slab(taddr, v[0]);
-#pragma unroll
-                    for (int h = 0; h < kSlabs; ++h) {
-                        if (kDepth == 1) tmem_load_slab(taddr + kSlab * h, v[0]);
-                        tmem_load_wait();
-                        if (kDepth == 2 && h + 1 < kSlabs)
-                            tmem_load_slab(taddr + kSlab * (h + 1), v[(h + 1) & 1]);
-                        if (h + 1 == kSlabs) {
-                            tc_fence_before();
-                            __syncwarp();
-                            if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
-                            if (et == 0) PF_STAMP(3, drained, 2);
-                        }
-                        const uint32_t (&vv)[kSlab] = v[kDepth == 2 ? (h & 1) : 0];
-#ifndef FORTAI_PF_NO_MATH
-                        const ulonglong2 *da = reinterpret_cast<const ulonglong2 *>(da_row + kSlab * h);
-#pragma unroll
-                        for (int q = 0; q < kSlab / 4; ++q) {
-                            const ulonglong2 a = da[q];
-#ifdef FORTAI_PF_SCALAR
-                            float a0, a1, a2, a3, c0, c1, c2, c3;
-                            unpack2(a.x, a0, a1);
-                            unpack2(a.y, a2, a3);
-                            unpack2(acc[kP * h + 2 * q], c0, c1);
-                            unpack2(acc[kP * h + 2 * q + 1], c2, c3);
-                            c0 = fmaf(__uint_as_float(vv[4 * q]), dw * a0, c0);
-                            c1 = fmaf(__uint_as_float(vv[4 * q + 1]), dw * a1, c1);
-                            c2 = fmaf(__uint_as_float(vv[4 * q + 2]), dw * a2, c2);
-                            c3 = fmaf(__uint_as_float(vv[4 * q + 3]), dw * a3, c3);
-                            acc[kP * h + 2 * q] = pack2(c0, c1);
-                            acc[kP * h + 2 * q + 1] = pack2(c2, c3);
-#else
-                            acc[kP * h + 2 * q] = fma2(pack_bits(vv[4 * q], vv[4 * q + 1]),
-                                mul2(dw2, a.x), acc[kP * h + 2 * q]);
-                            acc[kP * h + 2 * q + 1] = fma2(pack_bits(vv[4 * q + 2], vv[4 * q + 3]),
-                                mul2(dw2, a.y), acc[kP * h + 2 * q + 1]);
-#endif
-                        }
-#else
-                        acc[h] ^= vv[0];
-#endif
-                        if (DOTS && row_ok) {
-#pragma unroll
-                            for (int e = 0; e < kSlab; ++e) {
-                                const int t0 = token0 + col0 + kSlab * h + e;
-                                if (t0 < p.tokens)
-                                    p.block_dots[(static_cast<size_t>(t0) * p.rows + row) *
-                                        p.blocks + kb + j] = __float2int_rn(__uint_as_float(vv[e]));
-                            }
-                        }
-                    }
-                    if (et == 0) PF_STAMP(3, drained, 3);
+                const int buf = drained % kBufs;
+                const uint32_t parity = (drained / kBufs) & 1;
+                const uint32_t taddr = tmem_base +
+                    (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kBufStride + col0;
+                if (et == 0) PF_STAMP(3, drained, 0);
+                if (!mbar_wait_bounded(&sh->tmem_full[buf], parity)) {
+                    if (lane == 0) atomicExch(p.status, kStatusMmqMmaTimeout);
+                    *abort_flag = 1;
+                    failed = true;
+                    break;
                 }
-                if (!failed && (((kb + kPfStageBlocks) & (kPfChunkBlocks - 1)) == 0 ||
-                        i == count - 1)) {
+                tc_fence_after();
+                if (et == 0) PF_STAMP_DRAIN(3, drained, 1);
+                const int k8 = kb & 7;
+                const uint32_t word = k8 < 2 ? dw_chunk.x : k8 < 4 ? dw_chunk.y
+                    : k8 < 6 ? dw_chunk.z : dw_chunk.w;
+                const float dw = half_bits_to_float(
+                    static_cast<uint16_t>((k8 & 1) ? (word >> 16) : (word & 0xffffu)));
+                const unsigned long long dw2 = pack2(dw, dw);
+                // Slabs of kSlab columns through two register buffers.  Both buffers are
+                // requested at once and each is requested again (two slabs further) as soon as
+                // its math is done, so the accumulator buffer goes back to the MMA warp after
+                // kSlabs - 2 slab maths instead of kSlabs - 1, and the last two overlap with
+                // the next block's MMAs.
+                auto slab_math = [&](const uint32_t (&vv)[kSlab], int h) {
+#pragma unroll
+                    for (int q = 0; q < kP; ++q)
+                        acc[kP * h + q] = fma2(pack_bits(vv[2 * q], vv[2 * q + 1]), dw2,
+                            acc[kP * h + q]);
+                };
+                auto release = [&]() {
+                    tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->scale_empty[chunk]);
+                    if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+                    if (et == 0) PF_STAMP_DRAIN(3, drained, 2);
+                };
+                if (kSlabs == 1) {
+                    uint32_t v0[kSlab];
+                    tmem_load_slab(taddr, v0);
+                    tmem_load_wait();
+                    release();
+                    slab_math(v0, 0);
+                } else {
+                    uint32_t v0[kSlab], v1[kSlab];
+                    tmem_load_slab(taddr, v0);
+                    tmem_load_slab(taddr + kSlab, v1);
+#pragma unroll
+                    for (int h = 0; h < kSlabs; h += 2) {
+                        tmem_load_wait();
+                        if (h + 2 >= kSlabs) release();
+                        slab_math(v0, h);
+                        if (h + 2 < kSlabs) tmem_load_slab(taddr + kSlab * (h + 2), v0);
+                        slab_math(v1, h + 1);
+                        if (h + 3 < kSlabs) tmem_load_slab(taddr + kSlab * (h + 3), v1);
+                    }
                 }
-                if (!failed && converted < unit_count) failed = !convert_stage();
+                if (et == 0) PF_STAMP(3, drained, 3);
             }
-            if (!failed && row_ok && p.output) {
-                const bool split = count != p.stages_per_tile;
+            if (!failed && row_ok) {
+                const bool split = count != p.blocks;
 #pragma unroll
                 for (int e = 0; e < kPairs; ++e) {
                     const int t = token0 + col0 + 2 * e;
                     float lo, hi;
                     unpack2(acc[e], lo, hi);
+                    // tokens beyond the batch are padding rows of the image (unscale 0)
+                    const float2 un = *reinterpret_cast<const float2 *>(p.unscale + t);
                     float *dst = p.output + static_cast<size_t>(t) * p.rows + row;
                     if (split) {
-                        if (t < p.tokens) atomicAdd(dst, lo);
-                        if (t + 1 < p.tokens) atomicAdd(dst + p.rows, hi);
+                        if (t < p.tokens) atomicAdd(dst, lo * un.x);
+                        if (t + 1 < p.tokens) atomicAdd(dst + p.rows, hi * un.y);
                     } else {
-                        if (t < p.tokens) *dst = lo;
-                        if (t + 1 < p.tokens) dst[p.rows] = hi;
+                        if (t < p.tokens) *dst = lo * un.x;
+                        if (t + 1 < p.tokens) dst[p.rows] = hi * un.y;
                     }
                 }
             }
@@ -597,77 +640,129 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     }
 }
 
-// ---- activation image of several tokens, quants widened to binary16 ---------------------
-// quants[token][width] binary16 and scales[block][padded_tokens] float for `padded_tokens`
-// rows (rows >= tokens are zero), from fp32 rows (ACT == 1: eight lanes per Q8_0 block, same
-// arithmetic and bytes as quantize_lane) or from GGUF Q8_0 rows (ACT == 0).  Also zeroes the
-// output of every split tile (their pieces arrive as atomic adds).
+// ---- activation image -----------------------------------------------------------------
+// One CTA per (padded) token.  Per Q8_0 block: the quantized activation exactly as the
+// reference makes it (src/backend/cpu/fortai_q8_dot.c:153-198: same arithmetic and bytes as
+// quantize_lane), then da * q split into hi + lo, both binary16, both multiplied by the
+// token's power of two 2^(7 - E), E the exponent of the token's largest block scale, so that
+// |hi| < 2^15 and lo keeps its bits down to 2^-24.  image[token][block] = [32 hi | 32 lo];
+// unscale[token] = 2^(E - 7) (0 for padding rows).  Also zeroes the output of every split
+// tile (their pieces arrive as atomic adds).
+__device__ __forceinline__ void pf_split_store(float value, float up, __half &hi, __half &lo) {
+    const float scaled = value * up;                        // exact: a power of two
+    hi = __float2half_rn(scaled);
+    lo = __float2half_rn(scaled - __half2float(hi));        // exact difference, fits binary16
+}
+
 template <int ACT>
 __global__ void __launch_bounds__(256)
 pf_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_tokens, int width,
-    __half *__restrict__ quants, float *__restrict__ scales, float *__restrict__ output, int rows,
-    int tile_tokens, int tiles_n, int tiles, int stages_per_tile, int product_grid) {
+    __half *__restrict__ image, float *__restrict__ unscale, float *__restrict__ output, int rows,
+    int tile_tokens, int tiles_n, int tiles, int product_grid) {
     grid_dependents_may_launch();
+    __shared__ float warp_max[8];
+    __shared__ float token_up;
     const int blocks = width / kBlockElems;
-    if (ACT == 1) {
-        const float4 *x4 = static_cast<const float4 *>(activation);
-        uint2 *q64 = reinterpret_cast<uint2 *>(quants);
-        const int groups = width >> 2;                       // float4 per token, 8 per block
-        const long long total = static_cast<long long>(padded_tokens) * groups;
-        const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
-        // warp-uniform trip count: the shuffles below need all 32 lanes
-        for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x; base < total;
-             base += stride) {
-            const long long at = base + threadIdx.x;
-            const bool valid = at < total;
-            const int token = valid ? static_cast<int>(at / groups) : 0;
-            const int g = valid ? static_cast<int>(at - static_cast<long long>(token) * groups) : 0;
-            float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            if (valid && token < tokens) v = x4[static_cast<size_t>(token) * groups + g];
-            float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            const float scale = __fdiv_rn(amax, 127.0f);
-            const float inverse = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
-            const int q0 = max(-128, min(127, __float2int_rn(__fmul_rn(v.x, inverse))));
-            const int q1 = max(-128, min(127, __float2int_rn(__fmul_rn(v.y, inverse))));
-            const int q2 = max(-128, min(127, __float2int_rn(__fmul_rn(v.z, inverse))));
-            const int q3 = max(-128, min(127, __float2int_rn(__fmul_rn(v.w, inverse))));
-            if (valid) {
-                const __half2 lo = __floats2half2_rn(static_cast<float>(q0), static_cast<float>(q1));
-                const __half2 hi = __floats2half2_rn(static_cast<float>(q2), static_cast<float>(q3));
-                q64[static_cast<size_t>(token) * groups + g] = make_uint2(
-                    *reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
-                if ((g & 7) == 0)
-                    scales[static_cast<size_t>(g >> 3) * padded_tokens + token] =
-                        half_bits_to_float(__half_as_ushort(__float2half_rn(scale)));
+    const int lane = threadIdx.x & 31;
+    for (int token = blockIdx.x; token < padded_tokens; token += gridDim.x) {
+        const bool real = token < tokens;
+        // pass 1: the largest block scale of the token
+        float scale_max = 0.0f;
+        if (real) {
+            if (ACT == 1) {
+                const float4 *x4 = static_cast<const float4 *>(activation) +
+                    static_cast<size_t>(token) * (width >> 2);
+                // eight lanes per block; warp-uniform trip count for the shuffles
+                for (int base = 0; base < (width >> 2); base += blockDim.x) {
+                    const int g = base + threadIdx.x;
+                    float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    if (g < (width >> 2)) v = x4[g];
+                    float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    scale_max = fmaxf(scale_max,
+                        __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f))));
+                }
+            } else {
+                const uint8_t *q8 = static_cast<const uint8_t *>(activation) +
+                    static_cast<size_t>(token) * blocks * kBlockBytes;
+                for (int b = threadIdx.x; b < blocks; b += blockDim.x)
+                    scale_max = fmaxf(scale_max, fabsf(half_bits_to_float(
+                        *reinterpret_cast<const uint16_t *>(q8 + static_cast<size_t>(b) * kBlockBytes))));
             }
         }
-    } else {
-        const int lane = threadIdx.x & 31;
-        const long long total = static_cast<long long>(padded_tokens) * blocks;
-        for (long long i = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5); i < total;
-             i += static_cast<long long>(gridDim.x) * 8) {
-            const int token = static_cast<int>(i / blocks);
-            const int b = static_cast<int>(i - static_cast<long long>(token) * blocks);
-            int q = 0;
-            float scale = 0.0f;
-            if (token < tokens) {
-                const uint8_t *block = static_cast<const uint8_t *>(activation) +
-                    (static_cast<size_t>(token) * blocks + b) * kBlockBytes;
-                q = static_cast<int8_t>(block[2 + lane]);
-                scale = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
+#pragma unroll
+        for (int offset = 16; offset; offset >>= 1)
+            scale_max = fmaxf(scale_max, __shfl_xor_sync(0xffffffffu, scale_max, offset));
+        __syncthreads();            // the previous token's token_up has been read by everyone
+        if (lane == 0) warp_max[threadIdx.x >> 5] = scale_max;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = 0.0f;
+            for (int w = 0; w < 8; ++w) m = fmaxf(m, warp_max[w]);
+            // E = exponent of m; binary16 scales lie in [2^-24, 2^16), infinities clamp
+            int e = m > 0.0f ? ((__float_as_int(m) >> 23) & 0xff) - 127 : 7;
+            e = max(-30, min(e, 30));
+            token_up = __int_as_float((127 + 7 - e) << 23);
+            unscale[token] = real ? __int_as_float((127 - 7 + e) << 23) : 0.0f;
+        }
+        __syncthreads();
+        const float up = token_up;
+        // pass 2: quantize again (same arithmetic), split, store
+        __half *row = image + static_cast<size_t>(token) * width * 2;
+        if (ACT == 1) {
+            const float4 *x4 = static_cast<const float4 *>(activation) +
+                static_cast<size_t>(token) * (width >> 2);
+            for (int base = 0; base < (width >> 2); base += blockDim.x) {
+                const int g = base + threadIdx.x;
+                const bool valid = g < (width >> 2);
+                float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (valid && real) v = x4[g];
+                float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                const float da = __half2float(__float2half_rn(__fdiv_rn(amax, 127.0f)));
+                const float inverse = amax != 0.0f ? __fdiv_rn(127.0f, amax) : 0.0f;
+                const float q0 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v.x, inverse)))));
+                const float q1 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v.y, inverse)))));
+                const float q2 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v.z, inverse)))));
+                const float q3 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v.w, inverse)))));
+                if (valid) {
+                    __half h[4], l[4];
+                    pf_split_store(__fmul_rn(da, q0), up, h[0], l[0]);
+                    pf_split_store(__fmul_rn(da, q1), up, h[1], l[1]);
+                    pf_split_store(__fmul_rn(da, q2), up, h[2], l[2]);
+                    pf_split_store(__fmul_rn(da, q3), up, h[3], l[3]);
+                    // block g / 8, elements 4 * (g % 8) .. + 3
+                    __half *block = row + (g >> 3) * 64 + (g & 7) * 4;
+                    *reinterpret_cast<uint2 *>(block) = *reinterpret_cast<const uint2 *>(h);
+                    *reinterpret_cast<uint2 *>(block + 32) = *reinterpret_cast<const uint2 *>(l);
+                }
             }
-            quants[static_cast<size_t>(token) * width + b * kBlockElems + lane] =
-                __float2half_rn(static_cast<float>(q));
-            if (lane == 0) scales[static_cast<size_t>(b) * padded_tokens + token] = scale;
+        } else {
+            const uint8_t *q8 = static_cast<const uint8_t *>(activation) +
+                static_cast<size_t>(token) * blocks * kBlockBytes;
+            for (int i = threadIdx.x; i < width; i += blockDim.x) {
+                const int b = i >> 5, k = i & 31;
+                float value = 0.0f;
+                if (real) {
+                    const uint8_t *block = q8 + static_cast<size_t>(b) * kBlockBytes;
+                    const float da = half_bits_to_float(*reinterpret_cast<const uint16_t *>(block));
+                    value = __fmul_rn(da, static_cast<float>(static_cast<int8_t>(block[2 + k])));
+                }
+                __half h, l;
+                pf_split_store(value, up, h, l);
+                row[b * 64 + k] = h;
+                row[b * 64 + 32 + k] = l;
+            }
         }
     }
     if (!output) return;
-    const long long total_units = static_cast<long long>(tiles) * stages_per_tile;
+    const long long total_units = static_cast<long long>(tiles) * blocks;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        if (!mmq_tile_is_split(total_units, product_grid, stages_per_tile, tile)) continue;
+        if (!mmq_tile_is_split(total_units, product_grid, blocks, tile)) continue;
         const int row0 = (tile % tiles_n) * kPfTileRows;
         const int token0 = (tile / tiles_n) * tile_tokens;
         for (int i = threadIdx.x; i < kPfTileRows * tile_tokens; i += blockDim.x) {
@@ -679,45 +774,33 @@ pf_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_to
 }
 
 // ---- host side ----------------------------------------------------------------
-// uint8 matrix `rows` x `width` bytes, row pitch `pitch`; boxes of 128 rows x 64 bytes, dense.
+// uint8 matrix `rows` x `width` bytes, row pitch `pitch`; boxes of 128 rows x 128 bytes
+// (four blocks), 128-byte swizzle.
 inline bool pf_make_raw_map(CUtensorMap *map, const void *base, int rows, int width, size_t pitch) {
     EncodeTiledFn encode = mmq_encode_fn();
     if (!encode) return false;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
-    const cuuint32_t box[2] = {kPfStageK, kPfTileRows};
+    const cuuint32_t box[2] = {kPfRawBlocks * kBlockElems, kPfTileRows};
     const cuuint32_t elem[2] = {1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides,
-               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
-        CUDA_SUCCESS;
-}
-
-// binary16 matrix `rows` x `width`, dense; boxes of `box_rows` rows x 64 elements, 128-byte swizzle.
-inline bool pf_make_act_map(CUtensorMap *map, const void *base, int rows, int width, int box_rows) {
-    EncodeTiledFn encode = mmq_encode_fn();
-    if (!encode) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(width) * 2};
-    const cuuint32_t box[2] = {kPfStageK, static_cast<cuuint32_t>(box_rows)};
-    const cuuint32_t elem[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides,
                box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
         CUDA_SUCCESS;
 }
 
-// fp32 matrix `rows` (blocks) x `cols` (tokens), dense; boxes of 8 rows x `box_cols`, no swizzle.
-inline bool pf_make_scale_map(CUtensorMap *map, const void *base, int rows, int cols, int box_cols) {
+// binary16 matrix `rows` x `2 * width`, dense; boxes of `box_rows` rows x 64 elements
+// (one block: 32 hi, 32 lo), 128-byte swizzle.
+inline bool pf_make_act_map(CUtensorMap *map, const void *base, int rows, int width, int box_rows) {
     EncodeTiledFn encode = mmq_encode_fn();
     if (!encode) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(float)};
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), kPfChunkBlocks};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(width) * 2, static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(width) * 4};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t elem[2] = {1, 1};
-    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims,
-               strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
+    return encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void *>(base), dims, strides,
+               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) ==
         CUDA_SUCCESS;
 }
 
@@ -734,13 +817,13 @@ inline cudaError_t pf_reserve(void **aux, size_t *aux_bytes, int width, int toke
 }
 
 inline size_t pf_smem_bytes(int tn) {
-    return static_cast<size_t>(kPfStages) * pf_stage_bytes(tn) +
-        static_cast<size_t>(kPfChunks) * pf_chunk_bytes(tn) + sizeof(PfShared) + 64 + 1024;
+    return static_cast<size_t>(kPfStages) * pf_stage_bytes(tn) + kPfRawBuffers * kPfRawBytes +
+        sizeof(PfShared) + 64 + 1024;
 }
 
-template <int TN, bool DOTS>
+template <int TN>
 inline cudaError_t pf_launch(const cudaLaunchConfig_t &config, const CUtensorMap &weights_map,
-    const CUtensorMap &act_map, const CUtensorMap &scale_map, const PfParams &p) {
+    const CUtensorMap &act_map, const PfParams &p) {
     static bool configured[16] = {};
     int device = 0;
     cudaGetDevice(&device);
@@ -749,42 +832,41 @@ inline cudaError_t pf_launch(const cudaLaunchConfig_t &config, const CUtensorMap
         // given the pool it redistributes; a build that allocates fewer registers per
         // thread would wait for registers that never come, so refuse it here.
         cudaFuncAttributes attributes;
-        cudaError_t error = cudaFuncGetAttributes(&attributes, q8_prefill_kernel<TN, DOTS>);
+        cudaError_t error = cudaFuncGetAttributes(&attributes, q8_prefill_kernel<TN>);
         if (error != cudaSuccess) return error;
-        if (attributes.numRegs * kPfThreads < 128 * kPfProducerRegs + 32 * kPfEpilogueWarps * kPfEpilogueRegs)
+        if (attributes.numRegs * kPfThreads <
+            32 * kPfFrontWarps * kPfProducerRegs + 32 * kPfEpilogueWarps * kPfEpilogueRegs)
             return cudaErrorLaunchOutOfResources;
-        error = cudaFuncSetAttribute(q8_prefill_kernel<TN, DOTS>,
+        error = cudaFuncSetAttribute(q8_prefill_kernel<TN>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pf_smem_bytes(TN)));
         if (error != cudaSuccess) return error;
         configured[device] = true;
     }
-    return cudaLaunchKernelEx(&config, q8_prefill_kernel<TN, DOTS>, weights_map, act_map,
-        scale_map, p);
+    return cudaLaunchKernelEx(&config, q8_prefill_kernel<TN>, weights_map, act_map, p);
 }
 
 // activation: fp32 [tokens][width] (act == 1) or Q8_0 blocks (act == 0), device memory.
 inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, PfWeightsPlan *plan,
     const uint8_t *weights, int rows, int width, int row_stride, const void *activation, int act,
-    int tokens, float *output, int32_t *block_dots, void **aux, size_t *aux_bytes,
-    uint64_t *launches) {
+    int tokens, float *output, void **aux, size_t *aux_bytes, uint64_t *launches) {
     const int blocks = width / kBlockElems;
     const int tn = pf_tile_tokens(tokens);
     const int padded = pf_padded_tokens(tokens);
     cudaError_t error = pf_reserve(aux, aux_bytes, width, tokens);
     if (error != cudaSuccess) return error;
-    __half *quants = static_cast<__half *>(*aux);
-    float *scales = reinterpret_cast<float *>(quants + static_cast<size_t>(padded) * width);
+    __half *image = static_cast<__half *>(*aux);
+    float *unscale = reinterpret_cast<float *>(image + static_cast<size_t>(padded) * width * 2);
     if (!plan->ready) {
         if (!pf_make_raw_map(&plan->weights_map, weights, rows, width, row_stride))
             return cudaErrorNotSupported;
         plan->ready = true;
     }
-    CUtensorMap act_map, scale_map;
-    if (!pf_make_act_map(&act_map, quants, padded, width, tn)) return cudaErrorNotSupported;
-    if (!pf_make_scale_map(&scale_map, scales, blocks, padded, tn)) return cudaErrorNotSupported;
+    CUtensorMap act_map;
+    if (!pf_make_act_map(&act_map, image, padded, width, tn)) return cudaErrorNotSupported;
 
     PfParams p = {};
     p.weights = weights;
+    p.unscale = unscale;
     p.rows = rows;
     p.width = width;
     p.blocks = blocks;
@@ -793,23 +875,18 @@ inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, Pf
     p.padded_tokens = padded;
     p.tiles_n = (rows + kPfTileRows - 1) / kPfTileRows;
     p.tiles = p.tiles_n * (padded / tn);
-    p.stages_per_tile = blocks / kPfStageBlocks;
     p.output = output;
-    p.block_dots = block_dots;
     p.status = status;
-    const long long total_units = static_cast<long long>(p.tiles) * p.stages_per_tile;
+    const long long total_units = static_cast<long long>(p.tiles) * blocks;
     const int grid = static_cast<int>(std::min<long long>(sm_count, total_units));
     {
-        const long long work = act == 1 ? static_cast<long long>(padded) * (width / 4) / 256
-                                        : static_cast<long long>(padded) * blocks / 8;
-        const int prep_grid = static_cast<int>(std::max<long long>(1,
-            std::min<long long>(work + 1, static_cast<long long>(sm_count) * 8)));
+        const int prep_grid = std::min(padded, sm_count * 8);
         if (act == 1)
             pf_prepare_kernel<1><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
-                quants, scales, output, rows, tn, p.tiles_n, p.tiles, p.stages_per_tile, grid);
+                image, unscale, output, rows, tn, p.tiles_n, p.tiles, grid);
         else
             pf_prepare_kernel<0><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
-                quants, scales, output, rows, tn, p.tiles_n, p.tiles, p.stages_per_tile, grid);
+                image, unscale, output, rows, tn, p.tiles_n, p.tiles, grid);
         ++*launches;
         error = cudaGetLastError();
         if (error != cudaSuccess) return error;
@@ -825,16 +902,9 @@ inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, Pf
     overlap.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &overlap;
     config.numAttrs = 1;
-    const bool dots = block_dots != nullptr;
-    if (tn == 256)
-        error = dots ? pf_launch<256, true>(config, plan->weights_map, act_map, scale_map, p)
-                     : pf_launch<256, false>(config, plan->weights_map, act_map, scale_map, p);
-    else if (tn == 128)
-        error = dots ? pf_launch<128, true>(config, plan->weights_map, act_map, scale_map, p)
-                     : pf_launch<128, false>(config, plan->weights_map, act_map, scale_map, p);
-    else
-        error = dots ? pf_launch<64, true>(config, plan->weights_map, act_map, scale_map, p)
-                     : pf_launch<64, false>(config, plan->weights_map, act_map, scale_map, p);
+    if (tn == 256) error = pf_launch<256>(config, plan->weights_map, act_map, p);
+    else if (tn == 128) error = pf_launch<128>(config, plan->weights_map, act_map, p);
+    else error = pf_launch<64>(config, plan->weights_map, act_map, p);
     if (error != cudaSuccess) return error;
     ++*launches;
     return cudaGetLastError();
