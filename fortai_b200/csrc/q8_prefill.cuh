@@ -33,12 +33,13 @@
 // for long prompts (an MMA takes 128 cycles whatever N is, so N = 256 is the only shape at
 // full rate), 128 or 64 for short ones.
 //
-//   warp 0        TMA producer: per stage (one block) the activation tile (TN x [32 hi |
-//                 32 lo] binary16, 128-byte swizzle); per four blocks the raw int8 weight
-//                 tile (128 rows x 128 bytes)
+//   warps 0, 3    TMA producers (even / odd blocks): per block the CTA's half of the
+//                 activation tile (TN/2 x [32 hi | 32 lo] binary16, 128-byte swizzle); per
+//                 four blocks the raw int8 weight tile (128 rows x 128 bytes)
 //   warps 1, 2    MMA issue (one elected thread each, even / odd blocks), commits; warp 1
 //                 also owns the TMEM allocation
-//   warps 4..7    int8 -> binary16 of the weight tile into the swizzled K-major operand tile
+//   warps 4..7    int8 -> binary16 of the weight tile into the swizzled K-major operand
+//                 tile, each warp every fourth block
 //   warps 8..23   the drain: warp w owns TMEM lanes 32*(w%4).. and a quarter of the token
 //                 columns
 //
@@ -56,11 +57,11 @@
 
 namespace fortai_b200 {
 
-#ifndef FORTAI_PF_STAGES
-#define FORTAI_PF_STAGES 4
-#endif
 #ifndef FORTAI_PF_PRODUCER_REGS
 #define FORTAI_PF_PRODUCER_REGS 48
+#endif
+#ifndef FORTAI_PF_CONVERTER_REGS
+#define FORTAI_PF_CONVERTER_REGS 48
 #endif
 #ifndef FORTAI_PF_EPILOGUE_REGS
 #define FORTAI_PF_EPILOGUE_REGS 96
@@ -68,17 +69,16 @@ namespace fortai_b200 {
 #ifndef FORTAI_PF_SLAB
 #define FORTAI_PF_SLAB 16
 #endif
-#ifndef FORTAI_PF_SLAB_BUFFERS
-#define FORTAI_PF_SLAB_BUFFERS 2
-#endif
 
-constexpr int kPfTileRows = 128;
-constexpr int kPfStages = FORTAI_PF_STAGES;
+constexpr int kPfTileRows = 128;            // weight rows per CTA (TMEM lanes)
+constexpr int kPfPairRows = 256;            // weight rows per CTA pair (MMA M with cta_group::2)
+constexpr int kPfMaxStages = 8;
 constexpr int kPfEpilogueWarps = 16;        // 4 TMEM lane quadrants x 4 column groups
 constexpr int kPfFrontWarps = 8;            // producer, two MMA issuers, a spare, four converters
 constexpr int kPfConverterWarps = 4;
 constexpr int kPfThreads = (kPfFrontWarps + kPfEpilogueWarps) * 32;
 constexpr int kPfProducerRegs = FORTAI_PF_PRODUCER_REGS;   // per thread of the first warpgroup after the hand-over
+constexpr int kPfConverterRegs = FORTAI_PF_CONVERTER_REGS; // of the converter warpgroup
 constexpr int kPfEpilogueRegs = FORTAI_PF_EPILOGUE_REGS;   // and of the drain warpgroups
 constexpr int kPfSlab = FORTAI_PF_SLAB;                    // TMEM columns per tcgen05.ld
 constexpr int kPfRawBlocks = 4;                            // blocks per raw weight load (128 bytes of every row)
@@ -86,10 +86,13 @@ constexpr int kPfRawBytes = kPfTileRows * kPfRawBlocks * kBlockElems;
 constexpr int kPfRawBuffers = 2;
 constexpr int kPfW16Bytes = kPfTileRows * 128;             // binary16, each row [w | w]: 128 bytes
 
+// a CTA holds its 128 weight rows and its half of the pair's token tile
 __host__ __device__ constexpr int pf_stage_bytes(int tn) {
-    return kPfW16Bytes + tn * 128;
+    return kPfW16Bytes + (tn / 2) * 128;
 }
 __host__ __device__ constexpr int pf_tmem_buffers(int tn) { return tn >= 256 ? 2 : 4; }
+// shared-memory ring: as deep as fits (a tensor-map load takes well over a thousand cycles to land)
+__host__ __device__ constexpr int pf_stages(int tn) { return tn >= 256 ? 6 : 8; }
 
 inline int pf_tile_tokens(int tokens) { return tokens <= 64 ? 64 : tokens <= 128 ? 128 : 256; }
 
@@ -147,9 +150,9 @@ struct PfParams {
 };
 
 struct PfShared {
-    uint64_t full[kPfStages];           // the stage's activation tile has landed
-    uint64_t converted[kPfStages];      // binary16 weight tile written
-    uint64_t empty[kPfStages];          // the stage's MMAs have finished reading
+    uint64_t full[kPfMaxStages];           // the stage's activation tile has landed
+    uint64_t converted[kPfMaxStages];      // binary16 weight tile written
+    uint64_t empty[kPfMaxStages];          // the stage's MMAs have finished reading
     uint64_t raw_full[kPfRawBuffers];   // four blocks of raw int8 weights have landed
     uint64_t raw_empty[kPfRawBuffers];  // and have been converted
     uint64_t tmem_full[4];
@@ -169,6 +172,64 @@ __device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64
         "}\n"
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+
+// The same for a CTA pair: issued by one thread of the leader CTA, executed by both tensor
+// cores; each CTA contributes its 128 rows of A and its half of B from its own shared memory
+// (the descriptors are offsets valid in both) and keeps its 128 rows of D in its own TMEM.
+__device__ __forceinline__ void mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+    uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrive, once every MMA issued so far by this thread has finished, on the barrier at this
+// offset in both CTAs of the pair.
+__device__ __forceinline__ void pf_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+        " [%0], %1;"
+        ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t *smem_result, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(smem_result)), "r"(columns) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t base, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(base), "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    return rank;
+}
+
+// All threads of both CTAs of the pair.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\t"
+                 "barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive on the barrier at this shared-memory offset in CTA `rank` of the pair.
+__device__ __forceinline__ void mbar_arrive_in_cta(uint32_t bar, uint32_t rank) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 remote;\n\t"
+        "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+        "mbarrier.arrive.shared::cluster.b64 _, [remote];\n\t"
+        "}"
+        ::"r"(bar), "r"(rank) : "memory");
 }
 
 // Instruction descriptor of kind::f16: D = f32, A = B = f16, both K-major.
@@ -209,7 +270,7 @@ __device__ __forceinline__ void tmem_load_slab(uint32_t taddr, uint32_t (&v)[16]
 
 // Bounded wait on an mbarrier phase, by shared-memory address: one probe and one branch
 // when the phase is already complete (the single-thread roles of this kernel are bound by
-// their own instruction count).  Returns false after 2^22 probes.
+// their own instruction count).  Returns false after 2^20 probes.
 __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
@@ -221,7 +282,7 @@ __device__ __forceinline__ bool pf_wait(uint32_t bar, uint32_t parity) {
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "@p bra PF_WAIT_DONE;\n\t"
         "add.u32 n, n, 1;\n\t"
-        "setp.lt.u32 p, n, 4194304;\n\t"
+        "setp.lt.u32 p, n, 1048576;\n\t"
         "@p bra PF_WAIT_LOOP;\n\t"
         "setp.ne.u32 p, n, n;\n\t"
         "PF_WAIT_DONE:\n\t"
@@ -262,12 +323,13 @@ __global__ void __launch_bounds__(kPfThreads, 1)
 q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     const __grid_constant__ CUtensorMap act_map, const __grid_constant__ PfParams p) {
     constexpr int kStageBytes = pf_stage_bytes(TN);
+    constexpr int kPfStages = pf_stages(TN);
     constexpr int kBufs = pf_tmem_buffers(TN);
     constexpr int kBufStride = 512 / kBufs;             // TMEM columns per accumulator buffer
-    constexpr uint32_t kStageTx = TN * 128;
+    constexpr uint32_t kStageTx = (TN / 2) * 128;
 
     extern __shared__ uint8_t pf_smem_raw[];
-    // [stages x (W16 16 KB | A TN*128)] [raw weights: 2 x 16 KB] [barriers]; swizzled tiles
+    // [stages x (W16 16 KB | A TN/2*128)] [raw weights: 2 x 16 KB] [barriers]; swizzled tiles
     // start on 1024-byte boundaries (the launch reserves the slack).
     uint8_t *smem = pf_smem_raw + ((1024u - (smem_u32(pf_smem_raw) & 1023u)) & 1023u);
     uint8_t *raw_base = smem + kPfStages * kStageBytes;
@@ -277,16 +339,21 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     const int lane = threadIdx.x & 31;
     volatile int *abort_flag = &sh->abort_flag;
 
-    // units: one Q8_0 block of one tile, numbered tile-major
+    // The two CTAs of a cluster work on the same units: one Q8_0 block of one pair tile (256
+    // weight rows x TN tokens), numbered tile-major.  CTA `rank` owns weight rows 128 * rank ..
+    // of the tile and supplies tokens TN/2 * rank .. of the activation operand.
+    const uint32_t rank = cluster_cta_rank();
+    const int pair = blockIdx.x >> 1;
+    const int pairs = gridDim.x >> 1;
     const long long total_units = static_cast<long long>(p.tiles) * p.blocks;
-    const long long unit_begin = mmq_unit_begin(total_units, gridDim.x, blockIdx.x);
-    const long long unit_end = mmq_unit_begin(total_units, gridDim.x, blockIdx.x + 1);
+    const long long unit_begin = mmq_unit_begin(total_units, pairs, pair);
+    const long long unit_end = mmq_unit_begin(total_units, pairs, pair + 1);
     const int unit_count = static_cast<int>(unit_end - unit_begin);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPfStages; ++s) {
             mbar_init(&sh->full[s], 1);
-            mbar_init(&sh->converted[s], kPfConverterWarps);
+            mbar_init(&sh->converted[s], 2);   // one converter warp of each CTA
             mbar_init(&sh->empty[s], 1);
         }
         for (int b = 0; b < kPfRawBuffers; ++b) {
@@ -295,14 +362,15 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
         }
         for (int b = 0; b < 4; ++b) {
             mbar_init(&sh->tmem_full[b], 1);
-            mbar_init(&sh->tmem_empty[b], kPfEpilogueWarps);
+            mbar_init(&sh->tmem_empty[b], 2 * kPfEpilogueWarps);   // both CTAs' drain warps
         }
         sh->abort_flag = 0;
         mbar_fence_init();
     }
-    if (warp == 1) tmem_alloc(&sh->tmem_base, 512);
+    if (warp == 1) tmem_alloc_pair(&sh->tmem_base, 512);
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();         // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
     // everything above may run under the prepare kernel; the activation image and the
@@ -310,13 +378,16 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     grid_dependency_wait();
 
     if (warp < kPfFrontWarps) {
-        regs_release<kPfProducerRegs>();
-        if (warp == 0) {
-            // ------------------------------ TMA producer ------------------------------
-            // A tensor-map load costs this SM's copy engine about 500 cycles whatever its
-            // size, so the weights come four blocks at a time (128 rows x 128 bytes) and the
-            // activation tile, 256 rows of 128 bytes, is the one load per block.
+        if (warp < 4) regs_release<kPfProducerRegs>();
+        else regs_release<kPfConverterRegs>();
+        if (warp == 0 || warp == 3) {
+            // ------------------------------ TMA producers -----------------------------
+            // A tensor-map load holds the thread that issues it for about 500 cycles whatever
+            // its size, about as long as a block's MMAs take: two threads issue, one the even
+            // and one the odd blocks, and the weights come four blocks at a time (128 rows x
+            // 128 bytes; issued by whichever thread owns the block that starts the four).
             if (lane == 0) {
+                const int producer = warp == 0 ? 0 : 1;
                 bool ok = true;
                 int chunks = 0;         // raw weight loads armed so far
                 int tile = static_cast<int>(unit_begin / p.blocks);
@@ -325,27 +396,32 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const uint32_t raw_empty_bar = smem_u32(&sh->raw_empty[0]);
                 int armed = 0;
                 for (; armed < unit_count && ok; ++armed) {
-                    const int row0 = (tile % p.tiles_n) * kPfTileRows;
-                    const int token0 = (tile / p.tiles_n) * TN;
+                    const bool mine = (armed & 1) == producer;
+                    const int row0 = (tile % p.tiles_n) * kPfPairRows + rank * kPfTileRows;
+                    const int token0 = (tile / p.tiles_n) * TN + rank * (TN / 2);
                     if (armed == 0 || (kb & (kPfRawBlocks - 1)) == 0) {
-                        const int rb = chunks % kPfRawBuffers;
-                        const int use = chunks / kPfRawBuffers;
-                        if (use > 0) ok = pf_wait(raw_empty_bar + 8 * rb, (use - 1) & 1);
-                        if (!ok) break;
-                        mbar_arrive_expect_tx(&sh->raw_full[rb], kPfRawBytes);
-                        tma_load_2d(raw_base + rb * kPfRawBytes, &weights_map,
-                            (kb & ~(kPfRawBlocks - 1)) * kBlockElems, row0, &sh->raw_full[rb]);
+                        if (mine) {
+                            const int rb = chunks % kPfRawBuffers;
+                            const int use = chunks / kPfRawBuffers;
+                            if (use > 0) ok = pf_wait(raw_empty_bar + 8 * rb, (use - 1) & 1);
+                            if (!ok) break;
+                            mbar_arrive_expect_tx(&sh->raw_full[rb], kPfRawBytes);
+                            tma_load_2d(raw_base + rb * kPfRawBytes, &weights_map,
+                                (kb & ~(kPfRawBlocks - 1)) * kBlockElems, row0, &sh->raw_full[rb]);
+                        }
                         ++chunks;
                     }
-                    const int s = armed % kPfStages;
-                    const int use = armed / kPfStages;
-                    PF_STAMP(0, armed, 0);
-                    if (use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
-                    if (!ok) break;
-                    mbar_arrive_expect_tx(&sh->full[s], kStageTx);
-                    tma_load_2d(smem + s * kStageBytes + kPfW16Bytes, &act_map, kb * 64, token0,
-                        &sh->full[s]);
-                    PF_STAMP(0, armed, 1);
+                    if (mine) {
+                        const int s = armed % kPfStages;
+                        const int use = armed / kPfStages;
+                        if (producer == 0) PF_STAMP(0, armed >> 1, 0);
+                        if (use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
+                        if (!ok) break;
+                        mbar_arrive_expect_tx(&sh->full[s], kStageTx);
+                        tma_load_2d(smem + s * kStageBytes + kPfW16Bytes, &act_map, kb * 64,
+                            token0, &sh->full[s]);
+                        if (producer == 0) PF_STAMP(0, armed >> 1, 1);
+                    }
                     if (++kb == p.blocks) {
                         kb = 0;
                         ++tile;
@@ -375,8 +451,8 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
             // its two waits, the fence, four MMAs and two commits, more than the 512 cycles
             // the MMAs themselves take.  The stage ring is unrolled so that barrier addresses
             // and operand descriptors are loop constants.
-            if (lane == 0) {
-                constexpr uint32_t idesc = pf_instr_desc(kPfTileRows, TN);
+            if (lane == 0 && rank == 0) {
+                constexpr uint32_t idesc = pf_instr_desc(kPfPairRows, TN);
                 static_assert(kPfStages % 2 == 0 && kBufs % 2 == 0 && kPfStages % kBufs == 0,
                     "two issuers share the stage ring and the TMEM ring evenly");
                 const int issuer = warp - 1;
@@ -385,8 +461,14 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const uint32_t empty_bar = smem_u32(&sh->empty[0]);
                 const uint32_t tmem_full_bar = smem_u32(&sh->tmem_full[0]);
                 const uint32_t tmem_empty_bar = smem_u32(&sh->tmem_empty[0]);
+                // descriptors differ only in their low word (the start address in 16-byte
+                // units); keeping that word and building each descriptor where it is used
+                // keeps this thread inside its small register budget
                 const uint64_t desc_w0 = smem_desc_k_major_sw128(smem);
-                const uint64_t desc_a0 = smem_desc_k_major_sw128(smem + kPfW16Bytes);
+                const uint32_t desc_hi = static_cast<uint32_t>(desc_w0 >> 32);
+                const uint32_t w_lo0 = static_cast<uint32_t>(desc_w0);
+                const uint32_t a_lo0 = static_cast<uint32_t>(
+                    smem_desc_k_major_sw128(smem + kPfW16Bytes));
                 bool ok = true;
                 for (int n0 = 0; n0 < unit_count && ok; n0 += kPfStages) {
                     const uint32_t lap = static_cast<uint32_t>(n0 / kPfStages);
@@ -415,16 +497,17 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                         tc_fence_after();
                         if (issuer == 0) PF_STAMP(1, (n0 + s) >> 1, 3);
                         // stage s is s * kStageBytes further: the descriptor counts 16 bytes
-                        const uint64_t desc_w = desc_w0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
-                        const uint64_t desc_a = desc_a0 + static_cast<uint64_t>(s * (kStageBytes >> 4));
+                        const uint32_t w_lo = w_lo0 + s * (kStageBytes >> 4);
+                        const uint32_t a_lo = a_lo0 + s * (kStageBytes >> 4);
                         const uint32_t d = tmem_base + buf * kBufStride;
                         // the 128-byte operand rows are [w | w] and [hi | lo]: four K = 16 steps
                         // of 32 bytes, +2 each in the descriptor's 16-byte units
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
-                            mma_f16(d, desc_w + 2 * k, desc_a + 2 * k, idesc, k > 0 ? 1u : 0u);
-                        pf_commit(tmem_full_bar + 8 * buf);
-                        pf_commit(empty_bar + 8 * s);
+                            mma_f16_pair(d, pack_bits(w_lo + 2 * k, desc_hi),
+                                pack_bits(a_lo + 2 * k, desc_hi), idesc, k > 0 ? 1u : 0u);
+                        pf_commit_pair(tmem_full_bar + 8 * buf);
+                        pf_commit_pair(empty_bar + 8 * s);
                         if (issuer == 0) PF_STAMP(1, (n0 + s) >> 1, 4);
                     }
                 }
@@ -432,78 +515,102 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
             }
         } else if (warp >= kPfFrontWarps - kPfConverterWarps) {
             // ------------------------------ weight converters -------------------------
-            // int8 -> binary16 of one block's weight tile (128 rows x 32 quants): 128 threads,
-            // two pieces of 16 raw bytes (half a row) each, every piece written twice, as
+            // int8 -> binary16 of one block's weight tile (128 rows x 32 quants).  Four warps,
+            // each takes every fourth block whole: the waits, the proxy fence and the arrivals
+            // of a block cost a warp about as much as the conversion itself, and a warp that
+            // owns one block in four pays them once per four block times.  A thread converts
+            // eight pieces of 16 raw bytes (half a row each) and writes every piece twice, as
             // the first and the second half of the row's 128 bytes ([w | w]: the tensor core
             // multiplies the same weights with hi and with lo), in the 128-byte swizzled
             // K-major layout.  The raw bytes sit in the same swizzle (four blocks per row).
-            constexpr int kConverters = kPfConverterWarps * 32;
-            constexpr int kPieces = kPfTileRows * 2 / kConverters;
-            const int ct = threadIdx.x - (kPfFrontWarps - kPfConverterWarps) * 32;
+            const int cw = warp - (kPfFrontWarps - kPfConverterWarps);     // 0..3
             const uint32_t raw_full_bar = smem_u32(&sh->raw_full[0]);
             const uint32_t empty_bar = smem_u32(&sh->empty[0]);
+            const uint32_t full_bar = smem_u32(&sh->full[0]);
+            const uint32_t converted_bar = smem_u32(&sh->converted[0]);
             int tile = static_cast<int>(unit_begin / p.blocks);
             int kb = static_cast<int>(unit_begin - static_cast<long long>(tile) * p.blocks);
-            int chunks = 0;         // raw weight loads taken so far
-            const uint8_t *raw = raw_base;
+            int chunks = 0;             // raw weight loads seen so far
+            bool own_in_chunk = false;  // this warp has converted a block of the current load
             bool ok = true;
             for (int n = 0; n < unit_count && ok; ++n) {
-                if (ct == 0) PF_STAMP(2, n, 0);
+                const bool mine = (n & (kPfConverterWarps - 1)) == cw;
                 if (n == 0 || (kb & (kPfRawBlocks - 1)) == 0) {
-                    const int rb = chunks % kPfRawBuffers;
-                    ok = pf_wait(raw_full_bar + 8 * rb, (chunks / kPfRawBuffers) & 1);
-                    raw = raw_base + rb * kPfRawBytes;
                     ++chunks;
+                    own_in_chunk = false;
                 }
-                const int s = n % kPfStages;
-                const int use = n / kPfStages;
-                // the stage's previous binary16 tile has been read by its MMAs
-                if (ok && use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
-                if (!ok) {
-                    if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
-                    *abort_flag = 1;
-                    break;
-                }
-                if (ct == 0) PF_STAMP(2, n, 1);
-                uint8_t *stage = smem + s * kStageBytes;
+                const int rb = (chunks - 1) % kPfRawBuffers;
+                const uint32_t raw_parity = ((chunks - 1) / kPfRawBuffers) & 1;
                 const int j = kb & (kPfRawBlocks - 1);
-                uint4 x[kPieces];
+                const bool chunk_last = j == kPfRawBlocks - 1 || kb == p.blocks - 1 ||
+                    n == unit_count - 1;
+                if (mine) {
+                    if (cw == 0) PF_STAMP(2, n >> 2, 0);
+                    const int s = n % kPfStages;
+                    const int use = n / kPfStages;
+                    ok = pf_wait(raw_full_bar + 8 * rb, raw_parity);
+                    // the stage's previous binary16 tile has been read by its MMAs
+                    if (ok && use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
+                    if (!ok) {
+                        if (lane == 0) atomicExch(p.status, kStatusMmqLoadTimeout);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    if (cw == 0) PF_STAMP(2, n >> 2, 1);
+                    uint8_t *stage = smem + s * kStageBytes;
+                    const uint8_t *raw = raw_base + rb * kPfRawBytes;
 #pragma unroll
-                for (int q = 0; q < kPieces; ++q) {
-                    const int piece = ct + kConverters * q;
-                    const int r = piece >> 1;
-                    const int c = piece & 1;        // which 16 of the block's 32 quants
-                    x[q] = *reinterpret_cast<const uint4 *>(raw + r * 128 +
-                        (((2 * j + c) ^ (r & 7)) << 4));
-                }
+                    for (int half = 0; half < 2; ++half) {
+                        uint4 x[4];
 #pragma unroll
-                for (int q = 0; q < kPieces; ++q) {
-                    const int piece = ct + kConverters * q;
-                    const int r = piece >> 1;
-                    const int c = piece & 1;
-                    uint4 h0, h1;
-                    widen4(x[q].x, h0.x, h0.y);
-                    widen4(x[q].y, h0.z, h0.w);
-                    widen4(x[q].z, h1.x, h1.y);
-                    widen4(x[q].w, h1.z, h1.w);
-                    // 128-byte swizzle: 16-byte chunk k of row r lives at chunk k ^ (r & 7)
-                    uint8_t *row = stage + r * 128;
-                    const int x7 = r & 7;
-                    *reinterpret_cast<uint4 *>(row + (((2 * c) ^ x7) << 4)) = h0;
-                    *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ x7) << 4)) = h1;
-                    *reinterpret_cast<uint4 *>(row + (((2 * c + 4) ^ x7) << 4)) = h0;
-                    *reinterpret_cast<uint4 *>(row + (((2 * c + 5) ^ x7) << 4)) = h1;
+                        for (int q = 0; q < 4; ++q) {
+                            const int piece = lane + 32 * (4 * half + q);
+                            const int r = piece >> 1;
+                            const int c = piece & 1;        // which 16 of the block's 32 quants
+                            x[q] = *reinterpret_cast<const uint4 *>(raw + r * 128 +
+                                (((2 * j + c) ^ (r & 7)) << 4));
+                        }
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int piece = lane + 32 * (4 * half + q);
+                            const int r = piece >> 1;
+                            const int c = piece & 1;
+                            uint4 h0, h1;
+                            widen4(x[q].x, h0.x, h0.y);
+                            widen4(x[q].y, h0.z, h0.w);
+                            widen4(x[q].z, h1.x, h1.y);
+                            widen4(x[q].w, h1.z, h1.w);
+                            // 128-byte swizzle: 16-byte chunk k of row r lives at chunk k ^ (r & 7)
+                            uint8_t *row = stage + r * 128;
+                            const int x7 = r & 7;
+                            *reinterpret_cast<uint4 *>(row + (((2 * c) ^ x7) << 4)) = h0;
+                            *reinterpret_cast<uint4 *>(row + (((2 * c + 1) ^ x7) << 4)) = h1;
+                            *reinterpret_cast<uint4 *>(row + (((2 * c + 4) ^ x7) << 4)) = h0;
+                            *reinterpret_cast<uint4 *>(row + (((2 * c + 5) ^ x7) << 4)) = h1;
+                        }
+                    }
+                    // generic-proxy writes must be visible to the tensor core's async-proxy reads
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    // The leader CTA issues the MMAs for both; what it is told is "this CTA's
+                    // operands of the stage are in place", so the peer's converter also waits
+                    // for its own activation half before it arrives there.
+                    if (rank != 0) ok = pf_wait(full_bar + 8 * s, use & 1);
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive_in_cta(converted_bar + 8 * s, 0);
+                        // a warp owns at most one block of a raw load: hand the buffer back
+                        mbar_arrive(&sh->raw_empty[rb]);
+                    }
+                    own_in_chunk = true;
+                    if (cw == 0) PF_STAMP(2, n >> 2, 2);
+                } else if (chunk_last && !own_in_chunk) {
+                    // none of this load's blocks was this warp's: it still owes the buffer its
+                    // arrival, and gives it only once the load has landed, so that arrivals of
+                    // consecutive uses of the buffer cannot mix
+                    ok = pf_wait(raw_full_bar + 8 * rb, raw_parity);
+                    if (lane == 0) mbar_arrive(&sh->raw_empty[rb]);
                 }
-                // generic-proxy writes must be visible to the tensor core's async-proxy reads
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(&sh->converted[s]);
-                    // last block taken from this raw load: hand the buffer back
-                    if (j == kPfRawBlocks - 1 || kb == p.blocks - 1 || n == unit_count - 1)
-                        mbar_arrive(&sh->raw_empty[(chunks - 1) % kPfRawBuffers]);
-                }
-                if (ct == 0) PF_STAMP(2, n, 2);
+                if (chunk_last) own_in_chunk = true;    // nothing more is owed for this load
                 if (++kb == p.blocks) {
                     kb = 0;
                     ++tile;
@@ -521,8 +628,7 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
         const int col0 = (ew >> 2) * kCols;
         constexpr int kPairs = kCols / 2;
         constexpr int kSlabs = kCols / kSlab;
-        constexpr int kP = kSlab / 2;
-        unsigned long long acc[kPairs];             // fp32 accumulators, packed in pairs
+        float acc[kCols];                           // fp32 accumulators
         bool failed = false;
 
         int drained = 0;        // blocks drained (TMEM ring position)
@@ -531,14 +637,14 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
             const int first_block = static_cast<int>(u - static_cast<long long>(tile) * p.blocks);
             const long long tile_end = static_cast<long long>(tile + 1) * p.blocks;
             const int count = static_cast<int>((tile_end < unit_end ? tile_end : unit_end) - u);
-            const int row0 = (tile % p.tiles_n) * kPfTileRows;
+            const int row0 = (tile % p.tiles_n) * kPfPairRows + rank * kPfTileRows;
             const int token0 = (tile / p.tiles_n) * TN;
             const int row = row0 + quadrant * 32 + lane;
             const bool row_ok = row < p.rows;
             const uint8_t *scale_plane = p.weights +
                 static_cast<size_t>(row_ok ? row : 0) * p.row_stride + p.width;
 #pragma unroll
-            for (int i = 0; i < kPairs; ++i) acc[i] = 0ull;
+            for (int i = 0; i < kCols; ++i) acc[i] = 0.0f;
             // the row's fp16 weight scales, eight blocks (16 aligned bytes) at a time and one
             // chunk ahead; the scale plane is padded to a multiple of 32 bytes per row
             uint4 dw_chunk = ldg_early_16(scale_plane + (first_block & ~7) * 2);
@@ -556,7 +662,7 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const uint32_t taddr = tmem_base +
                     (static_cast<uint32_t>(quadrant * 32) << 16) + buf * kBufStride + col0;
                 if (et == 0) PF_STAMP(3, drained, 0);
-                if (!mbar_wait_bounded(&sh->tmem_full[buf], parity)) {
+                if (!pf_wait(smem_u32(&sh->tmem_full[buf]), parity)) {
                     if (lane == 0) atomicExch(p.status, kStatusMmqMmaTimeout);
                     *abort_flag = 1;
                     failed = true;
@@ -569,22 +675,22 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                     : k8 < 6 ? dw_chunk.z : dw_chunk.w;
                 const float dw = half_bits_to_float(
                     static_cast<uint16_t>((k8 & 1) ? (word >> 16) : (word & 0xffffu)));
-                const unsigned long long dw2 = pack2(dw, dw);
                 // Slabs of kSlab columns through two register buffers.  Both buffers are
                 // requested at once and each is requested again (two slabs further) as soon as
                 // its math is done, so the accumulator buffer goes back to the MMA warp after
                 // kSlabs - 2 slab maths instead of kSlabs - 1, and the last two overlap with
                 // the next block's MMAs.
                 auto slab_math = [&](const uint32_t (&vv)[kSlab], int h) {
+                    // scalar FMAs: the packed form needs its operands in aligned register
+                    // pairs, and pairing what tcgen05.ld delivers costs more than it saves
 #pragma unroll
-                    for (int q = 0; q < kP; ++q)
-                        acc[kP * h + q] = fma2(pack_bits(vv[2 * q], vv[2 * q + 1]), dw2,
-                            acc[kP * h + q]);
+                    for (int q = 0; q < kSlab; ++q)
+                        acc[kSlab * h + q] = fmaf(__uint_as_float(vv[q]), dw, acc[kSlab * h + q]);
                 };
                 auto release = [&]() {
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(&sh->tmem_empty[buf]);
+                    if (lane == 0) mbar_arrive_in_cta(smem_u32(&sh->tmem_empty[buf]), 0);
                     if (et == 0) PF_STAMP_DRAIN(3, drained, 2);
                 };
                 if (kSlabs == 1) {
@@ -614,8 +720,7 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
 #pragma unroll
                 for (int e = 0; e < kPairs; ++e) {
                     const int t = token0 + col0 + 2 * e;
-                    float lo, hi;
-                    unpack2(acc[e], lo, hi);
+                    const float lo = acc[2 * e], hi = acc[2 * e + 1];
                     // tokens beyond the batch are padding rows of the image (unscale 0)
                     const float2 un = *reinterpret_cast<const float2 *>(p.unscale + t);
                     float *dst = p.output + static_cast<size_t>(t) * p.rows + row;
@@ -632,11 +737,14 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
         }
     }
 
+    // neither CTA may leave while the peer's tensor core can still read its shared memory or
+    // a peer thread can still arrive on its barriers
     tc_fence_before();
     __syncthreads();
+    cluster_sync_all();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -763,11 +871,11 @@ pf_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_to
     const long long total_units = static_cast<long long>(tiles) * blocks;
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
         if (!mmq_tile_is_split(total_units, product_grid, blocks, tile)) continue;
-        const int row0 = (tile % tiles_n) * kPfTileRows;
+        const int row0 = (tile % tiles_n) * kPfPairRows;
         const int token0 = (tile / tiles_n) * tile_tokens;
-        for (int i = threadIdx.x; i < kPfTileRows * tile_tokens; i += blockDim.x) {
-            const int r = row0 + (i & (kPfTileRows - 1));
-            const int t = token0 + i / kPfTileRows;
+        for (int i = threadIdx.x; i < kPfPairRows * tile_tokens; i += blockDim.x) {
+            const int r = row0 + (i & (kPfPairRows - 1));
+            const int t = token0 + i / kPfPairRows;
             if (r < rows && t < tokens) output[static_cast<size_t>(t) * rows + r] = 0.0f;
         }
     }
@@ -817,7 +925,7 @@ inline cudaError_t pf_reserve(void **aux, size_t *aux_bytes, int width, int toke
 }
 
 inline size_t pf_smem_bytes(int tn) {
-    return static_cast<size_t>(kPfStages) * pf_stage_bytes(tn) + kPfRawBuffers * kPfRawBytes +
+    return static_cast<size_t>(pf_stages(tn)) * pf_stage_bytes(tn) + kPfRawBuffers * kPfRawBytes +
         sizeof(PfShared) + 64 + 1024;
 }
 
@@ -835,7 +943,7 @@ inline cudaError_t pf_launch(const cudaLaunchConfig_t &config, const CUtensorMap
         cudaError_t error = cudaFuncGetAttributes(&attributes, q8_prefill_kernel<TN>);
         if (error != cudaSuccess) return error;
         if (attributes.numRegs * kPfThreads <
-            32 * kPfFrontWarps * kPfProducerRegs + 32 * kPfEpilogueWarps * kPfEpilogueRegs)
+            128 * kPfProducerRegs + 128 * kPfConverterRegs + 32 * kPfEpilogueWarps * kPfEpilogueRegs)
             return cudaErrorLaunchOutOfResources;
         error = cudaFuncSetAttribute(q8_prefill_kernel<TN>,
             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(pf_smem_bytes(TN)));
@@ -862,7 +970,7 @@ inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, Pf
         plan->ready = true;
     }
     CUtensorMap act_map;
-    if (!pf_make_act_map(&act_map, image, padded, width, tn)) return cudaErrorNotSupported;
+    if (!pf_make_act_map(&act_map, image, padded, width, tn / 2)) return cudaErrorNotSupported;
 
     PfParams p = {};
     p.weights = weights;
@@ -873,20 +981,21 @@ inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, Pf
     p.row_stride = row_stride;
     p.tokens = tokens;
     p.padded_tokens = padded;
-    p.tiles_n = (rows + kPfTileRows - 1) / kPfTileRows;
+    p.tiles_n = (rows + kPfPairRows - 1) / kPfPairRows;
     p.tiles = p.tiles_n * (padded / tn);
     p.output = output;
     p.status = status;
     const long long total_units = static_cast<long long>(p.tiles) * blocks;
-    const int grid = static_cast<int>(std::min<long long>(sm_count, total_units));
+    const int pairs = static_cast<int>(std::min<long long>(sm_count / 2, total_units));
+    const int grid = 2 * pairs;
     {
         const int prep_grid = std::min(padded, sm_count * 8);
         if (act == 1)
             pf_prepare_kernel<1><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
-                image, unscale, output, rows, tn, p.tiles_n, p.tiles, grid);
+                image, unscale, output, rows, tn, p.tiles_n, p.tiles, pairs);
         else
             pf_prepare_kernel<0><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
-                image, unscale, output, rows, tn, p.tiles_n, p.tiles, grid);
+                image, unscale, output, rows, tn, p.tiles_n, p.tiles, pairs);
         ++*launches;
         error = cudaGetLastError();
         if (error != cudaSuccess) return error;
@@ -897,11 +1006,15 @@ inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, Pf
     config.blockDim = dim3(kPfThreads);
     config.dynamicSmemBytes = pf_smem_bytes(tn);
     config.stream = stream;
-    cudaLaunchAttribute overlap = {};
-    overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    overlap.val.programmaticStreamSerializationAllowed = 1;
-    config.attrs = &overlap;
-    config.numAttrs = 1;
+    cudaLaunchAttribute attributes[2] = {};
+    attributes[0].id = cudaLaunchAttributeClusterDimension;
+    attributes[0].val.clusterDim.x = 2;
+    attributes[0].val.clusterDim.y = 1;
+    attributes[0].val.clusterDim.z = 1;
+    attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attributes;
+    config.numAttrs = 2;
     if (tn == 256) error = pf_launch<256>(config, plan->weights_map, act_map, p);
     else if (tn == 128) error = pf_launch<128>(config, plan->weights_map, act_map, p);
     else error = pf_launch<64>(config, plan->weights_map, act_map, p);
