@@ -37,10 +37,13 @@ BLOCKS = WIDTH // 32
 WEIGHT_BYTES = ROWS * BLOCKS * 34
 MMQ_M, MMQ_K, MMQ_N = 512, 2560, 9728
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum per weight row, from the ncu capture of a
-# 65536-row launch (181.95 MB; profiles/q8_gemv_pipelined_lm_head.md); traffic grows in
-# proportion to rows, so a launch's traffic is this times its row count
-GEMV_DRAM_TRAFFIC_PER_ROW = 181.95e6 / 65536
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the register-pipelined GEMV
+# kernel over 65536 rows x 2560 (one ncu capture, 181.95 MB); DRAM traffic grows in
+# proportion to the rows, so a launch's traffic is this figure scaled by its row count.  It
+# describes that kernel only: `roofline.traffic_source` names it in the JSON line.
+GEMV_DRAM_TRAFFIC_CAPTURE = {"kernel": "q8_gemv_pipelined_kernel", "rows": 65536, "width": 2560,
+                             "bytes": 181.95e6}
+GEMV_DRAM_TRAFFIC_PER_ROW = GEMV_DRAM_TRAFFIC_CAPTURE["bytes"] / GEMV_DRAM_TRAFFIC_CAPTURE["rows"]
 
 
 def set_rows(rows: int) -> None:
@@ -73,7 +76,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                 "-i", str(self.device_index), "-lms", "50"],
+                 "-i", str(self.device_index), "-lms", "20"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -93,8 +96,18 @@ class ClockSampler:
             except subprocess.TimeoutExpired:
                 self.proc.kill()
 
-    def summary(self, t0: float, t1: float):
-        rows = [s for (t, s) in self.samples if t0 <= t <= t1 + 0.06] or [s for (_, s) in self.samples]
+    def summary(self, t0: float, t1: float, busy0: float = None, busy1: float = None):
+        """Samples taken inside the timed region [t0, t1]; when the region is shorter than the
+        sampling period, the samples of the busy period around it (the same loop, untimed:
+        [busy0, busy1]).  `window` says which."""
+        window = "timed region"
+        rows = [s for (t, s) in self.samples if t0 <= t <= t1]
+        if not rows and busy0 is not None:
+            window = "same loop continued around the timed region"
+            rows = [s for (t, s) in self.samples if busy0 <= t <= busy1]
+        if not rows:
+            window = "whole run"
+            rows = [s for (_, s) in self.samples]
         sm, smax, reasons = [], [], set()
         for row in rows:
             parts = [p.strip() for p in row.split(",")]
@@ -110,17 +123,26 @@ class ClockSampler:
                 if value.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0,
+                    "window": window}
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(smax)),
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 # ------------------------------------------------------------------------------ reference arm
 def reference_library():
+    """The reference's CPU matvec, on every core this process may use.  The reference's own
+    policy is OMP_NUM_THREADS=$(nproc) (tools/build_native.sh:7-9); a launcher that exports
+    OMP_NUM_THREADS=1 to its children (torch.distributed.run does) must not turn the
+    baseline into a one-thread run, so the count is set through the OpenMP API."""
     from oracle import q8_oracle as o
     o.build()
+    threads = int(os.environ.get("FORTAI_BENCH_CPU_THREADS", "0")) or o.host_threads()
+    o.set_threads(threads)
     if o.Reference.available(fast=True):
-        return o, o.Reference(fast=True), "reference"
+        ref = o.Reference(fast=True)
+        ref.set_threads(threads)
+        return o, ref, "reference"
     return o, None, "port"
 
 
@@ -176,7 +198,9 @@ def run_reference_arm(args):
     sample_bytes = rows * BLOCKS * 34
     value = sample_bytes * args.steps / seconds / 1e9
     sample = (f"each step = matvec of the first {rows} of {ROWS} rows x {WIDTH} "
-              f"({sample_bytes} weight bytes), OMP threads={threads}")
+              f"({sample_bytes} weight bytes), OMP threads={threads} of {os.cpu_count()} host "
+              f"cpus (OMP_NUM_THREADS in the environment: "
+              f"{os.environ.get('OMP_NUM_THREADS', 'unset')})")
     line = {
         "impl": "reference", "metric": "q8_0_gemv_weight_bandwidth", "value": value,
         "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -246,6 +270,9 @@ def run_gpu_arm(args):
                                 device_id=torch.device("cuda", local_rank))
     torch.cuda.set_device(local_rank)
     stream = torch.cuda.current_stream()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()         # nvidia-smi needs a moment before its first sample
 
     ctx = backend.cuda_q8_context_t()
     stat = ctx.create(local_rank, stream=stream.cuda_stream)
@@ -291,7 +318,7 @@ def run_gpu_arm(args):
         logits = torch.empty(ROWS, device="cuda", dtype=torch.float32)
     my_slice = logits[first_row:first_row + my_rows]
 
-    def step_allgather():
+    def step_allgather(x=x):
         stat = backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH,
                                                  my_slice.data_ptr(), my_rows)
         if not stat.is_ok():
@@ -299,14 +326,14 @@ def run_gpu_arm(args):
         if world > 1:
             sharded.all_gather_rows(dist, my_slice, counts, logits)
 
-    def step_peers():
+    def step_peers(x=x):
         stat = backend.cuda_q8_matvec_device_f32_peers(ctx, weights, x.data_ptr(), WIDTH,
                                                        peer_ptrs, first_row, ROWS)
         if not stat.is_ok():
             raise RuntimeError(f"peer matvec failed: {stat}")
         symm_handle.barrier(channel=0)
 
-    def step_fused():
+    def step_fused(x=x):
         stat = backend.cuda_q8_matvec_device_f32_allgather(ctx, weights, x.data_ptr(), WIDTH,
                                                            peer_ptrs, flag_ptrs, rank, first_row,
                                                            ROWS)
@@ -328,21 +355,55 @@ def run_gpu_arm(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def verify(fn):
+        """One step of `fn` on a fresh activation into zeroed logits; every rank's assembled
+        vector must equal, bit for bit, the slices that each rank's own GEMV wrote into a
+        private buffer, gathered by NCCL.  A store at a wrong offset, a flag raised before the
+        slice is visible or a stale slice all fail this."""
+        gen_v = torch.Generator(device="cuda")
+        gen_v.manual_seed(12345)
+        xv = torch.randn(WIDTH, generator=gen_v, device="cuda", dtype=torch.float32)
+        own = torch.empty(my_rows, device="cuda", dtype=torch.float32)
+        stat = backend.cuda_q8_matvec_device_f32(ctx, weights, xv.data_ptr(), WIDTH,
+                                                 own.data_ptr(), my_rows)
+        if not stat.is_ok():
+            raise RuntimeError(f"matvec failed: {stat}")
+        truth = torch.empty(ROWS, device="cuda", dtype=torch.float32)
+        sharded.all_gather_rows(dist, own, counts, truth)
+        logits.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        fn(xv)
+        torch.cuda.synchronize()
+        dist.barrier()
+        same = torch.tensor([1 if torch.equal(logits, truth) else 0], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        # leave the buffers as the timed loops expect them
+        torch.cuda.synchronize()
+        dist.barrier()
+        return bool(same.item())
+
     exchange = "none"
     exchange_ms = {}
+    exchange_verified = {}
     step = step_allgather
     if world > 1:
         exchange = "allgather"
-        exchange_ms["allgather"] = time_steps(step_allgather, 200)
+        candidates = {"allgather": step_allgather}
         if peer_ptrs is not None:
-            exchange_ms["peers"] = time_steps(step_peers, 200)
-            exchange_ms["fused"] = time_steps(step_fused, 200)
-            candidates = {"allgather": step_allgather, "peers": step_peers, "fused": step_fused}
-            if args.exchange in ("peers", "fused"):
-                exchange = args.exchange
-            else:
-                exchange = min(exchange_ms, key=exchange_ms.get)
-            step = candidates[exchange]
+            candidates["peers"] = step_peers
+            candidates["fused"] = step_fused
+        for name, fn in candidates.items():
+            exchange_verified[name] = verify(fn)
+            exchange_ms[name] = time_steps(fn, 200)
+        eligible = {k: v for k, v in exchange_ms.items() if exchange_verified[k]}
+        if not eligible:
+            raise SystemExit(f"no exchange mode reproduced the gathered logits: {exchange_verified}")
+        if args.exchange in ("peers", "fused") and args.exchange in eligible:
+            exchange = args.exchange
+        else:
+            exchange = min(eligible, key=eligible.get)
+        step = candidates[exchange]
 
     def barrier():
         torch.cuda.synchronize()
@@ -350,9 +411,31 @@ def run_gpu_arm(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
+    # The timed region of the default run is about a millisecond, far shorter than a clock
+    # sample: the same loop runs untimed for a while before and after it, so that the clocks
+    # reported are those of this loop under load.
+    # (a step count, the same on every rank: the steps contain collectives)
+    if world > 1:
+        step_ms_estimate = exchange_ms[exchange]
+    else:
+        for _ in range(5):
+            step()
+        torch.cuda.synchronize()
+        a0, b0 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record(stream)
+        for _ in range(50):
+            step()
+        b0.record(stream)
+        torch.cuda.synchronize()
+        step_ms_estimate = a0.elapsed_time(b0) / 50
+
+    def run_for(seconds):
+        count = int(min(20000, max(50, seconds * 1e3 / max(step_ms_estimate, 1e-3))))
+        for _ in range(count):
+            step()
+        torch.cuda.synchronize()
+    busy0 = time.time()
+    run_for(0.25)
     for _ in range(max(3, args.warmup)):
         step()
     barrier()
@@ -367,6 +450,9 @@ def run_gpu_arm(args):
     t1 = time.time()
     launches = ctx.launch_count() - launches_before
     elapsed_ms = start.elapsed_time(stop)
+    run_for(0.15)
+    barrier()
+    busy1 = time.time()
     if world > 1:
         t = torch.tensor([elapsed_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -443,9 +529,13 @@ def run_gpu_arm(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 scales", "data": "synthetic",
-        "config": dict(workload_config(world), exchange=exchange, exchange_ms_per_step=exchange_ms),
+        "config": workload_config(world),
+        "exchange": {"used": exchange, "ms_per_step": exchange_ms, "verified": exchange_verified},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "traffic": GEMV_DRAM_TRAFFIC_PER_ROW * my_rows,
+                     "traffic_source": ("one ncu capture of %(kernel)s over %(rows)d x %(width)d "
+                                        "(%(bytes).0f bytes), scaled by rows" %
+                                        GEMV_DRAM_TRAFFIC_CAPTURE),
                      "peak_source": f"of {peak_kind}",
                      "kernel": "q8_gemv (quantize prologue + streaming dot), this rank's shard",
                      "kernel_ms": kernel_ms, "algorithmic_bytes": shard_bytes,
@@ -455,7 +545,7 @@ def run_gpu_arm(args):
                 "ms_per_step": e2e_s / e2e_steps * 1e3,
                 "api": "fortai_cuda_q8_matvec_host_f32 (pinned host buffers; the activation is copied up, the kernel stores the results into the pinned output)"},
         "gpu_launches": int(launches),
-        "clocks": sampler.summary(t0, t1),
+        "clocks": sampler.summary(t0, t1, busy0, busy1),
     }
     if mmq is not None:
         line["mmq"] = mmq
@@ -515,10 +605,29 @@ def bench_mmq(torch, backend, ctx, tokens=MMQ_M, iters=50, warmup=3, rows=MMQ_N,
     ok = ctx.synchronize().is_ok()
     w.destroy()
     ops = 2.0 * MMQ_M * MMQ_K * MMQ_N
-    return {"metric": "q8_0_mmq_int8_throughput", "value": ops / (ms * 1e-3) / 1e12,
+    achieved = ops / (ms * 1e-3) / 1e12
+    # the denominators, measured here and now: a bare tcgen05.mma loop on every SM
+    i8_peak, _, stat_i8 = backend.cuda_tensor_peak(ctx, 0, 4000)
+    f16_peak, _, stat_f16 = backend.cuda_tensor_peak(ctx, 1, 4000)
+    peaks_ok = stat_i8.is_ok() and stat_f16.is_ok() and i8_peak > 0 and f16_peak > 0
+    roofline = {
+        "bound": "int8 tensor", "achieved": achieved, "unit": "TOPS",
+        "peak_measured": i8_peak if peaks_ok else None,
+        "frac": achieved / i8_peak if peaks_ok else None,
+        "peak_nominal": 4500.0, "frac_of_nominal": achieved / 4500.0,
+        "peak_source": "bare tcgen05.mma.kind::i8 loop, 128x256x32 tiles resident in shared "
+                       "memory, no drain, all SMs, timed in this run",
+        "kernel": "q8_prefill_kernel: kind::f16 MMAs on exact binary16 operands, four per "
+                  "Q8_0 block, i.e. twice the tensor time of one int8 MMA at half its rate",
+        "f16_peak_measured_tflops": f16_peak if peaks_ok else None,
+        # the kernel's own tensor work is 4 f16 MMAs of K=16 per block: 2*M*N*64 flops per block
+        "tensor_pipe_frac_of_measured_f16": (2.0 * ops / (ms * 1e-3) / 1e12 / f16_peak)
+        if peaks_ok else None,
+    }
+    return {"metric": "q8_0_mmq_int8_throughput", "value": achieved,
             "unit": "TOPS", "ms": ms, "m": MMQ_M, "k": MMQ_K, "n": MMQ_N,
             "includes": "activation quantization + product", "launches_per_call": int(launches),
-            "frac_of_4500_TOPS_nominal": ops / (ms * 1e-3) / 1e12 / 4500.0, "ok": ok}
+            "frac_of_4500_TOPS_nominal": achieved / 4500.0, "roofline": roofline, "ok": ok}
 
 
 def apply_options(ctx, spec):
@@ -815,16 +924,53 @@ def run_ffn(args):
     steps = max(10, min(args.steps, 5000))
     with_collective = timed(lambda: ffn.forward(dist, x, out), steps)
     without = timed(local_only, steps)
+    # batch 8: eight activations per call through the few-token kernels
+    batch = 8
+    xb = torch.randn(batch, hidden, generator=gen, device="cuda", dtype=torch.float32)
+    outb = torch.empty(batch, hidden, device="cuda", dtype=torch.float32)
+    batch_ms = timed(lambda: ffn.forward_batch(dist, xb, outb), steps)
+
+    # ---- what was timed is also checked: the sharded result against the unsharded FFN of
+    # the same weights on rank 0's GPU (the hidden vector is cut on block boundaries, so its
+    # Q8_0 image is the same; only the fp32 sum over the K shards is ordered differently)
+    verified = {}
+    ffn.forward(dist, x, out)
+    ffn.forward_batch(dist, xb, outb)
+    torch.cuda.synchronize()
+    if rank == 0:
+        full = [backend.cuda_q8_weights_t() for _ in range(3)]
+        for handle, (data, r, k) in zip(full, ((gate, inner, hidden), (up, inner, hidden),
+                                               (down, hidden, inner))):
+            if not handle.upload(ctx, data, data.size, r, k).is_ok():
+                raise SystemExit("full-matrix upload failed")
+        ref1 = torch.empty(hidden, device="cuda", dtype=torch.float32)
+        refb = torch.empty(batch, hidden, device="cuda", dtype=torch.float32)
+        backend.cuda_q8_ffn_device(ctx, full[0], full[1], full[2], x.data_ptr(), hidden,
+                                   ref1.data_ptr(), hidden)
+        backend.cuda_q8_ffn_batch_device(ctx, full[0], full[1], full[2], xb.data_ptr(), batch,
+                                         refb.data_ptr(), refb.numel())
+        torch.cuda.synchronize()
+
+        def close(a, b):
+            bound = 2e-5 * float(torch.linalg.vector_norm(b.double()))
+            return bool(float((a.double() - b.double()).abs().max()) <= bound)
+        verified["batch1"] = close(out, ref1)
+        verified["batch8"] = all(close(outb[t], refb[t]) for t in range(batch))
+        for handle in full:
+            handle.destroy()
     if rank == 0:
         nbytes = 3 * inner * (hidden // 32) * 34
         print(json.dumps({"metric": "q8_0_ffn_weight_bandwidth", "unit": "GB/s", "n_gpus": world,
                           "value": nbytes / with_collective / 1e6,
                           "ms_per_step": with_collective, "ms_per_step_without_all_reduce": without,
+                          "batch8_ms_per_step": batch_ms,
+                          "batch8_value": nbytes / batch_ms / 1e6,
+                          "verified": verified,
                           "scaling": "strong", "steps": steps,
-                          "config": {"workload": "FFN hidden 5120 inner 17408 batch 1",
+                          "config": {"workload": "FFN hidden 5120 inner 17408, batch 1 and batch 8",
                                      "weight_bytes": nbytes,
                                      "sharding": f"gate/up rows/{world}, down columns/{world}, "
-                                                 "fp32 all-reduce of 5120 floats",
+                                                 "fp32 all-reduce of 5120 floats per token",
                                      "cache": "284 MB of weights per step in total"}}),
               flush=True)
     ffn.destroy()
@@ -893,6 +1039,97 @@ def run_decode(args):
     return 0
 
 
+# ------------------------------------------------------------------------------ reference formats
+def run_reference_format(args):
+    """The reference's own micro-benchmark conventions, so that its scripts and result files
+    read both implementations alike.
+
+    `--format reference --rows R --width W --iterations I --warmup N [--seed S] [--device D]`:
+    the CLI and JSON line of backend/cuda/fortai_cuda_q8_bench.cu:97-165 (same fixture:
+    xorshift32 weights and activation with quants 127 / -127 planted in every block, same
+    scalar oracle and gate abs <= 2e-3, rel <= 1e-4, same events-around-the-loop timing of
+    the resident matvec, same GiB/s over weight + activation bytes), through this backend's
+    fortai_cuda_q8_matvec_device_q8 (the resident matvec, enqueue only).  The fixture generator and the
+    scalar oracle are the checker's (oracle/), used here to make inputs and to judge, never
+    timed.
+
+    `--format reference-cpu --rows R --width W --iterations I`: the CSV of
+    app/fortai_bench_cpu_matvec.f90:37-40 for the Q8_0 CPU matvec (the reference's own C
+    arithmetic under the restated OpenMP row loop), backend name `cpu-native-q8`."""
+    from oracle import q8_oracle as o
+    rows, width = args.rows, args.width
+    blocks = width // 32
+    if width % 32 or rows < 1 or args.iterations < 1:
+        raise SystemExit("rows, width (a multiple of 32) and iterations must be positive")
+    if args.format == "reference-cpu":
+        o_mod, ref, _ = reference_library()
+        weights = o.make_weights(rows, width, seed=0, sigma=0.02)
+        x = o.normal(width, seed=1)
+        time_cpu_matvec(o_mod, ref, weights, rows, x, 1)
+        global WIDTH
+        WIDTH = width
+        seconds = time_cpu_matvec(o_mod, ref, weights, rows, x, args.iterations)
+        checksum = float(np.sum(o.matvec(weights, rows, width, x)[0], dtype=np.float64))
+        print("backend,operation,rows,cols,repeats,seconds,matvec_per_second,checksum")
+        print(f"cpu-native-q8,matvec,{rows},{width},{args.iterations},{seconds:.8E},"
+              f"{args.iterations / seconds:.8E},{checksum:.8E}")
+        return 0
+    import torch
+    from fortai_b200 import backend_cuda as backend
+    seed = args.seed & 0xffffffff
+    weights = o.fixture_fill_q8(rows, blocks, seed, True)
+    activation = o.fixture_fill_q8(1, blocks, seed ^ 0x9e3779b9, False)
+    act = activation.view(np.int8)
+    for b in range(blocks):
+        act[b * 34 + 2] = 127
+        act[b * 34 + 3] = -127
+    expected = o.fixture_matvec(weights, activation, rows, blocks)
+    torch.cuda.set_device(args.device)
+    ctx = backend.cuda_q8_context_t()
+    if not ctx.create(args.device).is_ok():
+        raise SystemExit("context creation failed")
+    apply_options(ctx, args.options)
+    w = backend.cuda_q8_weights_t()
+    if not w.upload(ctx, weights.view(np.int8), weights.size, rows, width).is_ok():
+        raise SystemExit("weight upload failed")
+    d_act = torch.from_numpy(activation.copy()).cuda(args.device)
+    d_out = torch.empty(rows, dtype=torch.float32, device=f"cuda:{args.device}")
+    stream = torch.cuda.ExternalStream(ctx.stream())
+
+    def once():
+        return backend.cuda_q8_matvec_device_q8(ctx, w, d_act.data_ptr(), d_out.data_ptr(), rows)
+    for _ in range(args.warmup):
+        once()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(args.iterations):
+        once()
+    b.record(stream)
+    torch.cuda.synchronize()
+    elapsed_ms = a.elapsed_time(b)
+    if not ctx.synchronize().is_ok():
+        raise SystemExit(f"device reported: {ctx.last_error()}")
+    out = d_out.cpu().numpy()
+    absolute = np.abs(out - expected)
+    max_abs = float(absolute.max())
+    max_rel = float((absolute / np.maximum(1.0, np.abs(expected))).max())
+    correct = max_abs <= 2.0e-3 and max_rel <= 1.0e-4
+    tokens_per_second = args.iterations / (elapsed_ms / 1000.0)
+    bandwidth = (weights.size + activation.size) * tokens_per_second / (1 << 30)
+    props = torch.cuda.get_device_properties(args.device)
+    print(json.dumps({
+        "implementation": "fortai-b200-q8", "device": args.device, "device_name": props.name,
+        "compute_capability": f"{props.major}.{props.minor}", "rows": rows, "width": width,
+        "blocks": blocks, "iterations": args.iterations, "warmup": args.warmup,
+        "kernel_ms": elapsed_ms / args.iterations, "tokens_per_second": tokens_per_second,
+        "bandwidth_gib_per_second": bandwidth, "max_abs_error": max_abs,
+        "max_rel_error": max_rel, "correct": bool(correct)}, separators=(",", ":")), flush=True)
+    w.destroy()
+    ctx.destroy()
+    return 0 if correct else 1
+
+
 def ctx_cleanup(weights, ctx, dist):
     weights.destroy()
     ctx.destroy()
@@ -928,7 +1165,20 @@ def main():
                         help="whole decode steps of a random-init Qwen3.5-like model (tokens/s)")
     parser.add_argument("--kernel-only", action="store_true",
                         help="skip the e2e, prefill and CPU legs (profiler captures)")
+    parser.add_argument("--format", default="", choices=["", "reference", "reference-cpu"],
+                        help="the reference's own micro-benchmark CLI and output (see "
+                             "run_reference_format); takes --rows --width --iterations --warmup "
+                             "--seed --device")
+    parser.add_argument("--width", type=int, default=WIDTH, help="--format: matrix width")
+    parser.add_argument("--iterations", type=int, default=1000, help="--format: timed launches")
+    parser.add_argument("--seed", type=lambda t: int(t, 0), default=0x6f727461,
+                        help="--format reference: fixture seed")
+    parser.add_argument("--device", type=int, default=0, help="--format reference: device index")
     args = parser.parse_args()
+    if args.format:
+        if args.warmup == 200:
+            args.warmup = 100        # the reference's default (fortai_q8_bench_spec.h:107-108)
+        return run_reference_format(args)
     set_rows(args.rows)
     if args.impl == "reference":
         return run_reference_arm(args)

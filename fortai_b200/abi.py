@@ -87,6 +87,8 @@ SIGNATURES = {
                                                            c_int, c_size_t, c_size_t]),
     "fortai_cuda_q8_ffn_device_noalloc": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_size_t]),
     "fortai_cuda_q8_ffn_batch_device": (c_int, [_P, _P, _P, _P, _P, c_int, _P, c_size_t]),
+    "fortai_cuda_tensor_peak": (c_int, [_P, c_int, c_int, _F, _F]),
+    "fortai_cuda_q8_matvec_device_q8": (c_int, [_P, _P, _P, _P, c_size_t]),
     "fortai_cuda_qwen35_recurrent_step_device": (c_int, [_P, _P, c_size_t, _P, c_float]),
     "fortai_cuda_qwen35_attention_step_device": (c_int, [_P, _P, c_size_t, c_int, _P, c_float]),
     "fortai_cuda_q8_ffn_step_device": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_float]),

@@ -413,6 +413,22 @@ def cuda_q8_matvec_resident(context, weights, device_activation, device_output):
     return ms.value, stat
 
 
+def cuda_q8_matvec_device_q8(context, weights, device_activation, device_output,
+                             output_elements) -> status_t:
+    """The resident matvec as an enqueue-only call (pre-quantized device activation)."""
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not device_output or
+            output_elements <= 0):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 device matvec")
+        return stat
+    code = _lib().fortai_cuda_q8_matvec_device_q8(context.handle, weights.handle,
+                                                  device_activation, device_output,
+                                                  output_elements)
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 device matvec failed")
+    return stat
+
+
 def cuda_q8_matvec_device_f32(context, weights, device_activation, activation_elements,
                               device_output, output_elements) -> status_t:
     """fortai_backend_cuda.f90:1038-1062"""
@@ -564,6 +580,21 @@ def cuda_q8_matmul_host_f32(context, weights, activation, tokens, output):
     if code != FORTAI_CUDA_OK:
         return 0.0, _failed(stat, context, "CUDA Q8 host matmul failed")
     return ms.value, stat
+
+
+def cuda_tensor_peak(context, kind: int, iterations: int = 4000):
+    """Measured tensor-core peak (bare tcgen05.mma loop on every SM): kind 0 = int8 TOPS,
+    1 = binary16 TFLOPS.  Returns (tera-ops per second, elapsed ms, status)."""
+    stat = status_t()
+    if not context.handle or kind not in (0, 1) or iterations < 2:
+        stat.set(FORTAI_INVALID, "invalid CUDA tensor peak probe")
+        return 0.0, 0.0, stat
+    tops, ms = c_float(0.0), c_float(0.0)
+    code = _lib().fortai_cuda_tensor_peak(context.handle, int(kind), int(iterations), byref(tops),
+                                          byref(ms))
+    if code != FORTAI_CUDA_OK:
+        return 0.0, 0.0, _failed(stat, context, "CUDA tensor peak probe failed")
+    return tops.value, ms.value, stat
 
 
 def cuda_q8_matmul_block_dots_device(context, weights, device_activation, tokens, device_output,

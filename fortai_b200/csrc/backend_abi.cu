@@ -17,6 +17,7 @@
 #include "q8_gemv.cuh"
 #include "q8_mmq.cuh"
 #include "q8_prefill.cuh"
+#include "tensor_peak.cuh"
 #include "q8_fewtok.cuh"
 #include "qwen35_layers.cuh"
 
@@ -55,6 +56,7 @@ struct fortai_cuda_q8_context {
     int gemv_balance = 0;      // 1 = trim the grid so that the last round of rows is full
     int ring_stages = 0;
     int ring_rows = 0;
+    int peer_wait_clocks_millions = 2000;   // fused all-gather: wait for a peer's flag, in 1e6 SM clocks
     int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 33)
     int prefill_kind = 0;      // tcgen05 kernel: 0 = kind::f16, activation scale folded into the operand; 1 = kind::i8, scaled per block
     int fewtok_splits = 0;     // K ranges of the few-token kernel (0 = as few as fit)
@@ -132,6 +134,7 @@ const char *status_text(int code) {
     case kStatusMmqMmaTimeout: return "prefill kernel gave up waiting for the tensor core";
     case kStatusMmqDrainTimeout: return "prefill kernel gave up waiting for an accumulator";
     case kStatusPeerFlagTimeout: return "gave up waiting for a peer flag";
+    case kStatusPositionOutOfRange: return "attention position outside the layer's context";
     default: return "unknown device status";
     }
 }
@@ -1050,6 +1053,20 @@ extern "C" int fortai_cuda_q8_matvec_resident(fortai_cuda_q8_context *context,
     return finish(context, "resident matvec", error);
 }
 
+// The resident matvec without its event pair and wait: pre-quantized device activation in,
+// enqueue only (what the reference's micro-benchmark times back to back).
+extern "C" int fortai_cuda_q8_matvec_device_q8(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
+    size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !device_output ||
+        output_elements < static_cast<size_t>(weights->rows)) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    const GemvParams p = single_params(context, weights, device_activation,
+        static_cast<float *>(device_output));
+    const cudaError_t error = launch_gemv(context, p, kActQ8, kEpiPlain);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "device Q8 matvec", error);
+}
+
 extern "C" int fortai_cuda_q8_matvec_device_f32(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation,
     size_t activation_elements, void *device_output, size_t output_elements) {
@@ -1630,7 +1647,8 @@ int attention_run(fortai_cuda_qwen35_attention *layer, const void *device_activa
         error = launch_overlapped(c, attention_prepare_kernel, layer->heads + layer->kv_heads, 256,
             0, query, key, value, layer->q_norm, layer->k_norm, layer->key_cache,
             layer->value_cache, layer->heads, layer->kv_heads, layer->head_size, layer->value_size,
-            c->position, layer->rope_dimension, layer->rope_base, layer->epsilon);
+            c->position, layer->rope_dimension, layer->rope_base, layer->epsilon,
+            layer->max_context, c->status_device);
         // scores of every position, then one row of partial value sums per warp
         const size_t shared = (static_cast<size_t>(layer->max_context + 3) / 4 * 4 +
             8 * static_cast<size_t>(layer->value_size)) * sizeof(float);
@@ -1641,7 +1659,8 @@ int attention_run(fortai_cuda_qwen35_attention *layer, const void *device_activa
             error = launch_overlapped(c, attention_apply_kernel, layer->heads, 256, shared, query,
                 layer->key_cache, layer->value_cache, layer->attention, layer->heads,
                 layer->kv_heads, layer->head_size, layer->value_size,
-                (layer->max_context + 3) / 4 * 4, c->position);
+                (layer->max_context + 3) / 4 * 4, c->position, layer->max_context,
+                c->status_device);
     }
     if (error == cudaSuccess) {
         GemvParams o = single_params(c, layer->out, layer->attention,
@@ -1701,6 +1720,8 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
         context->ring_stages = value;
     else if (!std::strcmp(name, "ring_rows") && value <= 256) context->ring_rows = value;
     else if (!std::strcmp(name, "mmq_min_tokens")) context->mmq_min_tokens = value;
+    else if (!std::strcmp(name, "peer_wait_clocks_millions"))
+        context->peer_wait_clocks_millions = value > 0 ? value : 2000;
     else if (!std::strcmp(name, "prefill_kind")) context->prefill_kind = value;
     else if (!std::strcmp(name, "fewtok_splits") && value >= 0) context->fewtok_splits = value;
     else if (!std::strcmp(name, "fewtok_threads") && value >= 0 && value <= 512 &&
@@ -1826,6 +1847,16 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
     for (int i = 0; i < peer_count; ++i)
         if (!peer_outputs[i] || !peer_flags[i]) return FORTAI_CUDA_INVALID;
     cudaSetDevice(context->device);
+    // The sequence number is a kernel argument taken from a host counter: a captured launch
+    // would replay the same number, and from the second replay on the tail would find the
+    // peers' flags "already raised" and return without waiting.  Refuse capture.
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(context->stream, &capture) == cudaSuccess &&
+        capture != cudaStreamCaptureStatusNone) {
+        fail(context, "all-gather matvec cannot be captured into a CUDA graph "
+                      "(its flag sequence number is a launch argument)");
+        return FORTAI_CUDA_INVALID;
+    }
     GemvParams p = single_params(context, weights, device_activation, nullptr);
     for (int i = 0; i < peer_count; ++i) {
         p.peer_outputs[i] = static_cast<float *>(peer_outputs[i]);
@@ -1838,6 +1869,7 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
     p.my_rank = my_rank;
     if (++context->allgather_sequence == 0) ++context->allgather_sequence;   // 0 means "off"
     p.sequence = context->allgather_sequence;
+    p.flag_wait_clocks = static_cast<long long>(context->peer_wait_clocks_millions) * 1000000LL;
     const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-gather matvec", error);
 }
@@ -2083,6 +2115,35 @@ extern "C" int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *c
     const cudaError_t error = enqueue_matmul(context, weights, device_activation, kActQ8, tokens,
         nullptr, static_cast<int32_t *>(device_output));
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "matmul block dots", error);
+}
+
+// Measured tensor-core peak: `iterations` commits of four 128 x 256 MMAs on every SM, timed
+// with the context's events.  kind 0 = kind::i8, 1 = kind::f16.  Blocks.
+extern "C" int fortai_cuda_tensor_peak(fortai_cuda_q8_context *context, int kind, int iterations,
+    float *tera_ops_per_second, float *elapsed_ms) {
+    if (!context || (kind != 0 && kind != 1) || iterations < 2 || iterations > (1 << 24) ||
+        !tera_ops_per_second) return FORTAI_CUDA_INVALID;
+    *tera_ops_per_second = 0.0f;
+    if (elapsed_ms) *elapsed_ms = 0.0f;
+    cudaSetDevice(context->device);
+    // once untimed: the first launch pays for module loading and the attribute call
+    cudaError_t error = tensor_peak_launch(context->stream, kind, 64, context->sm_count,
+        context->status_device);
+    if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
+    if (error == cudaSuccess)
+        error = tensor_peak_launch(context->stream, kind, iterations, context->sm_count,
+            context->status_device);
+    context->launches += 2;
+    if (error == cudaSuccess) error = cudaEventRecord(context->stop, context->stream);
+    if (error == cudaSuccess) error = cudaEventSynchronize(context->stop);
+    float ms = 0.0f;
+    if (error == cudaSuccess) error = cudaEventElapsedTime(&ms, context->start, context->stop);
+    if (error == cudaSuccess && ms > 0.0f) {
+        *tera_ops_per_second = static_cast<float>(
+            tensor_peak_ops(kind, iterations, context->sm_count) / (ms * 1.0e-3) / 1.0e12);
+        if (elapsed_ms) *elapsed_ms = ms;
+    }
+    return finish(context, "tensor peak probe", error);
 }
 
 // h[i] = silu(gate[i]) * up[i], in place over gate

@@ -34,7 +34,8 @@ enum DeviceStatus : int {
     kStatusMmqLoadTimeout = 3,
     kStatusMmqMmaTimeout = 4,
     kStatusMmqDrainTimeout = 5,
-    kStatusPeerFlagTimeout = 6
+    kStatusPeerFlagTimeout = 6,
+    kStatusPositionOutOfRange = 7
 };
 
 __host__ __device__ inline size_t row_stride_bytes(int blocks) {

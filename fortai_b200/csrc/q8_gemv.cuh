@@ -77,6 +77,7 @@ struct GemvParams {
     unsigned *cta_counter;             // device word, zero between launches
     unsigned sequence;
     int my_rank;
+    long long flag_wait_clocks;        // how long the tail waits for a peer's flag (SM clocks)
     // optional fusions of the caller's glue (null = off): an RMS norm of the fp32
     // activation with learned scale in the prologue, and out[row] = dot + residual[row]
     // in the plain epilogue (residual may be the output vector itself)
@@ -137,7 +138,7 @@ __device__ __forceinline__ void peer_allgather_tail(const GemvParams &p) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.sequence) : "memory");
     const unsigned *local = p.my_flags + peer;
     const long long start = clock64();
-    const long long limit = 2000000000LL;         // about a second of SM clocks
+    const long long limit = p.flag_wait_clocks;   // about a second of SM clocks by default
     for (;;) {
         unsigned seen;
         asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(local) : "memory");

@@ -169,11 +169,19 @@ attention_prepare_kernel(float *__restrict__ query, float *__restrict__ key,
     const float *__restrict__ value, const float *__restrict__ query_norm,
     const float *__restrict__ key_norm, __half *__restrict__ key_cache,
     __half *__restrict__ value_cache, int heads, int kv_heads, int head_size, int value_size,
-    const int *__restrict__ position_ptr, int rope_dimension, float rope_base, float epsilon) {
+    const int *__restrict__ position_ptr, int rope_dimension, float rope_base, float epsilon,
+    int max_context, int *__restrict__ status) {
     grid_dependents_may_launch();
     grid_dependency_wait();
     __shared__ double reduce[32];
     const int position = *position_ptr;
+    // The position is a device word (a replayed graph or set_position may have put anything
+    // there): one outside the caches is never used as an index.  The CTA records a status
+    // and leaves; the next blocking call reports it.
+    if (position < 0 || position >= max_context) {
+        if (threadIdx.x == 0) atomicExch(status, kStatusPositionOutOfRange);
+        return;
+    }
     const bool is_query = static_cast<int>(blockIdx.x) < heads;
     const int head = is_query ? blockIdx.x : blockIdx.x - heads;
     float *v = is_query ? query + head * 2 * head_size : key + head * head_size;
@@ -219,13 +227,20 @@ __device__ __forceinline__ void load_half8(const __half *p, float (&out)[8]) {
 __global__ void __launch_bounds__(256)
 attention_apply_kernel(const float *__restrict__ query, const __half *__restrict__ key_cache,
     const __half *__restrict__ value_cache, float *__restrict__ attention, int heads, int kv_heads,
-    int head_size, int value_size, int max_context, const int *__restrict__ position_ptr) {
+    int head_size, int value_size, int max_context, const int *__restrict__ position_ptr,
+    int context_limit, int *__restrict__ status) {
     grid_dependents_may_launch();
     grid_dependency_wait();
     extern __shared__ __align__(16) float scores[];      // max_context entries, then partials
     __shared__ float reduce[32];
     const int head = blockIdx.x;
     const int position = *position_ptr;
+    // see attention_prepare_kernel: a position outside the caches (and outside scores[]) is
+    // reported, not used
+    if (position < 0 || position >= context_limit) {
+        if (threadIdx.x == 0) atomicExch(status, kStatusPositionOutOfRange);
+        return;
+    }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     const int kv_head = head / (heads / kv_heads);
     const float *q = query + head * 2 * head_size;

@@ -202,6 +202,16 @@ class ShardedFfn:
             raise RuntimeError(f"sharded FFN failed: {stat}")
         return all_reduce_sum(dist, out, self.world)
 
+    def forward_batch(self, dist, activations: "torch.Tensor", out: "torch.Tensor"):
+        """`tokens` activations at once (tokens x hidden in, tokens x hidden out)."""
+        tokens = int(activations.shape[0])
+        stat = self.backend.cuda_q8_ffn_batch_device(self.context, self.gate, self.up, self.down,
+                                                     activations.data_ptr(), tokens,
+                                                     out.data_ptr(), out.numel())
+        if not stat.is_ok():
+            raise RuntimeError(f"sharded batched FFN failed: {stat}")
+        return all_reduce_sum(dist, out, self.world)
+
     def destroy(self):
         for handle in (self.gate, self.up, self.down):
             handle.destroy()

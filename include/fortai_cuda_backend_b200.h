@@ -200,9 +200,12 @@ uint64_t fortai_cuda_q8_context_launch_count(const fortai_cuda_q8_context *conte
 int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context);
 /* Tuning knobs, by name: "gemv_variant" (0 = automatic, 1 = half-block-per-lane
  * kernel with 16-byte loads, 2 = bulk-copy ring, 3 = block-per-lane kernel with
- * 32-byte loads, 4 = register-pipelined kernel where the shape allows it), "gemv_ctas_per_sm", "gemv_rows_per_warp", "ring_stages",
- * "ring_rows", "mmq_min_tokens".  Zero means automatic.  Unknown names return
- * INVALID. */
+ * 32-byte loads, 4 = register-pipelined kernel where the shape allows it), "gemv_ctas_per_sm",
+ * "gemv_rows_per_warp", "ring_stages", "ring_rows", "mmq_min_tokens" (first token count that
+ * goes to the tcgen05 prefill kernel, default 33), "prefill_kind" (0 = kind::f16 MMAs with the
+ * activation scale folded into the operand, the default; 1 = kind::i8 MMAs scaled per block on
+ * the CUDA cores, the kernel that also serves the block-dot probe), "peer_wait_clocks_millions".
+ * Zero means automatic.  Unknown names return INVALID. */
 int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context, const char *name,
     int value);
 
@@ -222,9 +225,20 @@ int fortai_cuda_q8_weights_upload_columns(fortai_cuda_q8_context *context,
 int fortai_cuda_q8_quantize_device(fortai_cuda_q8_context *context, const void *device_input,
     size_t elements, void *device_output, size_t output_bytes);
 
-/* Parity probe: the exact int32 dot of every (row, block) pair, rows x (width/32)
- * values, produced by the same inner loop as the GEMV.  Enqueue only. */
+/* Parity probe: the exact int32 dot of every (row, block) pair, rows x (width/32) values.
+ * It runs the half-block-per-lane GEMV kernel with an epilogue that joins a block's two
+ * half dots; the default register-pipelined kernel forms the same two exact half-block
+ * dots per lane but scales each on its own and never materialises their sum, so on that
+ * kernel the integer arithmetic is covered through this sibling and the fp32 result through
+ * the 1e-5 * L2 bound.  Enqueue only. */
 int fortai_cuda_q8_block_dots_device(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
+    size_t output_elements);
+
+/* fortai_cuda_q8_matvec_resident (backend/cuda/fortai_cuda_backend.h:56-58) without its event
+ * pair and wait: device Q8_0 activation (width/32 blocks of 34 bytes) in, `rows` floats out.
+ * Enqueue only. */
+int fortai_cuda_q8_matvec_device_q8(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation, void *device_output,
     size_t output_elements);
 
@@ -256,6 +270,13 @@ int fortai_cuda_q8_matmul_host_f32(fortai_cuda_q8_context *context,
 int fortai_cuda_q8_matmul_block_dots_device(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation, int tokens,
     void *device_output, size_t output_elements);
+
+/* Measured tensor-core peak of this GPU, the denominator for the prefill kernel's
+ * utilisation: a bare tcgen05.mma loop (128 x 256 tiles, operands resident in shared memory,
+ * nothing drained) on every SM, `iterations` commits of four MMAs each.  kind 0 = kind::i8
+ * (int8 TOPS), 1 = kind::f16 (binary16 TFLOPS).  No counterpart in the reference; blocks. */
+int fortai_cuda_tensor_peak(fortai_cuda_q8_context *context, int kind, int iterations,
+    float *tera_ops_per_second, float *elapsed_ms);
 
 /* FFN for `tokens` activations at once: out[t] = down . Q8(silu(gate . x[t]) * (up . x[t])),
  * x and out token-major fp32 in device memory.  Same shape rules as
@@ -303,7 +324,13 @@ int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *context,
  * reached that number, so when the launch completes every rank's slice is in this rank's
  * output vector.  Every rank must make the same sequence of these calls, each on its own
  * GPU (the kernels wait on one another).  A wait that runs out is reported as
- * RUNTIME_ERROR by the next synchronizing call.  Enqueue only. */
+ * RUNTIME_ERROR by the next synchronizing call (option "peer_wait_clocks_millions" sets the
+ * limit, default 2000).  The flags say that a slice has ARRIVED, not that it has been
+ * CONSUMED: a rank that runs ahead stores call n+1's slice into a peer's vector while that
+ * peer may still read call n's result.  Alternate two output vectors between consecutive
+ * calls, or put a cross-rank barrier between reading the result and the next call.  The
+ * call cannot be captured into a CUDA graph (the sequence number is a launch argument; a
+ * replay would not wait): during capture it returns INVALID with a message.  Enqueue only. */
 int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation,
     size_t activation_elements, void *const *peer_outputs, void *const *peer_flags,

@@ -613,3 +613,12 @@ int oracle_thread_count(void)
     return 1;
 #endif
 }
+
+void oracle_set_threads(int threads)
+{
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}

@@ -23,15 +23,27 @@ BLOCK_ELEMS = 32
 BLOCK_BYTES = 34
 
 
+def reference_checkout() -> str:
+    """Where the reference's sources lie: FORTAI_REFERENCE, else a checkout named
+    `reference` beside this repository; empty when there is neither."""
+    given = os.environ.get("FORTAI_REFERENCE", "")
+    if given:
+        return given
+    sibling = os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
+    return sibling if os.path.isdir(sibling) else ""
+
+
 def build(force: bool = False) -> None:
     """Compile the restatement and (if the reference checkout is here) oracle/_ref."""
     target = os.path.join(HERE, "libq8oracle.so")
     if force or not os.path.exists(target) or (
             os.path.getmtime(target) < os.path.getmtime(os.path.join(HERE, "q8_oracle.c"))):
-        subprocess.run(["make", "-C", HERE, "all"], check=True, capture_output=True)
-    elif os.path.isdir("/root/reference") and not os.path.exists(
+        subprocess.run(["make", "-C", HERE, "all", f"REFERENCE={reference_checkout()}"],
+                       check=True, capture_output=True)
+    elif os.path.isdir(reference_checkout()) and not os.path.exists(
             os.path.join(HERE, "_ref", "libfortai_ref_q8.so")):
-        subprocess.run(["make", "-C", HERE, "ref"], check=True, capture_output=True)
+        subprocess.run(["make", "-C", HERE, "ref", f"REFERENCE={reference_checkout()}"],
+                       check=True, capture_output=True)
 
 
 def _ptr(array: np.ndarray):
@@ -83,6 +95,7 @@ class _Lib:
         L.oracle_fixture_fill_q8.argtypes = [c_void_p, c_int, c_int, c_uint32, c_int]
         L.oracle_fixture_matvec.argtypes = [c_void_p, c_void_p, c_int, c_int, c_void_p]
         L.oracle_thread_count.restype = c_int
+        L.oracle_set_threads.argtypes = [c_int]
 
 
 _LIB = None
@@ -275,6 +288,19 @@ def thread_count() -> int:
     return int(lib().oracle_thread_count())
 
 
+def host_threads() -> int:
+    """Cores this process may run on: the reference's own thread policy is all of them
+    (tools/build_native.sh:7-9)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        return max(1, os.cpu_count() or 1)
+
+
+def set_threads(threads: int) -> None:
+    lib().oracle_set_threads(int(threads))
+
+
 # --------------------------------------------------------------------------- reference build
 class Reference:
     """The reference's own C arithmetic (oracle/_ref).  `fast=True` loads the build
@@ -302,6 +328,7 @@ class Reference:
         L.ref_matvec_q8_repeat.argtypes = [c_void_p, c_int64, c_int64, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_int]
         L.ref_thread_count.restype = c_int
+        L.ref_set_threads.argtypes = [c_int]
         L.ref_uses_avx2.restype = c_int
         L.fortai_gdn_step.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float,
                                       c_int64, c_float, c_void_p]
@@ -380,6 +407,9 @@ class Reference:
 
     def thread_count(self) -> int:
         return int(self.lib.ref_thread_count())
+
+    def set_threads(self, threads: int) -> None:
+        self.lib.ref_set_threads(int(threads))
 
     def uses_avx2(self) -> bool:
         return bool(self.lib.ref_uses_avx2())

@@ -81,6 +81,18 @@ int ref_thread_count(void)
 #endif
 }
 
+/* The reference's own thread policy is "all cores" (tools/build_native.sh:7-9 exports
+ * OMP_NUM_THREADS=$(nproc)); a launcher that forces OMP_NUM_THREADS=1 on its children
+ * (torch.distributed.run does) would otherwise time this baseline on one thread. */
+void ref_set_threads(int threads)
+{
+#ifdef _OPENMP
+    if (threads > 0) omp_set_num_threads(threads);
+#else
+    (void)threads;
+#endif
+}
+
 int ref_uses_avx2(void)
 {
     return __builtin_cpu_supports("avx2") && __builtin_cpu_supports("f16c");

@@ -24,7 +24,8 @@ ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
 from oracle import q8_oracle as o  # noqa: E402
 
-REFERENCE = os.environ.get("FORTAI_REFERENCE", "/root/reference")
+REFERENCE = os.environ.get("FORTAI_REFERENCE") or os.path.normpath(
+    os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference"))
 
 
 def sha(a: np.ndarray) -> str:

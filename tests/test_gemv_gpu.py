@@ -406,3 +406,36 @@ def test_reference_host_call_into_page_locked_output(backend, context, dev, orac
     assert stat.is_ok(), stat
     assert np.array_equal(locked.numpy(), pageable)
     assert np.abs(pageable - expected).max() <= l2_tolerance(expected)
+
+
+def test_known_answers_of_the_reference_test_program_through_cuda(backend, context, dev, oracle):
+    """test/test_fortai_smoke.f90:221-265: one 32-wide row with scale 1.0 and quants 1..32
+    against a vector of ones gives 527.9677734375; the triplet of that row, two rows of
+    1x and 2x, and one of 3x gives [527.97, 527.97, 1055.94, 1583.90].  The same bytes
+    through the CUDA entry points (fp32 vector in, and pre-quantized)."""
+    w1 = np.zeros(34, np.int8); w1[1] = 0x3c; w1[2:] = np.arange(1, 33)
+    w2 = np.zeros(68, np.int8)
+    for r in range(2):
+        w2[r * 34 + 1] = 0x3c
+        w2[r * 34 + 2:r * 34 + 34] = (r + 1) * np.arange(1, 33)
+    w3 = np.zeros(34, np.int8); w3[1] = 0x3c; w3[2:] = 3 * np.arange(1, 33)
+    ones = np.ones(32, np.float32)
+    h1, h2, h3 = dev.weights(w1, 1, 32), dev.weights(w2, 2, 32), dev.weights(w3, 1, 32)
+    out = np.zeros(1, np.float32)
+    _, stat = backend.cuda_q8_matvec_host_f32(context, h1, ones, out)
+    assert stat.is_ok(), stat
+    assert abs(float(out[0]) - 527.9677734375) < 1.0e-4     # the reference test's own bound
+    assert float(out[0]) == 527.9677734375                  # and in fact exact
+    quantized = oracle.quantize(ones)[0]
+    a, b, c = np.zeros(1, np.float32), np.zeros(2, np.float32), np.zeros(1, np.float32)
+    _, stat = backend.cuda_q8_matvec_host_triplet(context, h1, h2, h3, quantized, quantized.size,
+                                                  a, a.nbytes, b, b.nbytes, c, c.nbytes)
+    assert stat.is_ok(), stat
+    got = np.array([a[0], b[0], b[1], c[0]], np.float64)
+    expected = np.array([527.9677734375, 527.9677734375, 1055.935546875, 1583.9033203125])
+    assert np.abs(got - expected).max() < 1.0e-4
+    # the exact int32 block dot of the row: sum(1..32) * 127
+    dq = dev.to_device(quantized)
+    ddots = dev.buffer(4)
+    assert backend.cuda_q8_block_dots_device(context, h1, dq, ddots, 1).is_ok()
+    assert int(dev.int32s(ddots, 1)[0]) == 127 * 528

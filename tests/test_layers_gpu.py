@@ -180,6 +180,37 @@ def test_attention_positions_match_the_cpu_model(oracle, backend, context, dev, 
     assert layer.destroy().is_ok()
 
 
+def test_attention_position_word_outside_the_cache_is_reported_not_used(oracle, backend, context,
+                                                                        dev):
+    """The kernels read the position from a device word that the host argument only bounds: a
+    word outside the caches (a replayed graph, a set_position the caller did not bound) must
+    not become an index.  The guarded kernels record a status and skip their work; nothing
+    faults, and the next blocking call says what happened."""
+    shape = (256, 2, 1, 64, 64, 12, 64, 3)
+    hidden, max_context = shape[0], shape[5]
+    layer, cpu = make_attention(oracle, backend, context, dev, shape, seed=91)
+    out_dev = dev.buffer(hidden * 4)
+    x = oracle.normal(hidden, seed=51, sigma=1.0)
+    x_dev = dev.to_device(x)
+    assert context.set_position(0).is_ok()
+    assert layer.run_device(x_dev, hidden, 0, out_dev, hidden).is_ok()
+    assert context.synchronize().is_ok()
+    layer_close(dev.floats(out_dev, hidden), cpu.run(x, 0))
+    # device word beyond the cache, host argument in range
+    assert context.set_position(max_context + 5).is_ok()
+    assert layer.run_device(x_dev, hidden, 1, out_dev, hidden).is_ok()      # enqueue only
+    stat = context.synchronize()
+    assert not stat.is_ok()
+    assert "attention position outside" in context.last_error()
+    # the layer is still usable: position 1 as if the bad call had not happened
+    x1 = oracle.normal(hidden, seed=52, sigma=1.0)
+    assert context.set_position(1).is_ok()
+    assert layer.run_device(dev.to_device(x1), hidden, 1, out_dev, hidden).is_ok()
+    assert context.synchronize().is_ok()
+    layer_close(dev.floats(out_dev, hidden), cpu.run(x1, 1))
+    assert layer.destroy().is_ok()
+
+
 def test_attention_last_cache_slot(oracle, backend, context, dev):
     """Fill every slot of a small cache; the last position reads all of them."""
     shape = (256, 2, 1, 64, 64, 12, 64, 12)

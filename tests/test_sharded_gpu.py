@@ -87,6 +87,78 @@ def test_column_shards_sum_to_the_full_ffn(backend, context, dev, oracle):
     assert float(np.abs(total - expected).max()) <= 2 * l2_tolerance(expected)
 
 
+def test_fused_allgather_gives_up_when_a_peer_never_answers(backend, context, dev, oracle):
+    """Failure detection without a fault: two "ranks" whose flag arrays are ordinary buffers
+    on this GPU, the second rank's flag is never raised.  The wait runs out (a few
+    milliseconds here), the kernel returns by itself, the next blocking call reports it, and
+    the context works again afterwards."""
+    rows, width = 256, 1024
+    weights = oracle.make_weights(rows, width, seed=9)
+    x = oracle.normal(width, seed=10)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    w = dev.weights(weights, rows, width)
+    dx = dev.to_device(x)
+    outs = [dev.to_device(np.zeros(2 * rows, np.float32)) for _ in range(2)]
+    flags = [dev.to_device(np.zeros(2, np.int32)) for _ in range(2)]
+    assert context.set_option("peer_wait_clocks_millions", 5).is_ok()
+    stat = backend.cuda_q8_matvec_device_f32_allgather(context, w, dx, width, outs, flags, 0, 0,
+                                                       2 * rows)
+    assert stat.is_ok(), stat               # enqueue only: the launch itself is fine
+    stat = context.synchronize()
+    assert not stat.is_ok()
+    assert "gave up waiting for a peer flag" in context.last_error()
+    # this rank's slice was stored everywhere all the same, and its own flag was raised
+    for ptr in outs:
+        assert float(np.abs(dev.floats(ptr, 2 * rows)[:rows] - expected).max()) <= l2_tolerance(expected)
+    assert dev.int32s(flags[1], 2)[0] != 0 and dev.int32s(flags[0], 2)[1] == 0
+    # the status was cleared by reporting it; an ordinary call succeeds
+    assert context.set_option("peer_wait_clocks_millions", 2000).is_ok()
+    assert context.synchronize().is_ok()
+    out = np.zeros(rows, np.float32)
+    _, stat = backend.cuda_q8_matvec_host_f32(context, w, x, out)
+    assert stat.is_ok(), stat
+    assert float(np.abs(out - expected).max()) <= l2_tolerance(expected)
+
+
+def test_fused_allgather_refuses_graph_capture(backend, context, dev, oracle):
+    rows, width = 64, 256
+    w = dev.weights(oracle.make_weights(rows, width, seed=1), rows, width)
+    dx = dev.to_device(oracle.normal(width, seed=2))
+    out = dev.to_device(np.zeros(rows, np.float32))
+    flags = dev.to_device(np.zeros(1, np.int32))
+    assert context.capture_begin().is_ok()
+    stat = backend.cuda_q8_matvec_device_f32_allgather(context, w, dx, width, [out], [flags], 0,
+                                                       0, rows)
+    assert not stat.is_ok()
+    assert "cannot be captured" in context.last_error()
+    assert context.capture_end().is_ok()
+
+
+def test_27b_ffn_at_its_eight_way_shard_sizes(backend, context, dev, oracle):
+    """hidden 5120, inner 17408 over 8 ranks: 2176 gate/up rows and a 68-block column shard of
+    the down matrix per rank (68 is not a multiple of 8: the raw GGUF rows of such a shard are
+    only 8-byte aligned).  All eight shards run on this GPU; their sum is the full FFN."""
+    from fortai_b200 import sharded
+    hidden, inner, world = 5120, 17408, 8
+    gate = oracle.make_weights(inner, hidden, seed=31)
+    up = oracle.make_weights(inner, hidden, seed=32)
+    down = oracle.make_weights(hidden, inner, seed=33)
+    x = oracle.normal(hidden, seed=34)
+    expected = oracle.ffn(gate, up, down, inner, hidden, hidden, x)
+    dx = dev.to_device(x)
+    total = np.zeros(hidden, np.float64)
+    for rank in range(world):
+        ffn = sharded.ShardedFfn(backend, context, gate, up, down, hidden, inner, rank, world)
+        assert ffn.count == 2176 and ffn.count // 32 == 68
+        dout = dev.buffer(4 * hidden)
+        stat = backend.cuda_q8_ffn_device(context, ffn.gate, ffn.up, ffn.down, dx, hidden, dout,
+                                          hidden)
+        assert stat.is_ok(), stat
+        total += dev.floats(dout, hidden)
+        ffn.destroy()
+    assert float(np.abs(total - expected).max()) <= 2 * l2_tolerance(expected)
+
+
 def _rank_main(rank, world, port, result_path):
     sys.path.insert(0, ROOT)
     os.environ["MASTER_ADDR"] = "127.0.0.1"

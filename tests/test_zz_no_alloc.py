@@ -41,6 +41,37 @@ def test_noalloc_ffn_matches_the_allocating_entry_point_twice_in_a_row(oracle):
     d_new = _buffer(lib, ctx, 4 * hidden)
     ref = np.zeros(hidden, np.float32)
     new = np.zeros(hidden, np.float32)
+    # The point of the entry point: it must not allocate.  The inner size (9728) is one for
+    # which the ordinary FFN would grow its prepared-activation buffer.  A throw-away context
+    # runs the call once first, so that the driver has loaded the kernels' code (lazy module
+    # loading takes device memory at a kernel's first launch in the process); then free device
+    # memory is compared around the first call on a context that has not grown any scratch.
+    import torch
+    x0 = oracle.normal(hidden, seed=19)
+    warm = c_void_p()
+    assert lib.fortai_cuda_q8_context_create(0, byref(warm)) == 0
+    warm_w = [_upload(lib, warm, oracle.make_weights(r, k, seed=1), r, k)
+              for r, k in ((inner, hidden), (inner, hidden), (hidden, inner))]
+    warm_in, warm_out = _buffer(lib, warm, 4 * hidden), _buffer(lib, warm, 4 * hidden)
+    assert lib.fortai_cuda_q8_device_buffer_upload(warm, warm_in, x0.ctypes.data_as(c_void_p),
+                                                   x0.nbytes) == 0
+    assert lib.fortai_cuda_q8_ffn_device_noalloc(warm, warm_w[0], warm_w[1], warm_w[2], warm_in,
+                                                 hidden, warm_out, hidden) == 0
+    assert lib.fortai_cuda_q8_context_synchronize(warm) == 0
+    for w in warm_w:
+        lib.fortai_cuda_q8_weights_destroy(w)
+    for b in (warm_in, warm_out):
+        lib.fortai_cuda_q8_device_buffer_destroy(warm, b)
+    lib.fortai_cuda_q8_context_destroy(warm)
+
+    assert lib.fortai_cuda_q8_device_buffer_upload(ctx, d_in, x0.ctypes.data_as(c_void_p),
+                                                   x0.nbytes) == 0
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info(0)[0]
+    code = lib.fortai_cuda_q8_ffn_device_noalloc(ctx, gate, up, down, d_in, hidden, d_new, hidden)
+    assert code == 0, lib.fortai_cuda_q8_last_error(ctx)
+    assert lib.fortai_cuda_q8_context_synchronize(ctx) == 0
+    assert torch.cuda.mem_get_info(0)[0] == free_before
     for call in range(2):          # the second call reuses whatever the first one left behind
         x = oracle.normal(hidden, seed=20 + call)
         assert lib.fortai_cuda_q8_device_buffer_upload(ctx, d_in, x.ctypes.data_as(c_void_p),
