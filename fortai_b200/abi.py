@@ -89,6 +89,14 @@ SIGNATURES = {
     "fortai_cuda_q8_ffn_batch_device": (c_int, [_P, _P, _P, _P, _P, c_int, _P, c_size_t]),
     "fortai_cuda_tensor_peak": (c_int, [_P, c_int, c_int, _F, _F]),
     "fortai_cuda_q8_matvec_device_q8": (c_int, [_P, _P, _P, _P, c_size_t]),
+    "fortai_cuda_q8_group_create": (c_int, [POINTER(c_int), c_int, _PP]),
+    "fortai_cuda_q8_group_destroy": (c_int, [_P]),
+    "fortai_cuda_q8_group_device_count": (c_int, [_P]),
+    "fortai_cuda_q8_group_last_error": (c_char_p, [_P]),
+    "fortai_cuda_q8_group_weights_upload": (c_int, [_P, _P, c_size_t, c_int, c_int, c_int, _PP]),
+    "fortai_cuda_q8_group_weights_destroy": (c_int, [_P]),
+    "fortai_cuda_q8_group_matvec_f32": (c_int, [_P, _P, _P, c_size_t, _P, c_size_t, _F]),
+    "fortai_cuda_q8_group_ffn_f32": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_size_t, _F]),
     "fortai_cuda_qwen35_recurrent_step_device": (c_int, [_P, _P, c_size_t, _P, c_float]),
     "fortai_cuda_qwen35_attention_step_device": (c_int, [_P, _P, c_size_t, c_int, _P, c_float]),
     "fortai_cuda_q8_ffn_step_device": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_float]),

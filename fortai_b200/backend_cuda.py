@@ -852,3 +852,77 @@ def _attention_step_device(self, device_x, elements, position, device_norm_weigh
 
 
 cuda_qwen35_attention_t.step_device = _attention_step_device
+
+
+# --------------------------------------------------------------------------- device groups
+class cuda_q8_group_t:
+    """Several GPUs of one box driven from one host thread through the C ABI: row- and
+    column-sharded projections without torch.distributed (what a Fortran host would call)."""
+
+    def __init__(self):
+        self.handle = None
+
+    def create(self, devices) -> status_t:
+        stat = status_t()
+        ids = (ctypes.c_int * len(devices))(*[int(d) for d in devices])
+        out = c_void_p()
+        code = _lib().fortai_cuda_q8_group_create(ids, len(devices), byref(out))
+        if code != FORTAI_CUDA_OK:
+            stat.set(FORTAI_UNSUPPORTED if code == 2 else FORTAI_INVALID,
+                     "CUDA Q8 device group creation failed")
+            return stat
+        self.handle = out
+        return stat
+
+    def destroy(self):
+        if self.handle:
+            _lib().fortai_cuda_q8_group_destroy(self.handle)
+            self.handle = None
+
+    def device_count(self) -> int:
+        return int(_lib().fortai_cuda_q8_group_device_count(self.handle)) if self.handle else 0
+
+    def last_error(self) -> str:
+        raw = _lib().fortai_cuda_q8_group_last_error(self.handle if self.handle else None)
+        return raw.decode(errors="replace") if raw else ""
+
+    def upload(self, host_weights, rows: int, width: int, shard_mode: int):
+        """shard_mode 0: row ranges; 1: block (K) ranges of every row.  Returns (handle, stat)."""
+        stat = status_t()
+        data = _as_bytes(host_weights)
+        out = c_void_p()
+        code = _lib().fortai_cuda_q8_group_weights_upload(self.handle, _host_ptr(data), data.size,
+                                                          int(rows), int(width), int(shard_mode),
+                                                          byref(out))
+        if code != FORTAI_CUDA_OK:
+            stat.set(FORTAI_INVALID if code == 1 else FORTAI_UNSUPPORTED,
+                     "CUDA Q8 group weights upload failed: " + self.last_error())
+            return None, stat
+        return out, stat
+
+    @staticmethod
+    def destroy_weights(weights):
+        if weights:
+            _lib().fortai_cuda_q8_group_weights_destroy(weights)
+
+    def matvec_f32(self, weights, activation, output):
+        stat = status_t()
+        ms = c_float(0.0)
+        code = _lib().fortai_cuda_q8_group_matvec_f32(self.handle, weights, _host_ptr(activation),
+                                                      activation.size, _host_ptr(output),
+                                                      output.nbytes, byref(ms))
+        if code != FORTAI_CUDA_OK:
+            stat.set(FORTAI_INVALID if code == 1 else FORTAI_UNSUPPORTED,
+                     "CUDA Q8 group matvec failed: " + self.last_error())
+        return ms.value, stat
+
+    def ffn_f32(self, gate, up, down, activation, output):
+        stat = status_t()
+        ms = c_float(0.0)
+        code = _lib().fortai_cuda_q8_group_ffn_f32(self.handle, gate, up, down,
+                                                   _host_ptr(activation), activation.size,
+                                                   _host_ptr(output), output.nbytes, byref(ms))
+        if code != FORTAI_CUDA_OK:
+            stat.set(FORTAI_INVALID if code == 1 else FORTAI_UNSUPPORTED,
+                     "CUDA Q8 group FFN failed: " + self.last_error())
+        return ms.value, stat

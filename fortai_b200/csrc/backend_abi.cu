@@ -9,6 +9,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <chrono>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -44,6 +45,8 @@ struct fortai_cuda_q8_context {
     unsigned allgather_sequence = 0;
     int *status_host = nullptr;              // pinned + mapped: kernels write, host reads
     int *status_device = nullptr;
+    unsigned *done_host = nullptr;           // pinned + mapped: completion word of host calls
+    unsigned *done_device = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
     uint64_t launches = 0;
@@ -68,6 +71,8 @@ struct fortai_cuda_q8_context {
     int gemv_even_rounds = 1;      // half-block kernel: equal rows per warp when rounds are few
     int gemv_early_trigger = 3;    // successor may be scheduled at once: 0 never, 1 always, 2 when the grid fills the machine, 3 after a residual epilogue
     int host_direct_output = 1;    // *_host_f32: store straight into page-locked output
+    int host_spin_wait = 1;        // *_host_f32 with page-locked buffers: no copy engine, no events
+    int peer_overlap = 1;          // fused all-gather GEMVs may start under their predecessor's tail
     int gemv_overlap = 1;      // GEMVs may start under the tail of the previous kernel
     int fewtok_overlap = 1;    // product kernel may start under the prepare kernel
     int fewtok_off = 0;        // 1 = small batches run one GEMV per token
@@ -199,7 +204,8 @@ cudaError_t launch_gemv_kernel(fortai_cuda_q8_context *c, Kernel kernel, int gri
     overlap.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     overlap.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &overlap;
-    config.numAttrs = c->gemv_overlap && p.peers == 0 && p.sequence == 0 ? 1 : 0;
+    // (p.overlap_ok: a "peer" launch whose only peer is this process's own host memory)
+    config.numAttrs = c->gemv_overlap && ((p.peers == 0 && p.sequence == 0) || p.overlap_ok) ? 1 : 0;
     const cudaError_t error = cudaLaunchKernelEx(&config, kernel, p);
     ++c->launches;
     return error != cudaSuccess ? error : cudaGetLastError();
@@ -319,9 +325,20 @@ cudaError_t launch_pipelined_depth(fortai_cuda_q8_context *c, const GemvParams &
     }
     int per_sm = c->gemv_ctas_per_sm;
     if (per_sm <= 0) {
-        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem);
-        if (error != cudaSuccess) return error;
-        if (per_sm < 1) per_sm = 1;
+        // the occupancy query costs a microsecond or two per call: remember the last answer
+        static size_t cached_smem[64] = {};
+        static int cached_per_sm[64] = {};
+        const int slot = c->device & 63;
+        if (cached_per_sm[slot] > 0 && cached_smem[slot] == smem) {
+            per_sm = cached_per_sm[slot];
+        } else {
+            error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads,
+                smem);
+            if (error != cudaSuccess) return error;
+            if (per_sm < 1) per_sm = 1;
+            cached_smem[slot] = smem;
+            cached_per_sm[slot] = per_sm;
+        }
     }
     const int limit = c->sm_count * per_sm;
     const int needed = (p.total_rows + kGemvWarps - 1) / kGemvWarps;
@@ -668,6 +685,13 @@ int create_context(int device, bool borrow, cudaStream_t stream, fortai_cuda_q8_
         ok = cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->status_device),
             c->status_host, 0) == cudaSuccess;
     }
+    ok = ok && cudaHostAlloc(reinterpret_cast<void **>(&c->done_host), sizeof(unsigned),
+        cudaHostAllocMapped) == cudaSuccess;
+    if (ok) {
+        *c->done_host = 0;
+        ok = cudaHostGetDevicePointer(reinterpret_cast<void **>(&c->done_device), c->done_host,
+            0) == cudaSuccess;
+    }
     int sms = 0;
     if (ok && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) == cudaSuccess
         && sms > 0)
@@ -908,6 +932,7 @@ extern "C" int fortai_cuda_q8_context_destroy(fortai_cuda_q8_context *context) {
     cudaFree(context->scratch_aux);
     cudaFree(context->scratch_planar);
     if (context->status_host) cudaFreeHost(context->status_host);
+    if (context->done_host) cudaFreeHost(context->done_host);
     if (context->start) cudaEventDestroy(context->start);
     if (context->stop) cudaEventDestroy(context->stop);
     if (context->owns_stream && context->stream) cudaStreamDestroy(context->stream);
@@ -1723,6 +1748,8 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
     else if (!std::strcmp(name, "peer_wait_clocks_millions"))
         context->peer_wait_clocks_millions = value > 0 ? value : 2000;
     else if (!std::strcmp(name, "prefill_kind")) context->prefill_kind = value;
+    else if (!std::strcmp(name, "host_spin_wait")) context->host_spin_wait = value;
+    else if (!std::strcmp(name, "peer_overlap")) context->peer_overlap = value;
     else if (!std::strcmp(name, "fewtok_splits") && value >= 0) context->fewtok_splits = value;
     else if (!std::strcmp(name, "fewtok_threads") && value >= 0 && value <= 512 &&
              value % 32 == 0) context->fewtok_threads = value;
@@ -1789,6 +1816,60 @@ extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
     float *mapped_output = nullptr;
     if (error == cudaSuccess && context->host_direct_output && weights->width % 512 == 0)
         mapped_output = mapped_host_pointer(host_output);
+    // Both buffers page-locked and mapped: the call needs neither the copy engine nor events.
+    // A one-CTA kernel pulls the activation over PCIe into scratch (the GEMV, launched as its
+    // programmatic dependent, streams its first weights meanwhile); the GEMV stores the
+    // results into the output itself; its last CTA then writes this call's sequence number
+    // into a mapped word of the context, on which the host spins.  That takes the two event
+    // records, the DMA set-up and the driver's blocking wait out of a ~60 us call.  elapsed_ms
+    // is then host time from here to completion (it still covers both transfers).
+    const float *mapped_input = mapped_output && context->host_spin_wait && in_bytes % 16 == 0
+        ? mapped_host_pointer(host_activation) : nullptr;
+    if (error == cudaSuccess && mapped_input) {
+        const auto begin = std::chrono::steady_clock::now();
+        q8_fetch_kernel<<<1, 256, 0, context->stream>>>(
+            reinterpret_cast<const float4 *>(mapped_input),
+            reinterpret_cast<float4 *>(context->scratch_activation),
+            static_cast<int>(in_bytes / 16));
+        ++context->launches;
+        error = cudaGetLastError();
+        unsigned sequence = 0;
+        if (error == cudaSuccess) {
+            GemvParams p = single_params(context, weights, context->scratch_activation,
+                context->scratch_output);
+            p.peers = 1;
+            p.peer_outputs[0] = mapped_output;
+            p.first_row = 0;
+            // the fused all-gather tail with one rank whose flag word is host memory
+            p.peer_flags[0] = context->done_device;
+            p.my_flags = context->done_device;
+            p.cta_counter = context->cta_counter;
+            p.my_rank = 0;
+            if (++context->allgather_sequence == 0) ++context->allgather_sequence;
+            sequence = p.sequence = context->allgather_sequence;
+            p.flag_wait_clocks = static_cast<long long>(context->peer_wait_clocks_millions) *
+                1000000LL;
+            p.overlap_ok = 1;
+            error = launch_gemv(context, p, kActF32, kEpiPeers);
+        }
+        if (error == cudaSuccess) {
+            volatile unsigned *done = context->done_host;
+            bool seen = false;
+            // about two seconds of polling, then the driver's own wait
+            for (long long spin = 0; spin < (1ll << 31); ++spin) {
+                if (static_cast<int>(*done - sequence) >= 0) {
+                    seen = true;
+                    break;
+                }
+                if ((spin & 0xfffff) == 0xfffff &&
+                    std::chrono::steady_clock::now() - begin > std::chrono::seconds(2)) break;
+            }
+            if (!seen) error = cudaStreamSynchronize(context->stream);
+        }
+        *elapsed_ms = std::chrono::duration<float, std::milli>(
+            std::chrono::steady_clock::now() - begin).count();
+        return finish(context, "host F32 matvec", error);
+    }
     if (error == cudaSuccess) error = cudaEventRecord(context->start, context->stream);
     if (error == cudaSuccess)
         error = cudaMemcpyAsync(context->scratch_activation, host_activation, in_bytes,
@@ -1870,6 +1951,12 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
     if (++context->allgather_sequence == 0) ++context->allgather_sequence;   // 0 means "off"
     p.sequence = context->allgather_sequence;
     p.flag_wait_clocks = static_cast<long long>(context->peer_wait_clocks_millions) * 1000000LL;
+    // A following call of this kind may be launched while this one still waits for its peers'
+    // flags: the kernel touches neither the peers' vectors nor the shared CTA counter before
+    // its own dependency wait, which ends only when this launch has completed, so what
+    // overlaps is the successor's launch latency and its first weight requests (option
+    // "peer_overlap", default on).
+    p.overlap_ok = context->peer_overlap;
     const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-gather matvec", error);
 }
@@ -2365,3 +2452,8 @@ extern "C" int fortai_cuda_mmq_trace_read(long long *host) {
     return fortai_b200::mmq_trace_read(host) == cudaSuccess ? 0 : 2;
 }
 #endif
+
+// ---------------------------------------------------------------------------
+// device groups
+// ---------------------------------------------------------------------------
+#include "device_group.cuh"

@@ -78,6 +78,7 @@ struct GemvParams {
     unsigned sequence;
     int my_rank;
     long long flag_wait_clocks;        // how long the tail waits for a peer's flag (SM clocks)
+    int overlap_ok;                    // the only "peer" is this process: dependent launch allowed
     // optional fusions of the caller's glue (null = off): an RMS norm of the fp32
     // activation with learned scale in the prologue, and out[row] = dot + residual[row]
     // in the plain epilogue (residual may be the output vector itself)
@@ -1008,6 +1009,15 @@ q8_gemv_ring_kernel(const __grid_constant__ GemvParams p, const __grid_constant_
             if (lane == 0) mbar_arrive(&empty[s]);
         }
     }
+}
+
+// `count` 16-byte pieces from page-locked host memory (through its device alias) into
+// device memory: the host-call path's replacement for a copy-engine transfer of a few
+// kilobytes.  Its dependent, the GEMV, may start at once.
+__global__ void __launch_bounds__(256)
+q8_fetch_kernel(const float4 *__restrict__ source, float4 *__restrict__ destination, int count) {
+    grid_dependents_may_launch();
+    for (int i = threadIdx.x; i < count; i += blockDim.x) destination[i] = source[i];
 }
 
 // --------------------------------------------------------------------------

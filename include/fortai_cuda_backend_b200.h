@@ -336,6 +336,49 @@ int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context *context,
     size_t activation_elements, void *const *peer_outputs, void *const *peer_flags,
     int peer_count, int my_rank, size_t first_row, size_t output_elements);
 
+/* ----------------------------------------------------------------------- *
+ * Device groups: the sharded path for hosts that drive several GPUs of one box from one
+ * thread (the reference is single-GPU, ROADMAP.md:31; its only multi-device hook is the
+ * device index of fortai_cuda_q8_context_create, reference header :22).  A group owns one
+ * context per device, enables peer access between them and keeps, on every device, a result
+ * vector and a flag array that the others store into.  Same return codes as everything
+ * above; messages through fortai_cuda_q8_group_last_error.  Not thread-safe.
+ * ----------------------------------------------------------------------- */
+typedef struct fortai_cuda_q8_group fortai_cuda_q8_group;
+typedef struct fortai_cuda_q8_group_weights fortai_cuda_q8_group_weights;
+
+/* `count` distinct device indices (1..8), every pair peer-accessible. */
+int fortai_cuda_q8_group_create(const int *devices, int count, fortai_cuda_q8_group **group);
+int fortai_cuda_q8_group_destroy(fortai_cuda_q8_group *group);
+int fortai_cuda_q8_group_device_count(const fortai_cuda_q8_group *group);
+const char *fortai_cuda_q8_group_last_error(const fortai_cuda_q8_group *group);
+
+/* A rows x width GGUF Q8_0 matrix cut over the group's devices.  shard_mode 0: contiguous
+ * row ranges (the partition of the reference's OpenMP row loop,
+ * src/fortai_gguf_runtime.f90:457-463; multiples of 32 rows when rows % 32 == 0);
+ * shard_mode 1: block ranges of every row (the K-slices of an FFN down matrix, matching
+ * the row ranges of its gate/up partners). */
+int fortai_cuda_q8_group_weights_upload(fortai_cuda_q8_group *group, const void *host_weights,
+    size_t weight_bytes, int rows, int width, int shard_mode,
+    fortai_cuda_q8_group_weights **weights);
+int fortai_cuda_q8_group_weights_destroy(fortai_cuda_q8_group_weights *weights);
+
+/* gguf_tensor_matvec_q8 (src/fortai_gguf_runtime.f90:424-465) over a row-sharded matrix:
+ * host fp32 vector in, every device computes its slice with the GEMV fused with its
+ * all-gather, host fp32 result out.  Per-row results are bit-identical to the one-device
+ * kernel.  Blocks; elapsed_ms is host time around the call, transfers included. */
+int fortai_cuda_q8_group_matvec_f32(fortai_cuda_q8_group *group,
+    const fortai_cuda_q8_group_weights *weights, const float *host_activation,
+    size_t activation_elements, float *host_output, size_t output_bytes, float *elapsed_ms);
+
+/* fortai_cuda_q8_ffn_host's computation (reference header :97-103) with gate/up
+ * row-sharded (shard_mode 0) and down column-sharded (shard_mode 1): no exchange between
+ * the halves; the partial outputs are summed on the first device in device order. */
+int fortai_cuda_q8_group_ffn_f32(fortai_cuda_q8_group *group,
+    const fortai_cuda_q8_group_weights *gate, const fortai_cuda_q8_group_weights *up,
+    const fortai_cuda_q8_group_weights *down, const float *host_activation,
+    size_t activation_elements, float *host_output, size_t output_bytes, float *elapsed_ms);
+
 /* Has no counterpart in the reference.  Same contract and same result as
  * fortai_cuda_q8_ffn_device, for hosts that must not allocate while they run (all
  * free device memory already belongs to their own pools, or a cudaMalloc/cudaFree
