@@ -65,8 +65,9 @@ def _lib():
     return abi.load()
 
 
-def _host_ptr(array: np.ndarray) -> c_void_p:
-    return array.ctypes.data_as(c_void_p)
+def _host_ptr(array: np.ndarray) -> int:
+    # (the plain address: building a ctypes pointer object costs a microsecond more per call)
+    return array.ctypes.data
 
 
 def _as_bytes(array) -> np.ndarray:

@@ -51,14 +51,14 @@ struct fortai_cuda_q8_context {
     cudaGraphExec_t graph_exec = nullptr;
     uint64_t launches = 0;
     // options
-    int gemv_variant = 0;      // 0 auto, 1 direct, 2 ring
+    int host_flush_rows = 8;   // rows per store group into a page-locked host output
+    int peer_flush_rows = 32;  // rows per store group into peers' vectors
+    int gemv_variant = 0;      // 0 = automatic choice, 1 = always the half-block kernel
     int gemv_ctas_per_sm = 0;  // 0 = occupancy-derived
     int gemv_rows_per_warp = 0;
     int gemv_depth = 1;        // rows in flight per warp in the pipelined kernel (1 or 2)
-    int gemv_split = 1;        // warps per row in the split-row kernel: 1 off (default: it never won), 0 auto, 2/4/8
+    int gemv_split = 0;        // slice kernel: 0 automatic, 1 off, 4 or 8 warps per row
     int gemv_balance = 0;      // 1 = trim the grid so that the last round of rows is full
-    int ring_stages = 0;
-    int ring_rows = 0;
     int peer_wait_clocks_millions = 2000;   // fused all-gather: wait for a peer's flag, in 1e6 SM clocks
     int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 33)
     int prefill_kind = 0;      // tcgen05 kernel: 0 = kind::f16, activation scale folded into the operand; 1 = kind::i8, scaled per block
@@ -133,8 +133,6 @@ int fail(fortai_cuda_q8_context *context, const char *operation,
 
 const char *status_text(int code) {
     switch (code) {
-    case kStatusRingProducerTimeout: return "GEMV ring producer gave up waiting for a free stage";
-    case kStatusRingConsumerTimeout: return "GEMV ring consumer gave up waiting for a weight tile";
     case kStatusMmqLoadTimeout: return "prefill kernel gave up waiting for an operand tile";
     case kStatusMmqMmaTimeout: return "prefill kernel gave up waiting for the tensor core";
     case kStatusMmqDrainTimeout: return "prefill kernel gave up waiting for an accumulator";
@@ -344,16 +342,6 @@ cudaError_t launch_pipelined_depth(fortai_cuda_q8_context *c, const GemvParams &
     const int needed = (p.total_rows + kGemvWarps - 1) / kGemvWarps;
     const int grid = c->gemv_balance ? balanced_grid(p.total_rows, kGemvWarps, limit)
                                      : std::max(1, std::min(needed, limit));
-    if (EPI == kEpiPeers) {
-        // room for one CTA's block of results, stored to the peers as whole lines
-        const size_t staged = static_cast<size_t>((p.total_rows + grid - 1) / grid) * sizeof(float);
-        if (smem + staged > 48 * 1024) {
-            error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                static_cast<int>(smem + staged));
-            if (error != cudaSuccess) return error;
-        }
-        return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem + staged, p, limit);
-    }
     return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem, p, limit);
 }
 
@@ -363,52 +351,6 @@ cudaError_t launch_pipelined_instance(fortai_cuda_q8_context *c, const GemvParam
     if (EPI != kEpiSiluPair && EPI != kEpiStacked && c->gemv_depth == 2)
         return launch_pipelined_depth<CPL, ACT, EPI, 2>(c, p);
     return launch_pipelined_depth<CPL, ACT, EPI, 1>(c, p);
-}
-
-template <int SPLIT, int ACT, int EPI>
-cudaError_t launch_splitrow_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
-    auto kernel = q8_gemv_splitrow_kernel<SPLIT, ACT, EPI>;
-    const size_t smem = activation_smem_bytes(p.width, p.blocks);
-    cudaError_t error = cudaSuccess;
-    if (smem > 48 * 1024) {
-        error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-            static_cast<int>(smem));
-        if (error != cudaSuccess) return error;
-    }
-    int per_sm = c->gemv_ctas_per_sm;
-    if (per_sm <= 0) {
-        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem);
-        if (error != cudaSuccess) return error;
-        if (per_sm < 1) per_sm = 1;
-    }
-    const int rows_per_cta = kGemvWarps / SPLIT;
-    const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
-    const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
-    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
-    ++c->launches;
-    return cudaGetLastError();
-}
-
-// Rows are split across warps when a warp-per-row grid would have fewer than about two
-// rows per resident warp and the rows are long enough for every slice to stay busy.
-template <int ACT, int EPI>
-bool launch_splitrow(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *error) {
-    if (p.segments != 1 || c->gemv_split == 1) return false;
-    const long long resident_warps = static_cast<long long>(c->sm_count) * 4 * kGemvWarps;
-    int split = c->gemv_split;
-    if (split == 0) {
-        if (p.total_rows * 2 > resident_warps * 3 || p.blocks < 128) return false;
-        split = 2;
-        while (split < 8 && static_cast<long long>(p.total_rows) * split < resident_warps &&
-               p.blocks / (split * 2) >= 64)
-            split *= 2;
-    }
-    switch (split) {
-    case 2: *error = launch_splitrow_instance<2, ACT, EPI>(c, p); return true;
-    case 4: *error = launch_splitrow_instance<4, ACT, EPI>(c, p); return true;
-    case 8: *error = launch_splitrow_instance<8, ACT, EPI>(c, p); return true;
-    default: return false;
-    }
 }
 
 // The pipelined kernel needs width == 512 * CPL exactly and a single matrix (or the
@@ -434,10 +376,10 @@ bool launch_pipelined(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_
     }
 }
 
-template <int P, int NR, int ACT, int EPI>
-cudaError_t launch_block_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
-    auto kernel = q8_gemv_block_kernel<P, NR, ACT, EPI>;
-    const size_t smem = activation_smem_bytes(p.width, p.blocks);
+template <int G, int SPLIT, int ACT>
+cudaError_t launch_slice_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
+    auto kernel = q8_gemv_slice_kernel<G, SPLIT, ACT>;
+    const size_t smem = slice_smem_bytes(p.width, p.blocks, G);
     cudaError_t error = cudaSuccess;
     if (smem > 48 * 1024) {
         error = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -446,133 +388,83 @@ cudaError_t launch_block_instance(fortai_cuda_q8_context *c, const GemvParams &p
     }
     int per_sm = c->gemv_ctas_per_sm;
     if (per_sm <= 0) {
-        error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads, smem);
-        if (error != cudaSuccess) return error;
-        if (per_sm < 1) per_sm = 1;
+        static size_t cached_smem[64] = {};
+        static int cached_per_sm[64] = {};
+        const int slot = c->device & 63;
+        if (cached_per_sm[slot] > 0 && cached_smem[slot] == smem) {
+            per_sm = cached_per_sm[slot];
+        } else {
+            error = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kGemvThreads,
+                smem);
+            if (error != cudaSuccess) return error;
+            if (per_sm < 1) per_sm = 1;
+            cached_smem[slot] = smem;
+            cached_per_sm[slot] = per_sm;
+        }
     }
-    const int rows_per_cta = kGemvWarps * (EPI == kEpiSiluPair ? 1 : NR);
-    const int needed = (p.total_rows + rows_per_cta - 1) / rows_per_cta;
-    const int grid = std::max(1, std::min(needed, c->sm_count * per_sm));
-    kernel<<<grid, kGemvThreads, smem, c->stream>>>(p);
-    ++c->launches;
-    return cudaGetLastError();
+    // the same number of rows for every CTA (as far as the row count allows)
+    const int rows_per_round = kGemvWarps / SPLIT;
+    const int needed = (p.total_rows + rows_per_round - 1) / rows_per_round;
+    const int limit = c->sm_count * per_sm;
+    const int rounds = (needed + limit - 1) / limit;
+    const int grid = std::max(1, (needed + rounds - 1) / rounds);
+    return launch_gemv_kernel(c, kernel, grid, kGemvThreads, smem, p, limit);
 }
 
-template <int NR, int ACT, int EPI>
-cudaError_t launch_block_passes(fortai_cuda_q8_context *c, const GemvParams &p) {
-    switch ((p.blocks + 31) / 32) {
-    case 1: return launch_block_instance<1, NR, ACT, EPI>(c, p);
-    case 2: return launch_block_instance<2, NR, ACT, EPI>(c, p);
-    case 3: return launch_block_instance<3, NR, ACT, EPI>(c, p);
-    case 4: return launch_block_instance<4, NR, ACT, EPI>(c, p);
-    default: return launch_block_instance<0, NR, ACT, EPI>(c, p);
+// Few long rows: K-slices of a row on 4 or 8 warps.  Chosen by itself for plain single-matrix
+// products of at least 16 granules (8192 elements) whose rows are fewer than two rounds of a
+// warp-per-row grid; "gemv_split" = 1 turns it off, 4 or 8 force it where the shape allows.
+template <int ACT>
+bool launch_slice(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *error) {
+    if (p.segments != 1 || p.norm_weights || p.conv_weights || p.width % 512 != 0 ||
+        c->gemv_split == 1)
+        return false;
+    const int granules = p.width / 512;
+    int split = c->gemv_split;
+    if (split == 0) {
+        if (granules < 16 || p.total_rows > 2 * c->sm_count * 4 * kGemvWarps) return false;
+        split = (granules + 3) / 4 <= 9 ? 4 : 8;
     }
-}
-
-template <int ACT, int EPI>
-cudaError_t launch_block(fortai_cuda_q8_context *c, const GemvParams &p) {
-    if (EPI == kEpiSiluPair || EPI == kEpiBlockDots || EPI == kEpiPeers)
-        return launch_block_passes<1, ACT, EPI>(c, p);
-    const int passes = (p.blocks + 31) / 32;
-    int rows_per_warp = c->gemv_rows_per_warp;
-    if (rows_per_warp <= 0) rows_per_warp = passes <= 2 ? 2 : 1;
-    return rows_per_warp == 2 ? launch_block_passes<2, ACT, kEpiPlain>(c, p)
-                              : launch_block_passes<1, ACT, kEpiPlain>(c, p);
-}
-
-bool ring_plan(const fortai_cuda_q8_context *c, const GemvParams &p, int epi, RingConfig *cfg) {
-    const int copies = epi == kEpiSiluPair ? 2 : 1;
-    const size_t stride = static_cast<size_t>(p.row_stride);
-    int rows = c->ring_rows;
-    if (rows <= 0) {
-        rows = static_cast<int>((24 * 1024) / (stride * copies));
-        rows = std::max(kRingConsumerWarps, std::min(64, rows / kRingConsumerWarps *
-            kRingConsumerWarps));
+    const int most = (granules + split - 1) / split;
+    if (most > 9 || granules < split) return false;
+    if (split == 4) {
+        if (most <= 3) *error = launch_slice_instance<3, 4, ACT>(c, p);
+        else if (most <= 5) *error = launch_slice_instance<5, 4, ACT>(c, p);
+        else *error = launch_slice_instance<9, 4, ACT>(c, p);
+    } else if (split == 8) {
+        if (most <= 3) *error = launch_slice_instance<3, 8, ACT>(c, p);
+        else if (most <= 5) *error = launch_slice_instance<5, 8, ACT>(c, p);
+        else *error = launch_slice_instance<9, 8, ACT>(c, p);
+    } else {
+        return false;
     }
-    const size_t stage = rows * stride * copies;
-    const size_t budget = 200 * 1024 - activation_smem_bytes(p.width, p.blocks) - 512;
-    if (stage * 2 > budget || stage * copies >= (1u << 20)) return false;
-    int stages = c->ring_stages > 0 ? c->ring_stages : kRingMaxStages;
-    stages = std::min<int>(stages, static_cast<int>(budget / stage));
-    stages = std::max(2, std::min(kRingMaxStages, stages));
-    cfg->stages = stages;
-    cfg->rows_per_tile = rows;
-    cfg->stage_bytes = static_cast<int>(stage);
-    cfg->tiles = (p.total_rows + rows - 1) / rows;
     return true;
 }
 
-template <int ACT, int EPI>
-cudaError_t launch_ring(fortai_cuda_q8_context *c, const GemvParams &p, const RingConfig &cfg) {
-    auto kernel = q8_gemv_ring_kernel<ACT, EPI>;
-    const size_t smem = ring_smem_bytes(p.width, p.blocks, cfg);
-    cudaError_t error = cudaFuncSetAttribute(kernel,
-        cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (error != cudaSuccess) return error;
-    const int grid = std::max(1, std::min(cfg.tiles, c->sm_count));
-    kernel<<<grid, kRingThreads, smem, c->stream>>>(p, cfg);
-    ++c->launches;
-    return cudaGetLastError();
-}
-
-// The automatic choice: the ring pays off once a matrix no longer fits in L2 and
-// is a single (or gate/up) stream; everything else takes the direct kernel.
-bool want_ring(const fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
-    if (epi == kEpiBlockDots) return false;
-    if (epi == kEpiPlain && p.segments != 1) return false;
-    return c->gemv_variant == 2;
-}
-
+// Kernel choice: the slice kernel for few long rows, the pipelined kernel where the width is
+// one of its granule counts, else the half-block kernel ("gemv_variant" = 1: always that one).
 template <int ACT>
 cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int epi) {
-    if (p.norm_weights || p.residual || p.conv_weights) {
-        // the fused norm / residual live in the pipelined and the half-block kernel only
-        cudaError_t error = cudaSuccess;
-        if (epi == kEpiSiluPair) {
-            if (launch_pipelined<ACT, kEpiSiluPair>(c, p, &error)) return error;
-            return launch_direct<ACT, kEpiSiluPair>(c, p);
-        }
-        if (epi != kEpiPlain) return cudaErrorNotSupported;
-        if (p.segments > 1 && launch_pipelined<ACT, kEpiStacked>(c, p, &error)) return error;
-        if (launch_pipelined<ACT, kEpiPlain>(c, p, &error)) return error;
-        return launch_direct<ACT, kEpiPlain>(c, p);
-    }
-    RingConfig cfg;
-    const bool ring = want_ring(c, p, epi) && ring_plan(c, p, epi, &cfg);
-    // automatic: the pipelined kernel where the shape allows, else the half-block kernel
-    const bool half_block = c->gemv_variant <= 1 || c->gemv_variant == 4;
-    if (c->gemv_variant == 0 && (epi == kEpiPlain || epi == kEpiPeers)) {
-        cudaError_t error = cudaSuccess;
-        const bool done = epi == kEpiPlain ? launch_splitrow<ACT, kEpiPlain>(c, p, &error)
-                                           : launch_splitrow<ACT, kEpiPeers>(c, p, &error);
-        if (done) return error;
-    }
-    if (c->gemv_variant == 0 || c->gemv_variant == 4) {
+    // the fused norm, residual and convolution exist for the plain and gate/up epilogues only
+    if ((p.norm_weights || p.residual || p.conv_weights) && epi != kEpiPlain &&
+        epi != kEpiSiluPair)
+        return cudaErrorNotSupported;
+    if (c->gemv_variant == 0) {
         cudaError_t error = cudaSuccess;
         bool done = false;
+        if (epi == kEpiPlain && launch_slice<ACT>(c, p, &error)) return error;
         if (epi == kEpiPlain && p.segments > 1)
             done = launch_pipelined<ACT, kEpiStacked>(c, p, &error);
-        else if (epi == kEpiPlain) done = launch_pipelined<ACT, kEpiPlain>(c, p, &error);
+        if (!done && epi == kEpiPlain) done = launch_pipelined<ACT, kEpiPlain>(c, p, &error);
         else if (epi == kEpiSiluPair) done = launch_pipelined<ACT, kEpiSiluPair>(c, p, &error);
         else if (epi == kEpiPeers) done = launch_pipelined<ACT, kEpiPeers>(c, p, &error);
         if (done) return error;
     }
     switch (epi) {
-    case kEpiPlain:
-        if (ring) return launch_ring<ACT, kEpiPlain>(c, p, cfg);
-        return half_block ? launch_direct<ACT, kEpiPlain>(c, p) : launch_block<ACT, kEpiPlain>(c, p);
-    case kEpiSiluPair:
-        if (ring) return launch_ring<ACT, kEpiSiluPair>(c, p, cfg);
-        return half_block ? launch_direct<ACT, kEpiSiluPair>(c, p)
-                          : launch_block<ACT, kEpiSiluPair>(c, p);
-    case kEpiPeers:
-        // the fused all-gather tail lives in the pipelined and half-block kernels
-        if (p.sequence != 0) return launch_direct<ACT, kEpiPeers>(c, p);
-        if (ring) return launch_ring<ACT, kEpiPeers>(c, p, cfg);
-        return half_block ? launch_direct<ACT, kEpiPeers>(c, p) : launch_block<ACT, kEpiPeers>(c, p);
-    default:
-        return half_block ? launch_direct<kActQ8, kEpiBlockDots>(c, p)
-                          : launch_block<kActQ8, kEpiBlockDots>(c, p);
+    case kEpiPlain: return launch_direct<ACT, kEpiPlain>(c, p);
+    case kEpiSiluPair: return launch_direct<ACT, kEpiSiluPair>(c, p);
+    case kEpiPeers: return launch_direct<ACT, kEpiPeers>(c, p);
+    default: return launch_direct<kActQ8, kEpiBlockDots>(c, p);
     }
 }
 
@@ -799,6 +691,7 @@ int matvec_host_many(fortai_cuda_q8_context *c, const HostRequest *requests, int
         GemvParams p = single_params(c, first, c->scratch_activation, c->scratch_output);
         p.peers = 1;
         p.peer_outputs[0] = mapped_output;
+            p.peer_flush = c->host_flush_rows;
         error = launch_gemv(c, p, kActQ8, kEpiPeers);
     } else if (error == cudaSuccess) {
         GemvParams p = {};
@@ -1730,20 +1623,23 @@ extern "C" int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *contex
 extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context,
     const char *name, int value) {
     if (!context || !name || value < 0) return FORTAI_CUDA_INVALID;
-    if (!std::strcmp(name, "gemv_variant") && value <= 4) context->gemv_variant = value;
+    if (!std::strcmp(name, "gemv_variant") && value <= 1) context->gemv_variant = value;
+    else if (!std::strcmp(name, "host_flush_rows") && value >= 1 && value <= 32 &&
+             (value & (value - 1)) == 0)
+        context->host_flush_rows = static_cast<int>(value);
+    else if (!std::strcmp(name, "peer_flush_rows") && value >= 1 && value <= 32 &&
+             (value & (value - 1)) == 0)
+        context->peer_flush_rows = static_cast<int>(value);
     else if (!std::strcmp(name, "gemv_ctas_per_sm") && value <= 32)
         context->gemv_ctas_per_sm = value;
     else if (!std::strcmp(name, "gemv_rows_per_warp") && value <= 2)
         context->gemv_rows_per_warp = value;
     else if (!std::strcmp(name, "gemv_balance") && value <= 1) context->gemv_balance = value;
     else if (!std::strcmp(name, "planar_min_width")) context->planar_min_width = value;
-    else if (!std::strcmp(name, "gemv_split") && (value <= 2 || value == 4 || value == 8))
+    else if (!std::strcmp(name, "gemv_split") && (value <= 1 || value == 4 || value == 8))
         context->gemv_split = value;
     else if (!std::strcmp(name, "gemv_depth") && value >= 1 && value <= 2)
         context->gemv_depth = value;
-    else if (!std::strcmp(name, "ring_stages") && value <= kRingMaxStages)
-        context->ring_stages = value;
-    else if (!std::strcmp(name, "ring_rows") && value <= 256) context->ring_rows = value;
     else if (!std::strcmp(name, "mmq_min_tokens")) context->mmq_min_tokens = value;
     else if (!std::strcmp(name, "peer_wait_clocks_millions"))
         context->peer_wait_clocks_millions = value > 0 ? value : 2000;
@@ -1839,6 +1735,7 @@ extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
                 context->scratch_output);
             p.peers = 1;
             p.peer_outputs[0] = mapped_output;
+            p.peer_flush = context->host_flush_rows;
             p.first_row = 0;
             // the fused all-gather tail with one rank whose flag word is host memory
             p.peer_flags[0] = context->done_device;
@@ -1880,6 +1777,7 @@ extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
         if (mapped_output) {
             p.peers = 1;
             p.peer_outputs[0] = mapped_output;
+            p.peer_flush = context->host_flush_rows;
             p.first_row = 0;
             error = launch_gemv(context, p, kActF32, kEpiPeers);
         } else {
@@ -1911,6 +1809,7 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *co
     GemvParams p = single_params(context, weights, device_activation, nullptr);
     for (int i = 0; i < peer_count; ++i) p.peer_outputs[i] = static_cast<float *>(peer_outputs[i]);
     p.peers = peer_count;
+    p.peer_flush = context->peer_flush_rows;
     p.first_row = static_cast<int>(first_row);
     const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "peer-output matvec", error);
@@ -1944,6 +1843,7 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
         p.peer_flags[i] = static_cast<unsigned *>(peer_flags[i]);
     }
     p.peers = peer_count;
+    p.peer_flush = context->peer_flush_rows;
     p.first_row = static_cast<int>(first_row);
     p.my_flags = static_cast<unsigned *>(peer_flags[my_rank]);
     p.cta_counter = context->cta_counter;

@@ -29,8 +29,6 @@ constexpr int kSmCountB200 = 148;
 // waits ran out.  Zero means no kernel gave up.
 enum DeviceStatus : int {
     kStatusOk = 0,
-    kStatusRingProducerTimeout = 1,
-    kStatusRingConsumerTimeout = 2,
     kStatusMmqLoadTimeout = 3,
     kStatusMmqMmaTimeout = 4,
     kStatusMmqDrainTimeout = 5,

@@ -15,13 +15,14 @@
 // path.
 //
 // This is HBM-streaming integer/byte work (about 1.9 int-ops per weight byte),
-// so no tensor cores: the design goal is bytes in flight.  Two variants:
-//   direct  persistent warps, each lane issues U 16-byte no-allocate loads per
-//           row before consuming any of them;
-//   ring    one producer thread per CTA feeds a shared-memory ring of row tiles
-//           with 1-D bulk asynchronous copies (the TMA engine) completed on
-//           mbarriers; eight consumer warps dequant-and-dot out of shared
-//           memory.  Every barrier wait is bounded and reports a status word.
+// so no tensor cores: the design goal is bytes in flight.  Three kernels:
+//   pipelined   persistent warps, one row (or gate/up row pair) per warp at a time, the
+//               next row requested while the current one is reduced; widths that are a
+//               whole number of 512-element granules (the default where it applies);
+//   slice       the same inner loop over K-slices of a row shared by 2, 4 or 8 warps,
+//               for few long rows;
+//   half-block  (q8_gemv_direct_kernel) any width, U loads per lane in flight; also
+//               carries the int32 block-dot probe and the convolution epilogue.
 #pragma once
 
 #include "q8_common.cuh"
@@ -79,6 +80,11 @@ struct GemvParams {
     int my_rank;
     long long flag_wait_clocks;        // how long the tail waits for a peer's flag (SM clocks)
     int overlap_ok;                    // the only "peer" is this process: dependent launch allowed
+    // peer outputs of the pipelined kernel: a warp stores its results every `peer_flush`
+    // finished rows (a power of two up to 32; 0 = 32).  32 rows make one 128-byte line per
+    // store (NVLink peers); 8 keep a slow link (a page-locked host vector behind PCIe) busy
+    // throughout the kernel instead of handing it the whole vector at the end.
+    int peer_flush;
     // optional fusions of the caller's glue (null = off): an RMS norm of the fp32
     // activation with learned scale in the prologue, and out[row] = dot + residual[row]
     // in the plain epilogue (residual may be the output vector itself)
@@ -390,82 +396,6 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
 }
 
 // --------------------------------------------------------------------------
-// split-row variant: few rows, long rows (FFN down projections)
-// --------------------------------------------------------------------------
-// With fewer rows than resident warps (5120 rows of 18.5 KB on 4736 warps) a
-// warp-per-row grid leaves most of the machine idle in its last round.  Here SPLIT
-// adjacent warps of a CTA share a row: each takes a contiguous K-slice (a whole
-// number of blocks), and the SPLIT partial sums meet in shared memory.  Same lane
-// mapping and arithmetic as the half-block kernel; only the fp32 summation order
-// differs.
-template <int SPLIT, int ACT, int EPI>
-__global__ void __launch_bounds__(kGemvThreads)
-q8_gemv_splitrow_kernel(const __grid_constant__ GemvParams p) {
-    extern __shared__ __align__(16) uint8_t gemv_smem[];
-    __shared__ float partial[kGemvWarps];
-    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
-    __syncthreads();
-    const int4 *act_q = reinterpret_cast<const int4 *>(gemv_smem);
-    const float *act_s = reinterpret_cast<const float *>(gemv_smem + p.width);
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    constexpr int ROWS_PER_ROUND = kGemvWarps / SPLIT;
-    constexpr int U = 8;
-    const int slice = warp % SPLIT;
-    const int blocks_per_slice = (p.blocks + SPLIT - 1) / SPLIT;
-    const int chunk_begin = min(p.blocks, slice * blocks_per_slice) * 2;
-    const int chunk_end = min(p.blocks, (slice + 1) * blocks_per_slice) * 2;
-    const size_t stride = static_cast<size_t>(p.row_stride);
-
-    for (int first = blockIdx.x * ROWS_PER_ROUND; first < p.total_rows;
-         first += gridDim.x * ROWS_PER_ROUND) {
-        const int row = first + warp / SPLIT;
-        const bool row_ok = row < p.total_rows;
-        const uint8_t *base = p.weights[0] + static_cast<size_t>(row_ok ? row : first) * stride;
-        float acc = 0.0f;
-        for (int c0 = chunk_begin; c0 < chunk_end; c0 += 32 * U) {
-            int4 w[U];
-            uint16_t d[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int idx = c0 + u * 32 + lane;
-                if (idx < chunk_end) {
-                    w[u] = ldg_stream_16(base + static_cast<size_t>(idx) * 16);
-                    d[u] = ldg_stream_u16(base + p.width + (idx >> 1) * 2);
-                } else {
-                    w[u] = make_int4(0, 0, 0, 0);
-                    d[u] = 0;
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int idx = c0 + u * 32 + lane;
-                const bool ok = idx < chunk_end;
-                const int4 a = ok ? act_q[idx] : make_int4(0, 0, 0, 0);
-                const float sa = ok ? act_s[idx >> 1] : 0.0f;
-                acc = fmaf(half_bits_to_float(d[u]) * sa, static_cast<float>(dot16(w[u], a)), acc);
-            }
-        }
-        acc = warp_sum(acc);
-        if (lane == 0) partial[warp] = acc;
-        __syncthreads();
-        if (lane == 0 && slice == 0 && row_ok) {
-            float total = 0.0f;
-#pragma unroll
-            for (int k = 0; k < SPLIT; ++k) total += partial[warp + k];
-            if (EPI == kEpiPeers) {
-                for (int peer = 0; peer < p.peers; ++peer)
-                    p.peer_outputs[peer][p.first_row + row] = total;
-            } else {
-                p.outputs[0][row] = total;
-            }
-        }
-        __syncthreads();
-    }
-    if (EPI == kEpiPeers) peer_allgather_tail(p);
-}
-
-// --------------------------------------------------------------------------
 // pipelined variant: two rows in flight per warp, one request for a row's scales
 // --------------------------------------------------------------------------
 // Same lane mapping as the half-block kernel (lane l owns 16-byte chunks l,
@@ -556,24 +486,28 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         warp_in_cta * ROWS * (2 * CPL * 16);
 
     // Row assignment.  Ordinary outputs: grid-stride over warps (warp g takes rows g,
-    // g + W, ...).  Peer outputs: each CTA takes one contiguous block of rows, collects
-    // its results in shared memory and stores them to every peer as whole 128-byte lines
-    // at the end - one NVLink packet per 32 rows instead of one per row.
-    int row, row_step, row_end, cta_first = 0;
+    // g + W, ...).  Peer outputs: each CTA takes one contiguous block of rows and each of
+    // its warps a contiguous run inside it; a warp keeps its results in its lanes (row i of
+    // the run in lane i mod 32) and stores them to every peer a group at a time, so that
+    // the link carries whole sectors or lines, spread over the kernel's duration.
+    int row, row_step, row_end, warp_first = 0;
     if (EPI == kEpiPeers) {
         const int per_cta = (p.total_rows + gridDim.x - 1) / gridDim.x;
-        cta_first = blockIdx.x * per_cta;
-        row = cta_first + warp_in_cta;
-        row_step = kGemvWarps;
-        row_end = min(p.total_rows, cta_first + per_cta);
+        const int per_warp = (per_cta + kGemvWarps - 1) / kGemvWarps;
+        const int cta_end = min(p.total_rows, (static_cast<int>(blockIdx.x) + 1) * per_cta);
+        warp_first = blockIdx.x * per_cta + warp_in_cta * per_warp;
+        row = warp_first;
+        row_step = 1;
+        row_end = min(cta_end, warp_first + per_warp);
     } else {
         row = blockIdx.x * kGemvWarps + warp_in_cta;
         row_step = gridDim.x * kGemvWarps;
         row_end = p.total_rows;
     }
     const size_t step = stride * row_step;
-    float *staged = reinterpret_cast<float *>(gemv_smem +
-        pipelined_smem_bytes(p.width, p.blocks, CPL, ROWS));
+    const int flush_mask = (p.peer_flush > 0 ? p.peer_flush : 32) - 1;
+    float held = 0.0f;
+    int flushed = 0;
 
     // several stacked matrices (plain epilogue, one row in flight): the row's matrix and
     // local index are looked up per row instead of stepping one base pointer
@@ -624,11 +558,21 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         float total[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) total[r] = warp_sum(partial[r]);
-        if (lane == 0) {
+        if (EPI == kEpiPeers) {
+            // every lane holds the sum (butterfly); lane i mod 32 keeps row i of the run
+            const int done = finished - warp_first + 1;
+            if (lane == ((done - 1) & 31)) held = total[0];
+            if ((done & flush_mask) == 0 || row >= row_end) {
+                const int mine = flushed + ((lane - flushed) & 31);
+                if (mine < done) {
+                    for (int peer = 0; peer < p.peers; ++peer)
+                        p.peer_outputs[peer][p.first_row + warp_first + mine] = held;
+                }
+                flushed = done;
+            }
+        } else if (lane == 0) {
             if (EPI == kEpiSiluPair) {
                 p.outputs[0][finished] = silu_mul(total[0], total[ROWS - 1]);
-            } else if (EPI == kEpiPeers) {
-                staged[finished - cta_first] = total[0];
             } else if (stacked) {
                 float value = total[0];
                 if (p.conv_weights && finished < p.conv_rows)
@@ -650,365 +594,109 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         }
     }
     grid_dependents_may_launch();
-    if (EPI == kEpiPeers) {
-        __syncthreads();
-        const int count = row_end - cta_first;
-        for (int peer = 0; peer < p.peers; ++peer) {
-            float *dst = p.peer_outputs[peer] + p.first_row + cta_first;
-            for (int i = threadIdx.x; i < count; i += kGemvThreads) dst[i] = staged[i];
-        }
-    }
     if (EPI == kEpiPeers) peer_allgather_tail(p);
 }
 
 // --------------------------------------------------------------------------
-// block-per-lane variant: one 32-byte load fetches a whole Q8_0 block
+// slice variant: few long rows (FFN down projections)
 // --------------------------------------------------------------------------
-// Lane l owns blocks l, l + 32, ... of a row, so every int32 block dot is formed
-// inside one lane (eight dp4a) and no shuffle is needed before scaling.  With
-// P > 0 the row has at most 32 * P blocks and the lane's share of the quantized
-// activation (P blocks, 9 registers each) stays in registers for the whole
-// kernel; with P == 0 the activation is read from shared memory.  Compared with
-// the half-block kernel above this issues about a quarter of the instructions
-// per weight byte, which is what keeps the SM clock up under the power cap.
-struct Block32 {
-    int4 lo, hi;
-};
-
-__device__ __forceinline__ Block32 ldg_stream_32(const void *address) {
-    Block32 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v8.s32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(v.lo.x), "=r"(v.lo.y), "=r"(v.lo.z), "=r"(v.lo.w), "=r"(v.hi.x),
-                   "=r"(v.hi.y), "=r"(v.hi.z), "=r"(v.hi.w)
-                 : "l"(address));
-    return v;
+// 5120 rows of 18.5 KB on 4736 resident warps are 1.08 rounds of a warp-per-row grid, and
+// one warp cannot keep enough of an 18 KB row in flight.  Here SPLIT adjacent warps of a CTA
+// share a row, as the reference's long-row kernel does with four warps
+// (backend/cuda/fortai_cuda_backend.cu:88-126): each takes a contiguous slice of whole
+// 512-element granules (at most G of them, the counts differing by at most one), with the
+// pipelined kernel's structure - one request for the slice's scales, immediate offsets, the
+// next row's slice requested as soon as the registers are free.  The SPLIT partial sums meet
+// in shared memory and are added in slice order by the first warp of the row, so the result
+// does not depend on timing.  Per half-block the arithmetic is that of the pipelined kernel.
+template <int G>
+__device__ __forceinline__ void slice_issue(RowRegs<G> &regs, const uint8_t *quants,
+    const uint8_t *scales, int lane, int count) {
+#pragma unroll
+    for (int u = 0; u < G; ++u)
+        if (u < count) regs.w[u] = ldg_stream_16(quants + u * 512);
+    if (lane < 2 * count) regs.scales = ldg_stream_16(scales);
 }
 
-__device__ __forceinline__ int dot32(const Block32 &w, const Block32 &a) {
-    return dot16(w.hi, a.hi) + dot16(w.lo, a.lo);
-}
-
-template <int P, int NR, int ACT, int EPI>
-__global__ void __launch_bounds__(kGemvThreads)
-q8_gemv_block_kernel(const __grid_constant__ GemvParams p) {
-    extern __shared__ __align__(16) uint8_t gemv_smem[];
-    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
-    __syncthreads();
-    const int4 *act_q = reinterpret_cast<const int4 *>(gemv_smem);
-    const float *act_s = reinterpret_cast<const float *>(gemv_smem + p.width);
-    const int lane = threadIdx.x & 31;
-    const int warp = blockIdx.x * kGemvWarps + (threadIdx.x >> 5);
-    const int warps = gridDim.x * kGemvWarps;
-    const int blocks = p.blocks;
-    const size_t stride = static_cast<size_t>(p.row_stride);
-    constexpr int PR = P > 0 ? P : 1;
-    constexpr int ROWS_AT_ONCE = EPI == kEpiSiluPair ? 2 : NR;
-
-    // register image of this lane's activation blocks (P > 0 only)
-    Block32 a_reg[PR];
-    float sa_reg[PR];
-    if (P > 0) {
-#pragma unroll
-        for (int u = 0; u < PR; ++u) {
-            const int b = u * 32 + lane;
-            const bool ok = b < blocks;
-            a_reg[u].lo = ok ? act_q[2 * b] : make_int4(0, 0, 0, 0);
-            a_reg[u].hi = ok ? act_q[2 * b + 1] : make_int4(0, 0, 0, 0);
-            sa_reg[u] = ok ? act_s[b] : 0.0f;
-        }
-    }
-    const int lane_q = lane * 32;   // byte offset of the lane's first block in a row
-    const int lane_s = p.width + lane * 2;
-
-    for (int first = warp * NR; first < p.total_rows; first += warps * NR) {
-        const uint8_t *base[ROWS_AT_ONCE];
-        int local_row[ROWS_AT_ONCE];
-        int seg_of[ROWS_AT_ONCE];
-#pragma unroll
-        for (int r = 0; r < ROWS_AT_ONCE; ++r) {
-            if (EPI == kEpiSiluPair) {
-                local_row[r] = first;
-                seg_of[r] = r;
-            } else {
-                int row = first + r;
-                if (row >= p.total_rows) row = first;
-                int seg = 0;
-                if (EPI == kEpiPlain && p.segments > 1) {
-#pragma unroll
-                    for (int s = 0; s < kMaxSegments - 1; ++s)
-                        if (seg == s && s + 1 < p.segments && row >= p.rows[s]) {
-                            row -= p.rows[s];
-                            seg = s + 1;
-                        }
-                }
-                local_row[r] = row;
-                seg_of[r] = seg;
-            }
-            base[r] = p.weights[seg_of[r]] + local_row[r] * stride;
-        }
-        float acc[ROWS_AT_ONCE];
-#pragma unroll
-        for (int r = 0; r < ROWS_AT_ONCE; ++r) acc[r] = 0.0f;
-
-        if (P > 0) {
-            Block32 w[ROWS_AT_ONCE][PR];
-            uint16_t d[ROWS_AT_ONCE][PR];
-#pragma unroll
-            for (int u = 0; u < PR; ++u) {
-                // only the last pass can be ragged
-                const bool ok = (u + 1 < PR) || (u * 32 + lane < blocks);
-#pragma unroll
-                for (int r = 0; r < ROWS_AT_ONCE; ++r) {
-                    if (ok) {
-                        w[r][u] = ldg_stream_32(base[r] + lane_q + u * 1024);
-                        d[r][u] = ldg_stream_u16(base[r] + lane_s + u * 64);
-                    } else {
-                        w[r][u].lo = w[r][u].hi = make_int4(0, 0, 0, 0);
-                        d[r][u] = 0;
-                    }
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < PR; ++u) {
-#pragma unroll
-                for (int r = 0; r < ROWS_AT_ONCE; ++r) {
-                    const int dot = dot32(w[r][u], a_reg[u]);
-                    acc[r] = fmaf(half_bits_to_float(d[r][u]) * sa_reg[u],
-                        static_cast<float>(dot), acc[r]);
-                    if (EPI == kEpiBlockDots && u * 32 + lane < blocks)
-                        reinterpret_cast<int32_t *>(p.outputs[0])[
-                            static_cast<size_t>(local_row[r]) * blocks + u * 32 + lane] = dot;
-                }
-            }
-        } else {
-            constexpr int U = 4;
-            for (int b0 = 0; b0 < blocks; b0 += 32 * U) {
-                Block32 w[ROWS_AT_ONCE][U];
-                uint16_t d[ROWS_AT_ONCE][U];
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int b = b0 + u * 32 + lane;
-                    const bool ok = b < blocks;
-#pragma unroll
-                    for (int r = 0; r < ROWS_AT_ONCE; ++r) {
-                        if (ok) {
-                            w[r][u] = ldg_stream_32(base[r] + static_cast<size_t>(b) * 32);
-                            d[r][u] = ldg_stream_u16(base[r] + p.width + b * 2);
-                        } else {
-                            w[r][u].lo = w[r][u].hi = make_int4(0, 0, 0, 0);
-                            d[r][u] = 0;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int b = b0 + u * 32 + lane;
-                    const bool ok = b < blocks;
-                    Block32 a;
-                    a.lo = ok ? act_q[2 * b] : make_int4(0, 0, 0, 0);
-                    a.hi = ok ? act_q[2 * b + 1] : make_int4(0, 0, 0, 0);
-                    const float sa = ok ? act_s[b] : 0.0f;
-#pragma unroll
-                    for (int r = 0; r < ROWS_AT_ONCE; ++r) {
-                        const int dot = dot32(w[r][u], a);
-                        acc[r] = fmaf(half_bits_to_float(d[r][u]) * sa, static_cast<float>(dot),
-                            acc[r]);
-                        if (EPI == kEpiBlockDots && ok)
-                            reinterpret_cast<int32_t *>(p.outputs[0])[
-                                static_cast<size_t>(local_row[r]) * blocks + b] = dot;
-                    }
-                }
-            }
-        }
-
-        if (EPI == kEpiSiluPair) {
-            const float gate = warp_sum(acc[0]);
-            const float up = warp_sum(acc[ROWS_AT_ONCE - 1]);
-            if (lane == 0) p.outputs[0][first] = silu_mul(gate, up);
-        } else {
-#pragma unroll
-            for (int r = 0; r < ROWS_AT_ONCE; ++r) {
-                const float total = warp_sum(acc[r]);
-                if (lane == 0 && first + r < p.total_rows) {
-                    if (EPI == kEpiPlain) {
-                        p.outputs[seg_of[r]][local_row[r]] = total;
-                    } else if (EPI == kEpiPeers) {
-                        for (int peer = 0; peer < p.peers; ++peer)
-                            p.peer_outputs[peer][p.first_row + local_row[r]] = total;
-                    }
-                }
-            }
-        }
-    }
-}
-
-// --------------------------------------------------------------------------
-// ring variant
-// --------------------------------------------------------------------------
-constexpr int kRingConsumerWarps = 8;
-constexpr int kRingThreads = (kRingConsumerWarps + 1) * 32;
-constexpr int kRingMaxStages = 16;
-
-struct RingConfig {
-    int stages;         // 2..kRingMaxStages
-    int rows_per_tile;  // rows of one matrix per stage
-    int stage_bytes;    // rows_per_tile * row_stride * (2 for the SiLU pair)
-    int tiles;          // ceil(total_rows / rows_per_tile)
-};
-
-__host__ __device__ inline size_t ring_smem_bytes(int width, int blocks, const RingConfig &cfg) {
-    size_t bytes = activation_smem_bytes(width, blocks);
-    bytes += 2 * kRingMaxStages * sizeof(uint64_t);
-    bytes = (bytes + 127) & ~size_t(127);
-    return bytes + static_cast<size_t>(cfg.stages) * cfg.stage_bytes;
-}
-
-__device__ __forceinline__ float row_dot_shared(const uint8_t *row, const int4 *act_q,
-    const float *act_s, int width, int nchunks, int lane) {
+template <int G>
+__device__ __forceinline__ float slice_consume(const RowRegs<G> &regs, const int4 *act_lane,
+    const float *scale_lane, uint8_t *slot, int lane, int count) {
+    if (lane < 2 * count) *reinterpret_cast<int4 *>(slot + lane * 16) = regs.scales;
+    __syncwarp();
     float acc = 0.0f;
-    const int passes = (nchunks + 31) >> 5;
-#pragma unroll 4
-    for (int pass = 0; pass < passes; ++pass) {
-        const int idx = pass * 32 + lane;
-        const bool ok = idx < nchunks;
-        const int safe = ok ? idx : 0;
-        const int4 w = *reinterpret_cast<const int4 *>(row + safe * 16);
-        const uint16_t d = *reinterpret_cast<const uint16_t *>(row + width + (safe >> 1) * 2);
-        const int4 a = act_q[safe];
-        const float sa = (ok && !(lane & 1)) ? act_s[safe >> 1] : 0.0f;
-        int dot = ok ? dot16(w, a) : 0;
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        acc = fmaf(half_bits_to_float(d) * sa, static_cast<float>(dot), acc);
+#pragma unroll
+    for (int u = 0; u < G; ++u) {
+        if (u < count) {
+            const uint16_t dw =
+                *reinterpret_cast<const uint16_t *>(slot + ((lane >> 1) + u * 16) * 2);
+            const int4 a = act_lane[u * 32];
+            const float sa = scale_lane[u * 16];
+            acc = fmaf(half_bits_to_float(dw) * sa, static_cast<float>(dot16(regs.w[u], a)), acc);
+        }
     }
+    __syncwarp();
     return acc;
 }
 
-template <int ACT, int EPI>
-__global__ void __launch_bounds__(kRingThreads, 1)
-q8_gemv_ring_kernel(const __grid_constant__ GemvParams p, const __grid_constant__ RingConfig cfg) {
-    extern __shared__ __align__(128) uint8_t ring_smem[];
-    const size_t act_bytes = activation_smem_bytes(p.width, p.blocks);
-    uint64_t *full = reinterpret_cast<uint64_t *>(ring_smem + act_bytes);
-    uint64_t *empty = full + kRingMaxStages;
-    uint8_t *stages = ring_smem +
-        ((act_bytes + 2 * kRingMaxStages * sizeof(uint64_t) + 127) & ~size_t(127));
-    __shared__ int abort_flag;
+__host__ __device__ inline size_t slice_smem_bytes(int width, int blocks, int granules) {
+    return activation_smem_bytes(width, blocks) +
+        static_cast<size_t>(kGemvWarps) * (2 * granules * 16);
+}
 
-    const int warp = threadIdx.x >> 5;
+template <int G, int SPLIT, int ACT>
+__global__ void __launch_bounds__(kGemvThreads)
+q8_gemv_slice_kernel(const __grid_constant__ GemvParams p) {
+    if (p.trigger_early) grid_dependents_may_launch();
+    extern __shared__ __align__(16) uint8_t gemv_smem[];
+    __shared__ float partial[2][kGemvWarps];
+    constexpr int ROWS_PER_ROUND = kGemvWarps / SPLIT;
     const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int slice = warp % SPLIT;
+    const int group = warp / SPLIT;
+    const int granules = p.width >> 9;
+    const int begin = slice * granules / SPLIT;
+    const int count = (slice + 1) * granules / SPLIT - begin;      // <= G by the launcher
     const size_t stride = static_cast<size_t>(p.row_stride);
-    const int copies = EPI == kEpiSiluPair ? 2 : 1;
+    uint8_t *slot = gemv_smem + activation_smem_bytes(p.width, p.blocks) + warp * (2 * G * 16);
 
-    if (threadIdx.x == 0) {
-        abort_flag = 0;
-        for (int s = 0; s < cfg.stages; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], kRingConsumerWarps);
-        }
-        mbar_fence_init();
-    }
+    int row = blockIdx.x * ROWS_PER_ROUND + group;
+    const int row_step = gridDim.x * ROWS_PER_ROUND;
+    const size_t step = stride * row_step;
+    const uint8_t *quants = p.weights[0] + row * stride + begin * 512 + lane * 16;
+    const uint8_t *scales = p.weights[0] + row * stride + p.width + begin * 32 + lane * 16;
+    RowRegs<G> cur;
+    if (row < p.total_rows) slice_issue<G>(cur, quants, scales, lane, count);
+
+    // the weight requests above do not depend on the previous kernel; everything below does
+    grid_dependency_wait();
+    stage_activation<ACT>(p.activation, p.width, p.blocks, gemv_smem, threadIdx.x, kGemvThreads);
     __syncthreads();
+    const int4 *act_lane = reinterpret_cast<const int4 *>(gemv_smem) + begin * 32 + lane;
+    const float *scale_lane =
+        reinterpret_cast<const float *>(gemv_smem + p.width) + begin * 16 + (lane >> 1);
 
-    // ---------------- producer: one thread drives the copy engine --------------
-    // It first arms every stage once (no waits are needed for the first lap), so
-    // weight tiles are in flight while the whole CTA stages the activation; only
-    // after the CTA-wide barrier does it enter the steady state, where each refill
-    // waits for the consumers to release the stage.
-    const bool producer = warp == kRingConsumerWarps && lane == 0;
-    int issued = 0;
-    int next_tile = blockIdx.x;
-    auto issue = [&](int tile, int s) {
-        const int first_row = tile * cfg.rows_per_tile;
-        const int rows = min(cfg.rows_per_tile, p.total_rows - first_row);
-        const uint32_t bytes = static_cast<uint32_t>(rows * stride);
-        uint8_t *dst = stages + static_cast<size_t>(s) * cfg.stage_bytes;
-        mbar_arrive_expect_tx(&full[s], bytes * copies);
-        bulk_copy_g2s(dst, p.weights[0] + first_row * stride, bytes, &full[s]);
-        if (copies == 2)
-            bulk_copy_g2s(dst + cfg.rows_per_tile * stride, p.weights[1] + first_row * stride,
-                bytes, &full[s]);
-    };
-    if (producer) {
-        for (; next_tile < cfg.tiles && issued < cfg.stages; next_tile += gridDim.x, ++issued)
-            issue(next_tile, issued);
-    }
-
-    stage_activation<ACT>(p.activation, p.width, p.blocks, ring_smem, threadIdx.x, kRingThreads);
-    __syncthreads();
-
-    if (producer) {
-        bool gave_up = false;
-        for (; next_tile < cfg.tiles; next_tile += gridDim.x, ++issued) {
-            const int s = issued % cfg.stages;
-            const int use = issued / cfg.stages;
-            if (!mbar_wait_bounded(&empty[s], (use - 1) & 1)) {
-                atomicExch(p.status, kStatusRingProducerTimeout);
-                atomicExch(&abort_flag, 1);
-                gave_up = true;
-                break;
-            }
-            if (*reinterpret_cast<volatile int *>(&abort_flag)) {
-                gave_up = true;
-                break;
-            }
-            issue(next_tile, s);
+    int round = 0;
+    while (row < p.total_rows) {
+        float acc = slice_consume<G>(cur, act_lane, scale_lane, slot, lane, count);
+        const int finished = row;
+        row += row_step;
+        quants += step;
+        scales += step;
+        if (row < p.total_rows) slice_issue<G>(cur, quants, scales, lane, count);
+        acc = warp_sum(acc);
+        if (lane == 0) partial[round & 1][warp] = acc;
+        // the SPLIT warps of this row meet; two slots by round parity make one barrier enough
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "r"(SPLIT * 32) : "memory");
+        if (slice == 0 && lane == 0) {
+            float total = partial[round & 1][warp];
+#pragma unroll
+            for (int s = 1; s < SPLIT; ++s) total += partial[round & 1][warp + s];
+            p.outputs[0][finished] = p.residual ? total + p.residual[finished] : total;
         }
-        if (gave_up) {
-            // Let copies that are still in flight land before the CTA's shared
-            // memory is released: wait (bounded) on the full barrier of every
-            // stage that was armed in the last lap.
-            const int lap = issued < cfg.stages ? issued : cfg.stages;
-            for (int k = 0; k < lap; ++k) {
-                const int n = issued - 1 - k;
-                mbar_wait_bounded(&full[n % cfg.stages], (n / cfg.stages) & 1, 1u << 16);
-            }
-        }
+        ++round;
     }
-
-    if (warp < kRingConsumerWarps) {
-        const int4 *act_q = reinterpret_cast<const int4 *>(ring_smem);
-        const float *act_s = reinterpret_cast<const float *>(ring_smem + p.width);
-        const int nchunks = p.width >> 4;
-        int consumed = 0;
-        for (int tile = blockIdx.x; tile < cfg.tiles; tile += gridDim.x, ++consumed) {
-            const int s = consumed % cfg.stages;
-            const int use = consumed / cfg.stages;
-            bool ready = true;
-            if (lane == 0) {
-                ready = mbar_wait_bounded(&full[s], use & 1);
-                if (!ready) {
-                    atomicExch(p.status, kStatusRingConsumerTimeout);
-                    atomicExch(&abort_flag, 1);
-                }
-            }
-            ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
-            if (!ready || *reinterpret_cast<volatile int *>(&abort_flag)) break;
-            // lane 0 observed the phase; the others re-check once, which returns
-            // at once and gives each lane its own acquire of the copied bytes
-            mbar_wait_bounded(&full[s], use & 1, 1u << 10);
-            const uint8_t *tile_base = stages + static_cast<size_t>(s) * cfg.stage_bytes;
-            const int first_row = tile * cfg.rows_per_tile;
-            const int rows = min(cfg.rows_per_tile, p.total_rows - first_row);
-            for (int r = warp; r < rows; r += kRingConsumerWarps) {
-                const float a0 = warp_sum(row_dot_shared(tile_base + r * stride, act_q, act_s,
-                    p.width, nchunks, lane));
-                if (EPI == kEpiSiluPair) {
-                    const float a1 = warp_sum(row_dot_shared(
-                        tile_base + (cfg.rows_per_tile + r) * stride, act_q, act_s, p.width,
-                        nchunks, lane));
-                    if (lane == 0) p.outputs[0][first_row + r] = silu_mul(a0, a1);
-                } else if (EPI == kEpiPeers) {
-                    if (lane == 0)
-                        for (int peer = 0; peer < p.peers; ++peer)
-                            p.peer_outputs[peer][p.first_row + first_row + r] = a0;
-                } else {
-                    if (lane == 0) p.outputs[0][first_row + r] = a0;
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-        }
-    }
+    grid_dependents_may_launch();
 }
 
 // `count` 16-byte pieces from page-locked host memory (through its device alias) into

@@ -198,10 +198,13 @@ uint64_t fortai_cuda_q8_context_launch_count(const fortai_cuda_q8_context *conte
 /* Blocks until the stream is idle, then reports any device-side wait that gave
  * up (bounded mbarrier waits in the staged kernels) as RUNTIME_ERROR. */
 int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context);
-/* Tuning knobs, by name: "gemv_variant" (0 = automatic, 1 = half-block-per-lane
- * kernel with 16-byte loads, 2 = bulk-copy ring, 3 = block-per-lane kernel with
- * 32-byte loads, 4 = register-pipelined kernel where the shape allows it), "gemv_ctas_per_sm",
- * "gemv_rows_per_warp", "ring_stages", "ring_rows", "mmq_min_tokens" (first token count that
+/* Tuning knobs, by name: "gemv_variant" (0 = automatic: slice kernel for few long rows,
+ * register-pipelined kernel where the width is one of its granule counts, else the
+ * half-block-per-lane kernel; 1 = always the half-block-per-lane kernel), "gemv_split" (warps
+ * that share a row in the slice kernel: 0 = automatic, 1 = never, 4, 8), "gemv_ctas_per_sm",
+ * "gemv_depth", "gemv_balance", "host_flush_rows" and "peer_flush_rows" (rows per store group
+ * of a GEMV that writes a page-locked host vector / peers' vectors: a power of two up to 32),
+ * "gemv_rows_per_warp", "mmq_min_tokens" (first token count that
  * goes to the tcgen05 prefill kernel, default 33), "prefill_kind" (0 = kind::f16 MMAs with the
  * activation scale folded into the operand, the default; 1 = kind::i8 MMAs scaled per block on
  * the CUDA cores, the kernel that also serves the block-dot probe), "peer_wait_clocks_millions".

@@ -9,7 +9,7 @@ from conftest import ROOT, golden, l2_tolerance, reference_gate
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = [0, 1, 2, 3]   # 0 = automatic (register-pipelined where the shape allows), 1 = half-block per lane, 2 = bulk-copy ring, 3 = block per lane
+VARIANTS = [0, 1]   # 0 = automatic choice (slice / register-pipelined / half-block), 1 = always half-block per lane
 
 
 def check_vector(actual, expected):
@@ -110,6 +110,36 @@ def test_decode_projection_sweep(backend, context, dev, oracle, rows, width, var
     assert backend.cuda_q8_block_dots_device(context, w, dact, ddots, rows * (width // 32)).is_ok()
     assert np.array_equal(dev.int32s(ddots, rows * (width // 32)).reshape(rows, -1),
                           oracle.block_dots(weights, quantized, rows, width // 32))
+
+
+# --------------------------------------------------------------------------- few long rows
+@pytest.mark.parametrize("split", [0, 4, 8])
+@pytest.mark.parametrize("rows,width", [(5, 8192), (130, 9728), (64, 17408), (9, 2048), (257, 4608),
+                                        (33, 18432)])
+def test_slice_kernel_on_long_rows(backend, context, dev, oracle, rows, width, split):
+    """K-slices of a row on 4 or 8 warps: granule counts that the warps share evenly (16, 36),
+    unevenly (19, 34, 9) and barely (4), from Q8_0 and from fp32 activations, against the
+    oracle and against the half-block kernel (same block arithmetic, other summation order)."""
+    context.set_option("gemv_split", split)
+    weights = oracle.make_weights(rows, width, seed=rows + width)
+    x = oracle.normal(width, seed=2)
+    expected, quantized, _ = oracle.matvec(weights, rows, width, x)
+    w = dev.weights(weights, rows, width)
+    out = np.zeros(rows, np.float32)
+    _, stat = backend.cuda_q8_matvec_host(context, w, quantized, quantized.size, out, out.nbytes)
+    assert stat.is_ok(), stat
+    check_vector(out, expected)
+    dx = dev.to_device(x)
+    dout = dev.buffer(4 * rows)
+    assert backend.cuda_q8_matvec_device_f32(context, w, dx, width, dout, rows).is_ok()
+    sliced = dev.floats(dout, rows)
+    assert np.array_equal(sliced, out)           # Q8_0 input and fp32 input: same arithmetic
+    again = dev.buffer(4 * rows)
+    assert backend.cuda_q8_matvec_device_f32(context, w, dx, width, again, rows).is_ok()
+    assert np.array_equal(dev.floats(again, rows), sliced)   # fixed summation order
+    context.set_option("gemv_variant", 1)
+    assert backend.cuda_q8_matvec_device_f32(context, w, dx, width, again, rows).is_ok()
+    check_vector(dev.floats(again, rows), sliced)
 
 
 def test_config0_against_golden(backend, context, dev, oracle):
