@@ -924,6 +924,32 @@ def run_ffn(args):
     steps = max(10, min(args.steps, 5000))
     with_collective = timed(lambda: ffn.forward(dist, x, out), steps)
     without = timed(local_only, steps)
+    # the same with the partial vectors exchanged by the down GEMV itself (no collective call)
+    fused_ms, fused_out, keep = None, None, []
+    if world > 1:
+        try:
+            import torch.distributed._symmetric_memory as symm
+            device = torch.device("cuda", local_rank)
+            slots = symm.empty(2 * world * hidden, dtype=torch.float32, device=device)
+            slots.zero_()
+            slot_handle = symm.rendezvous(slots, dist.group.WORLD)
+            flags = symm.empty(world, dtype=torch.int32, device=device)
+            flags.zero_()
+            flag_handle = symm.rendezvous(flags, dist.group.WORLD)
+            keep += [slots, slot_handle, flags, flag_handle]
+            torch.cuda.synchronize()
+            dist.barrier()
+            ffn.attach([int(p) for p in slot_handle.buffer_ptrs],
+                       [int(p) for p in flag_handle.buffer_ptrs])
+            fused_out = torch.empty(hidden, device="cuda", dtype=torch.float32)
+            fused_ms = timed(lambda: ffn.forward_fused(x, fused_out), steps)
+            stat = ctx.synchronize()
+            if not stat.is_ok():
+                raise RuntimeError(f"fused FFN: {stat}")
+        except Exception as error:
+            if rank == 0:
+                print(f"fused FFN exchange unavailable: {error}", file=sys.stderr)
+            fused_ms = None
     # batch 8: eight activations per call through the few-token kernels
     batch = 8
     xb = torch.randn(batch, hidden, generator=gen, device="cuda", dtype=torch.float32)
@@ -936,6 +962,8 @@ def run_ffn(args):
     verified = {}
     ffn.forward(dist, x, out)
     ffn.forward_batch(dist, xb, outb)
+    if fused_ms is not None:
+        ffn.forward_fused(x, fused_out)
     torch.cuda.synchronize()
     if rank == 0:
         full = [backend.cuda_q8_weights_t() for _ in range(3)]
@@ -956,6 +984,8 @@ def run_ffn(args):
             return bool(float((a.double() - b.double()).abs().max()) <= bound)
         verified["batch1"] = close(out, ref1)
         verified["batch8"] = all(close(outb[t], refb[t]) for t in range(batch))
+        if fused_ms is not None:
+            verified["batch1_fused"] = close(fused_out, ref1)
         for handle in full:
             handle.destroy()
     if rank == 0:
@@ -963,6 +993,7 @@ def run_ffn(args):
         print(json.dumps({"metric": "q8_0_ffn_weight_bandwidth", "unit": "GB/s", "n_gpus": world,
                           "value": nbytes / with_collective / 1e6,
                           "ms_per_step": with_collective, "ms_per_step_without_all_reduce": without,
+                          "ms_per_step_fused_exchange": fused_ms,
                           "batch8_ms_per_step": batch_ms,
                           "batch8_value": nbytes / batch_ms / 1e6,
                           "verified": verified,

@@ -696,6 +696,29 @@ def cuda_q8_matvec_device_f32_allgather(context, weights, device_activation, act
     return stat
 
 
+def cuda_q8_ffn_device_allreduce(context, gate, up, down, device_activation, activation_elements,
+                                 peer_slots, peer_flags, my_rank, device_output,
+                                 output_elements) -> status_t:
+    """Sharded FFN with the sum over ranks inside the call: the down GEMV stores this rank's
+    partial vector into every rank's slot array, exchanges flags, and the slots are added in
+    rank order.  peer_slots[p]: 2 * world * hidden floats in rank p's memory."""
+    stat = status_t()
+    if (not context.handle or not gate.handle or not up.handle or not down.handle or
+            not device_activation or not device_output or not peer_slots or
+            len(peer_slots) != len(peer_flags)):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 all-reduce FFN")
+        return stat
+    slots = (c_void_p * len(peer_slots))(*[c_void_p(p) for p in peer_slots])
+    flags = (c_void_p * len(peer_flags))(*[c_void_p(p) for p in peer_flags])
+    code = _lib().fortai_cuda_q8_ffn_device_allreduce(
+        context.handle, gate.handle, up.handle, down.handle, device_activation,
+        int(activation_elements), slots, flags, len(peer_slots), int(my_rank), device_output,
+        int(output_elements))
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 all-reduce FFN failed")
+    return stat
+
+
 # --------------------------------------------------------------------------- layer objects
 class cuda_qwen35_recurrent_t:
     """fortai_backend_cuda.f90:35-43 (gated-delta-net layer; state lives on the device)."""

@@ -42,7 +42,9 @@ struct fortai_cuda_q8_context {
     int planar_min_width = 6144;             // vectors at least this long are prepared once
     int *position = nullptr;
     unsigned *cta_counter = nullptr;         // device word used by the fused all-gather tail
-    unsigned allgather_sequence = 0;
+    unsigned allgather_sequence = 0;   // fused all-gather launches so far (wraps)
+    unsigned host_sequence = 0;        // host-call completions so far (wraps)
+    unsigned ffn_exchange_calls = 0;   // all-reduce FFN calls so far (slot parity)
     int *status_host = nullptr;              // pinned + mapped: kernels write, host reads
     int *status_device = nullptr;
     unsigned *done_host = nullptr;           // pinned + mapped: completion word of host calls
@@ -53,6 +55,7 @@ struct fortai_cuda_q8_context {
     // options
     int host_flush_rows = 8;   // rows per store group into a page-locked host output
     int peer_flush_rows = 32;  // rows per store group into peers' vectors
+    int peer_publish_per_cta = 0;   // fused exchanges: 0 = the last CTA raises a flag, 1 = per-CTA adds (capturable)
     int gemv_variant = 0;      // 0 = automatic choice, 1 = always the half-block kernel
     int gemv_ctas_per_sm = 0;  // 0 = occupancy-derived
     int gemv_rows_per_warp = 0;
@@ -203,7 +206,7 @@ cudaError_t launch_gemv_kernel(fortai_cuda_q8_context *c, Kernel kernel, int gri
     overlap.val.programmaticStreamSerializationAllowed = 1;
     config.attrs = &overlap;
     // (p.overlap_ok: a "peer" launch whose only peer is this process's own host memory)
-    config.numAttrs = c->gemv_overlap && ((p.peers == 0 && p.sequence == 0) || p.overlap_ok) ? 1 : 0;
+    config.numAttrs = c->gemv_overlap && ((p.peers == 0 && p.exchange == kExchangeOff) || p.overlap_ok) ? 1 : 0;
     const cudaError_t error = cudaLaunchKernelEx(&config, kernel, p);
     ++c->launches;
     return error != cudaSuccess ? error : cudaGetLastError();
@@ -376,9 +379,9 @@ bool launch_pipelined(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_
     }
 }
 
-template <int G, int SPLIT, int ACT>
+template <int G, int SPLIT, int ACT, int EPI>
 cudaError_t launch_slice_instance(fortai_cuda_q8_context *c, const GemvParams &p) {
-    auto kernel = q8_gemv_slice_kernel<G, SPLIT, ACT>;
+    auto kernel = q8_gemv_slice_kernel<G, SPLIT, ACT, EPI>;
     const size_t smem = slice_smem_bytes(p.width, p.blocks, G);
     cudaError_t error = cudaSuccess;
     if (smem > 48 * 1024) {
@@ -414,10 +417,10 @@ cudaError_t launch_slice_instance(fortai_cuda_q8_context *c, const GemvParams &p
 // Few long rows: K-slices of a row on 4 or 8 warps.  Chosen by itself for plain single-matrix
 // products of at least 16 granules (8192 elements) whose rows are fewer than two rounds of a
 // warp-per-row grid; "gemv_split" = 1 turns it off, 4 or 8 force it where the shape allows.
-template <int ACT>
+template <int ACT, int EPI>
 bool launch_slice(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *error) {
     if (p.segments != 1 || p.norm_weights || p.conv_weights || p.width % 512 != 0 ||
-        c->gemv_split == 1)
+        c->gemv_split == 1 || (EPI == kEpiPeers && p.residual))
         return false;
     const int granules = p.width / 512;
     int split = c->gemv_split;
@@ -428,13 +431,13 @@ bool launch_slice(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *e
     const int most = (granules + split - 1) / split;
     if (most > 9 || granules < split) return false;
     if (split == 4) {
-        if (most <= 3) *error = launch_slice_instance<3, 4, ACT>(c, p);
-        else if (most <= 5) *error = launch_slice_instance<5, 4, ACT>(c, p);
-        else *error = launch_slice_instance<9, 4, ACT>(c, p);
+        if (most <= 3) *error = launch_slice_instance<3, 4, ACT, EPI>(c, p);
+        else if (most <= 5) *error = launch_slice_instance<5, 4, ACT, EPI>(c, p);
+        else *error = launch_slice_instance<9, 4, ACT, EPI>(c, p);
     } else if (split == 8) {
-        if (most <= 3) *error = launch_slice_instance<3, 8, ACT>(c, p);
-        else if (most <= 5) *error = launch_slice_instance<5, 8, ACT>(c, p);
-        else *error = launch_slice_instance<9, 8, ACT>(c, p);
+        if (most <= 3) *error = launch_slice_instance<3, 8, ACT, EPI>(c, p);
+        else if (most <= 5) *error = launch_slice_instance<5, 8, ACT, EPI>(c, p);
+        else *error = launch_slice_instance<9, 8, ACT, EPI>(c, p);
     } else {
         return false;
     }
@@ -452,7 +455,8 @@ cudaError_t launch_gemv_act(fortai_cuda_q8_context *c, const GemvParams &p, int 
     if (c->gemv_variant == 0) {
         cudaError_t error = cudaSuccess;
         bool done = false;
-        if (epi == kEpiPlain && launch_slice<ACT>(c, p, &error)) return error;
+        if (epi == kEpiPlain && launch_slice<ACT, kEpiPlain>(c, p, &error)) return error;
+        if (epi == kEpiPeers && launch_slice<ACT, kEpiPeers>(c, p, &error)) return error;
         if (epi == kEpiPlain && p.segments > 1)
             done = launch_pipelined<ACT, kEpiStacked>(c, p, &error);
         if (!done && epi == kEpiPlain) done = launch_pipelined<ACT, kEpiPlain>(c, p, &error);
@@ -748,9 +752,38 @@ struct Glue {
     const float *residual = nullptr;
 };
 
+// A column-sharded down projection whose ranks exchange their partial output vectors inside
+// the GEMV: rank r's partial goes to slot r of every rank's slot array, then the flag
+// exchange of the fused all-gather.
+struct FfnExchange {
+    float *slots[kMaxPeers] = {};      // every rank's slot array (peers x hidden floats)
+    unsigned *flags[kMaxPeers] = {};
+    int peers = 0;
+    int rank = 0;
+};
+
+void attach_exchange(fortai_cuda_q8_context *c, GemvParams *d, const FfnExchange &x, int hidden) {
+    for (int i = 0; i < x.peers; ++i) {
+        d->peer_outputs[i] = x.slots[i];
+        d->peer_flags[i] = x.flags[i];
+    }
+    d->outputs[0] = nullptr;
+    d->peers = x.peers;
+    d->peer_flush = c->peer_flush_rows;
+    d->first_row = x.rank * hidden;
+    d->my_flags = x.flags[x.rank];
+    d->cta_counter = c->cta_counter;
+    d->my_rank = x.rank;
+    d->sequence = ++c->allgather_sequence;
+    d->exchange = c->peer_publish_per_cta ? kExchangeCounters : kExchangeLastCta;
+    d->flag_wait_clocks = static_cast<long long>(c->peer_wait_clocks_millions) * 1000000LL;
+    d->overlap_ok = c->peer_overlap;
+}
+
 cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *gate,
     const fortai_cuda_q8_weights *up, const fortai_cuda_q8_weights *down, const void *activation,
-    int act, float *output, const Glue &glue = Glue()) {
+    int act, float *output, const Glue &glue = Glue(), const FfnExchange *exchange = nullptr) {
+    const int down_epi = exchange ? kEpiPeers : kEpiPlain;
     GemvParams p = single_params(c, gate, activation, c->scratch_output);
     p.weights[1] = up->data;
     p.rows[1] = up->rows;
@@ -776,7 +809,8 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
         if (error == cudaSuccess) {
             GemvParams d = single_params(c, down, c->scratch_planar, output);
             d.residual = glue.residual;
-            error = launch_gemv_raw(c, d, kActPlanar, kEpiPlain);
+            if (exchange) attach_exchange(c, &d, *exchange, down->rows);
+            error = launch_gemv_raw(c, d, kActPlanar, down_epi);
         }
         return error;
     }
@@ -786,14 +820,16 @@ cudaError_t enqueue_ffn(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights 
         // costs more than the separate kernel)
         GemvParams d = single_params(c, down, c->scratch_output, output);
         d.residual = glue.residual;
-        return launch_gemv_raw(c, d, kActF32, kEpiPlain);
+        if (exchange) attach_exchange(c, &d, *exchange, down->rows);
+        return launch_gemv_raw(c, d, kActF32, down_epi);
     }
     error = launch_quantize(c, c->scratch_output, c->scratch_activation,
         static_cast<size_t>(down->blocks));
     if (error == cudaSuccess) {
         GemvParams d = single_params(c, down, c->scratch_activation, output);
         d.residual = glue.residual;
-        error = launch_gemv(c, d, kActQ8, kEpiPlain);
+        if (exchange) attach_exchange(c, &d, *exchange, down->rows);
+        error = launch_gemv(c, d, kActQ8, down_epi);
     }
     return error;
 }
@@ -1191,6 +1227,55 @@ extern "C" int fortai_cuda_q8_ffn_device(fortai_cuda_q8_context *context,
         error = enqueue_ffn(context, gate_weights, up_weights, down_weights, device_activation,
             kActF32, static_cast<float *>(device_output));
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "Qwen FFN device", error);
+}
+
+extern "C" int fortai_cuda_q8_ffn_device_allreduce(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_slots, void *const *peer_flags, int peer_count,
+    int my_rank, void *device_output, size_t output_elements) {
+    if (!context || !gate_weights || !up_weights || !down_weights || !device_activation ||
+        !device_output || !peer_slots || !peer_flags || peer_count <= 0 ||
+        peer_count > kMaxPeers || my_rank < 0 || my_rank >= peer_count)
+        return FORTAI_CUDA_INVALID;
+    if (!ffn_shapes_ok(context, gate_weights, up_weights, down_weights) ||
+        activation_elements != static_cast<size_t>(gate_weights->blocks) * kBlockElems ||
+        output_elements < static_cast<size_t>(down_weights->rows)) return FORTAI_CUDA_INVALID;
+    for (int i = 0; i < peer_count; ++i)
+        if (!peer_slots[i] || !peer_flags[i]) return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(context->stream, &capture) == cudaSuccess &&
+        capture != cudaStreamCaptureStatusNone) {
+        // (the slot parity below is a host counter, whichever flag protocol is in use)
+        fail(context, "all-reduce FFN cannot be captured into a CUDA graph "
+                      "(its slot parity is a launch argument)");
+        return FORTAI_CUDA_INVALID;
+    }
+    const int hidden = down_weights->rows;
+    // two sets of slots, used alternately: a rank that runs ahead stores call n+1's partial
+    // while a peer may still be summing call n's; it cannot reach call n+2 before that peer
+    // has raised its flag for call n+1, which comes after its sum of call n in stream order
+    const size_t parity_offset = static_cast<size_t>(context->ffn_exchange_calls++ & 1u) *
+        peer_count * hidden;
+    FfnExchange exchange;
+    for (int i = 0; i < peer_count; ++i) {
+        exchange.slots[i] = static_cast<float *>(peer_slots[i]) + parity_offset;
+        exchange.flags[i] = static_cast<unsigned *>(peer_flags[i]);
+    }
+    exchange.peers = peer_count;
+    exchange.rank = my_rank;
+    cudaError_t error = ensure_scratch(context,
+        static_cast<size_t>(down_weights->blocks) * kBlockBytes,
+        static_cast<size_t>(gate_weights->rows) * sizeof(float));
+    if (error == cudaSuccess)
+        error = enqueue_ffn(context, gate_weights, up_weights, down_weights, device_activation,
+            kActF32, nullptr, Glue(), &exchange);
+    if (error == cudaSuccess)
+        error = launch_overlapped(context, q8_sum_slots_kernel, (hidden + 255) / 256, 256, 0,
+            static_cast<const float *>(exchange.slots[my_rank]), peer_count, hidden,
+            static_cast<const float *>(nullptr), static_cast<float *>(device_output));
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-reduce FFN", error);
 }
 
 // ---------------------------------------------------------------------------
@@ -1627,6 +1712,8 @@ extern "C" int fortai_cuda_q8_context_set_option(fortai_cuda_q8_context *context
     else if (!std::strcmp(name, "host_flush_rows") && value >= 1 && value <= 32 &&
              (value & (value - 1)) == 0)
         context->host_flush_rows = static_cast<int>(value);
+    else if (!std::strcmp(name, "peer_publish_per_cta") && value <= 1)
+        context->peer_publish_per_cta = value;
     else if (!std::strcmp(name, "peer_flush_rows") && value >= 1 && value <= 32 &&
              (value & (value - 1)) == 0)
         context->peer_flush_rows = static_cast<int>(value);
@@ -1723,10 +1810,13 @@ extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
         ? mapped_host_pointer(host_activation) : nullptr;
     if (error == cudaSuccess && mapped_input) {
         const auto begin = std::chrono::steady_clock::now();
-        q8_fetch_kernel<<<1, 256, 0, context->stream>>>(
-            reinterpret_cast<const float4 *>(mapped_input),
-            reinterpret_cast<float4 *>(context->scratch_activation),
-            static_cast<int>(in_bytes / 16));
+        // one 16-byte request per thread, all in flight at once: the transfer then costs one
+        // round trip over the link (three in a row took about 8 us for 10 KB)
+        const int pieces = static_cast<int>(in_bytes / 16);
+        const int fetch_threads = std::min(1024, (pieces + 31) / 32 * 32);
+        q8_fetch_kernel<<<(pieces + fetch_threads - 1) / fetch_threads, fetch_threads, 0,
+            context->stream>>>(reinterpret_cast<const float4 *>(mapped_input),
+            reinterpret_cast<float4 *>(context->scratch_activation), pieces);
         ++context->launches;
         error = cudaGetLastError();
         unsigned sequence = 0;
@@ -1742,8 +1832,8 @@ extern "C" int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
             p.my_flags = context->done_device;
             p.cta_counter = context->cta_counter;
             p.my_rank = 0;
-            if (++context->allgather_sequence == 0) ++context->allgather_sequence;
-            sequence = p.sequence = context->allgather_sequence;
+            sequence = p.sequence = ++context->host_sequence;
+            p.exchange = kExchangeLastCta;   // a host word: plain stores only
             p.flag_wait_clocks = static_cast<long long>(context->peer_wait_clocks_millions) *
                 1000000LL;
             p.overlap_ok = 1;
@@ -1827,14 +1917,16 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
     for (int i = 0; i < peer_count; ++i)
         if (!peer_outputs[i] || !peer_flags[i]) return FORTAI_CUDA_INVALID;
     cudaSetDevice(context->device);
-    // The sequence number is a kernel argument taken from a host counter: a captured launch
-    // would replay the same number, and from the second replay on the tail would find the
-    // peers' flags "already raised" and return without waiting.  Refuse capture.
+    // With the last-CTA protocol the call's number is a kernel argument taken from a host
+    // counter: a captured launch would replay the same number, and from the second replay on
+    // the tail would find the peers' flags "already raised" and return without waiting.
+    // Refuse capture there.  (The per-CTA protocol takes the number from the flag words.)
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-    if (cudaStreamIsCapturing(context->stream, &capture) == cudaSuccess &&
+    if (!context->peer_publish_per_cta &&
+        cudaStreamIsCapturing(context->stream, &capture) == cudaSuccess &&
         capture != cudaStreamCaptureStatusNone) {
-        fail(context, "all-gather matvec cannot be captured into a CUDA graph "
-                      "(its flag sequence number is a launch argument)");
+        fail(context, "all-gather matvec with peer_publish_per_cta = 0 cannot be captured into "
+                      "a CUDA graph (its flag sequence number is a launch argument)");
         return FORTAI_CUDA_INVALID;
     }
     GemvParams p = single_params(context, weights, device_activation, nullptr);
@@ -1848,8 +1940,8 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
     p.my_flags = static_cast<unsigned *>(peer_flags[my_rank]);
     p.cta_counter = context->cta_counter;
     p.my_rank = my_rank;
-    if (++context->allgather_sequence == 0) ++context->allgather_sequence;   // 0 means "off"
-    p.sequence = context->allgather_sequence;
+    p.sequence = ++context->allgather_sequence;
+    p.exchange = context->peer_publish_per_cta ? kExchangeCounters : kExchangeLastCta;
     p.flag_wait_clocks = static_cast<long long>(context->peer_wait_clocks_millions) * 1000000LL;
     // A following call of this kind may be launched while this one still waits for its peers'
     // flags: the kernel touches neither the peers' vectors nor the shared CTA counter before

@@ -313,7 +313,7 @@ extern "C" int fortai_cuda_q8_group_matvec_f32(fortai_cuda_q8_group *group,
     }
     // every rank of one call must carry the same flag sequence number, whatever else its
     // context has been used for
-    if (++group->sequence == 0) ++group->sequence;
+    ++group->sequence;
     for (int k = 0; k < owner_count; ++k) {
         const int g = owners[k];
         group->contexts[g]->allgather_sequence = group->sequence - 1;

@@ -48,6 +48,8 @@ enum ActivationKind : int {
     kActPlanar = 2   // the shared-memory image itself, prepared once in global memory
 };
 
+enum PeerExchange : int { kExchangeOff = 0, kExchangeLastCta = 1, kExchangeCounters = 2 };
+
 struct GemvParams {
     const uint8_t *weights[kMaxSegments];
     float *outputs[kMaxSegments];
@@ -72,11 +74,12 @@ struct GemvParams {
     float *peer_outputs[kMaxPeers];
     int peers;
     int first_row;  // element offset of this shard inside the peers' vectors
-    // fused all-gather (sequence != 0): flag words in every rank's memory
-    unsigned *peer_flags[kMaxPeers];   // peer_flags[p][my_rank] is written with `sequence`
+    // fused all-gather (exchange != kExchangeOff): flag words in every rank's memory
+    unsigned *peer_flags[kMaxPeers];   // peer_flags[p][my_rank] belongs to this rank
     unsigned *my_flags;                // this rank's own flag array, one word per peer
     unsigned *cta_counter;             // device word, zero between launches
-    unsigned sequence;
+    unsigned sequence;                 // this launch's number among the rank's exchanging launches
+    int exchange;                      // kExchangeOff, kExchangeLastCta or kExchangeCounters
     int my_rank;
     long long flag_wait_clocks;        // how long the tail waits for a peer's flag (SM clocks)
     int overlap_ok;                    // the only "peer" is this process: dependent launch allowed
@@ -119,43 +122,87 @@ __device__ __forceinline__ float conv_silu_channel(const float *__restrict__ con
 
 // Tail of a peer-output GEMV: turns "every rank stored its slice everywhere" into "this
 // launch is complete only when every rank's slice has arrived here", without a second
-// kernel.  Every CTA publishes its stores system-wide and counts itself; in the last one,
-// one lane per peer raises this rank's flag in that peer's memory and then waits, for at
-// most about one second, until that peer has raised its flag here.  A wait that runs out writes a
-// status word and returns; the kernel never spins without a bound.  All ranks must run
-// on different GPUs (they wait on one another).
+// kernel.  Two protocols (GemvParams::exchange), both on one 32-bit word per (receiver,
+// sender) pair that starts at zero, and both bounded: a wait that runs out writes a status
+// word and returns.  All ranks must run on different GPUs (they wait on one another).
+//   kExchangeCounters  every CTA, once its stores are issued, adds its share of 2^20 to this
+//       rank's word in every peer's memory (a system-wide fence orders the CTA's stores
+//       before the adds; nothing comes back).  A launch adds exactly 2^20 per sender,
+//       whatever its grid, so the n-th launch on a set of words is complete at a receiver
+//       when the word has reached n * 2^20 (modulo 2^32); n comes from the rank's own word,
+//       not from the host, so a launch can be replayed from a CUDA graph.  CTA 0 waits, one
+//       lane per peer.  After the last row the critical path is one release and one trip
+//       over the link.
+//   kExchangeLastCta   every CTA publishes its stores system-wide and counts itself in a
+//       device word; the last one writes the call's sequence number to the peers and waits
+//       for theirs.  Needs no remote atomic: used when the "peer" is page-locked host memory.
+constexpr unsigned kExchangeUnitsLog2 = 20;
+
+__device__ __forceinline__ void peer_wait_word(const GemvParams &p, const unsigned *word,
+    unsigned target) {
+    const long long start = clock64();
+    for (;;) {
+        unsigned seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(word) : "memory");
+        // the words only grow; the signed difference survives wrap-around
+        if (static_cast<int>(seen - target) >= 0) break;
+        if (clock64() - start > p.flag_wait_clocks) {   // about a second of SM clocks by default
+            atomicExch(p.status, kStatusPeerFlagTimeout);
+            break;
+        }
+    }
+}
+
 __device__ __forceinline__ void peer_allgather_tail(const GemvParams &p) {
-    if (p.sequence == 0) return;
+    if (p.exchange == kExchangeOff) return;
+    if (p.exchange == kExchangeCounters) {
+        __syncthreads();                              // the whole CTA's stores are issued
+        if (threadIdx.x < 32) {
+            // one system-wide fence for the CTA (by lane 0, handed to the warp), then one
+            // relaxed add per peer: a release on every add would fence once per peer
+            if (threadIdx.x == 0) __threadfence_system();
+            __syncwarp();
+            if (threadIdx.x < p.peers) {
+                // CTA 0 derives the launch's target from this rank's own word BEFORE adding
+                // its share: all earlier launches of this rank have completed (stream order),
+                // so the word holds (launches so far) * 2^20 plus what other CTAs of this
+                // launch have added, which stays below 2^20 as long as this CTA's share is
+                // missing.
+                unsigned target = 0;
+                if (blockIdx.x == 0) {
+                    unsigned own;
+                    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];"
+                                 : "=r"(own) : "l"(p.my_flags + p.my_rank) : "memory");
+                    target = ((own >> kExchangeUnitsLog2) + 1u) << kExchangeUnitsLog2;
+                }
+                const unsigned long long units = 1ull << kExchangeUnitsLog2;
+                const unsigned share = static_cast<unsigned>(
+                    (blockIdx.x + 1ull) * units / gridDim.x - blockIdx.x * units / gridDim.x);
+                unsigned *remote = p.peer_flags[threadIdx.x] + p.my_rank;
+                asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(remote), "r"(share)
+                             : "memory");
+                if (blockIdx.x == 0) peer_wait_word(p, p.my_flags + threadIdx.x, target);
+            }
+        }
+        return;
+    }
     __shared__ int is_last_cta;
     __syncthreads();
     if (threadIdx.x == 0) {
         __threadfence_system();
         const unsigned arrived = atomicAdd(p.cta_counter, 1u);
         is_last_cta = arrived == gridDim.x - 1;
-        if (is_last_cta) {
-            *p.cta_counter = 0;                   // ready for the next launch
-            __threadfence_system();
-        }
     }
     __syncthreads();
-    if (!is_last_cta || threadIdx.x >= p.peers) return;
+    if (!is_last_cta) return;
     // one lane per peer: raise this rank's flag there, then wait for that peer's flag here
-    const int peer = threadIdx.x;
-    unsigned *remote = p.peer_flags[peer] + p.my_rank;
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.sequence) : "memory");
-    const unsigned *local = p.my_flags + peer;
-    const long long start = clock64();
-    const long long limit = p.flag_wait_clocks;   // about a second of SM clocks by default
-    for (;;) {
-        unsigned seen;
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(local) : "memory");
-        // sequence numbers only grow; the signed difference survives wrap-around
-        if (static_cast<int>(seen - p.sequence) >= 0) break;
-        if (clock64() - start > limit) {
-            atomicExch(p.status, kStatusPeerFlagTimeout);
-            break;
-        }
+    if (threadIdx.x < p.peers) {
+        unsigned *remote = p.peer_flags[threadIdx.x] + p.my_rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(p.sequence)
+                     : "memory");
     }
+    if (threadIdx.x == 0) *p.cta_counter = 0;         // ready for the next launch in the stream
+    if (threadIdx.x < p.peers) peer_wait_word(p, p.my_flags + threadIdx.x, p.sequence);
 }
 
 // Shared-memory image of the activation: `width` int8 quants, then `blocks`
@@ -643,7 +690,7 @@ __host__ __device__ inline size_t slice_smem_bytes(int width, int blocks, int gr
         static_cast<size_t>(kGemvWarps) * (2 * granules * 16);
 }
 
-template <int G, int SPLIT, int ACT>
+template <int G, int SPLIT, int ACT, int EPI>
 __global__ void __launch_bounds__(kGemvThreads)
 q8_gemv_slice_kernel(const __grid_constant__ GemvParams p) {
     if (p.trigger_early) grid_dependents_may_launch();
@@ -692,20 +739,43 @@ q8_gemv_slice_kernel(const __grid_constant__ GemvParams p) {
             float total = partial[round & 1][warp];
 #pragma unroll
             for (int s = 1; s < SPLIT; ++s) total += partial[round & 1][warp + s];
-            p.outputs[0][finished] = p.residual ? total + p.residual[finished] : total;
+            if (EPI == kEpiPeers) {
+                // few rows (a partial output vector): one word per row and peer
+                for (int peer = 0; peer < p.peers; ++peer)
+                    p.peer_outputs[peer][p.first_row + finished] = total;
+            } else {
+                p.outputs[0][finished] = p.residual ? total + p.residual[finished] : total;
+            }
         }
         ++round;
     }
     grid_dependents_may_launch();
+    if (EPI == kEpiPeers) peer_allgather_tail(p);
+}
+
+// out[i] = slots[0][i] + slots[1][i] + ... in slot order (+ residual[i]): the reduction of
+// the partial output vectors that a column-sharded projection's ranks stored into one
+// another's slot arrays, the same order on every rank.
+__global__ void __launch_bounds__(256)
+q8_sum_slots_kernel(const float *__restrict__ slots, int slot_count, int elements,
+    const float *__restrict__ residual, float *__restrict__ out) {
+    grid_dependents_may_launch();
+    grid_dependency_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= elements) return;
+    float total = slots[i];
+    for (int s = 1; s < slot_count; ++s) total += slots[static_cast<size_t>(s) * elements + i];
+    out[i] = residual ? total + residual[i] : total;
 }
 
 // `count` 16-byte pieces from page-locked host memory (through its device alias) into
 // device memory: the host-call path's replacement for a copy-engine transfer of a few
 // kilobytes.  Its dependent, the GEMV, may start at once.
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 q8_fetch_kernel(const float4 *__restrict__ source, float4 *__restrict__ destination, int count) {
     grid_dependents_may_launch();
-    for (int i = threadIdx.x; i < count; i += blockDim.x) destination[i] = source[i];
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count) destination[i] = source[i];
 }
 
 // --------------------------------------------------------------------------

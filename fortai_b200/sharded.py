@@ -202,6 +202,22 @@ class ShardedFfn:
             raise RuntimeError(f"sharded FFN failed: {stat}")
         return all_reduce_sum(dist, out, self.world)
 
+    def attach(self, peer_slot_ptrs: Sequence[int], peer_flag_ptrs: Sequence[int]):
+        """Slot arrays (2 * world * hidden floats per rank) and flag arrays (world words per
+        rank, zeroed once) that every rank can reach, for `forward_fused`."""
+        self.slot_ptrs = list(peer_slot_ptrs)
+        self.flag_ptrs = list(peer_flag_ptrs)
+
+    def forward_fused(self, activation: "torch.Tensor", out: "torch.Tensor"):
+        """The same result without a collective call: partial vectors are exchanged by the
+        down GEMV itself and added in rank order (the same bits on every rank)."""
+        stat = self.backend.cuda_q8_ffn_device_allreduce(
+            self.context, self.gate, self.up, self.down, activation.data_ptr(), self.hidden,
+            self.slot_ptrs, self.flag_ptrs, self.rank, out.data_ptr(), self.hidden)
+        if not stat.is_ok():
+            raise RuntimeError(f"fused sharded FFN failed: {stat}")
+        return out
+
     def forward_batch(self, dist, activations: "torch.Tensor", out: "torch.Tensor"):
         """`tokens` activations at once (tokens x hidden in, tokens x hidden out)."""
         tokens = int(activations.shape[0])

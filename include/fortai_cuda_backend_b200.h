@@ -321,23 +321,47 @@ int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *context,
     size_t output_elements);
 
 /* The same with the all-gather fused into the kernel: peer_flags[p] is rank p's flag array
- * (peer_count 32-bit words, zero-initialised once, e.g. in symmetric memory).  Each rank's
- * last CTA raises word [my_rank] in every rank's array with a per-context sequence number
- * and then waits - for about a second at most - until every word of its own array has
- * reached that number, so when the launch completes every rank's slice is in this rank's
- * output vector.  Every rank must make the same sequence of these calls, each on its own
- * GPU (the kernels wait on one another).  A wait that runs out is reported as
- * RUNTIME_ERROR by the next synchronizing call (option "peer_wait_clocks_millions" sets the
- * limit, default 2000).  The flags say that a slice has ARRIVED, not that it has been
- * CONSUMED: a rank that runs ahead stores call n+1's slice into a peer's vector while that
- * peer may still read call n's result.  Alternate two output vectors between consecutive
- * calls, or put a cross-rank barrier between reading the result and the next call.  The
- * call cannot be captured into a CUDA graph (the sequence number is a launch argument; a
- * replay would not wait): during capture it returns INVALID with a message.  Enqueue only. */
+ * (peer_count 32-bit words, zero-initialised once, e.g. in symmetric memory); word
+ * [my_rank] of every array belongs to this rank.  When the launch completes, every rank's
+ * slice is in this rank's output vector.  Two protocols, chosen by option
+ * "peer_publish_per_cta" (all ranks must use the same one, on flag arrays of its own):
+ *   0 (default)  every CTA publishes its stores and counts itself; the rank's last CTA
+ *     writes a per-context call number into its word in every rank's array and waits - for
+ *     about a second at most - until every word of its own array has reached that number.
+ *     The number is a launch argument, so the call cannot be captured into a CUDA graph (a
+ *     replay would not wait): during capture it returns INVALID with a message.
+ *   1  every CTA, once its rows are stored, adds its share of 2^20 to the rank's word in
+ *     every array, so a launch adds exactly 2^20 per sender, and one CTA waits until every
+ *     word of the rank's own array has reached (calls made on these arrays) * 2^20 modulo
+ *     2^32.  The count is read from the rank's own word: the call may be captured and
+ *     replayed.  Measured 2-3 us slower per call on two B200s than protocol 0.
+ * Every rank must make the same sequence of these calls, each on its own GPU (the kernels
+ * wait on one another).  A wait that runs out is reported as RUNTIME_ERROR by the next
+ * synchronizing call (option "peer_wait_clocks_millions" sets the limit, default 2000).
+ * The flags say that a slice has ARRIVED, not that it has been CONSUMED: a rank that runs
+ * ahead stores call n+1's slice into a peer's vector while that peer may still read call
+ * n's result.  Alternate two output vectors between consecutive calls, or put a cross-rank
+ * barrier between reading the result and the next call.  Enqueue only. */
 int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *weights, const void *device_activation,
     size_t activation_elements, void *const *peer_outputs, void *const *peer_flags,
     int peer_count, int my_rank, size_t first_row, size_t output_elements);
+
+/* The FFN of fortai_cuda_q8_ffn_device for ranks that hold gate/up row shards and the
+ * matching column shard of down, with the sum over ranks inside the call (no reference
+ * counterpart: the reference is single-GPU).  peer_slots[p] is rank p's slot array of
+ * 2 * peer_count * hidden floats, peer_flags[p] its flag array (peer_count words, zeroed
+ * once), both reachable from every rank (peer access or symmetric memory).  The down GEMV
+ * stores this rank's partial vector into slot my_rank of every rank's array (the two halves
+ * of the array alternate between consecutive calls), exchanges flags as the all-gather
+ * matvec does (same options, same bounded wait), and a small kernel then adds the slots in
+ * rank order into device_output: every rank gets the same bits.  Every rank must make the
+ * same sequence of these calls, each on its own GPU.  Not capturable.  Enqueue only. */
+int fortai_cuda_q8_ffn_device_allreduce(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
+    const fortai_cuda_q8_weights *down_weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_slots, void *const *peer_flags, int peer_count,
+    int my_rank, void *device_output, size_t output_elements);
 
 /* ----------------------------------------------------------------------- *
  * Device groups: the sharded path for hosts that drive several GPUs of one box from one

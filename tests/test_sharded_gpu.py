@@ -62,7 +62,18 @@ def test_fused_allgather_with_a_single_rank(backend, context, dev, oracle):
                                                            0, 0, rows)
         assert stat.is_ok(), stat
         assert context.synchronize().is_ok()
-        assert dev.int32s(flags, 1)[0] == call + 1
+        assert dev.int32s(flags, 1)[0] == call + 1      # the last CTA writes the call's number
+    assert float(np.abs(dev.floats(out, rows) - expected).max()) <= l2_tolerance(expected)
+    # the other protocol: every launch adds exactly 2^20 to the sender's word, whatever its grid
+    assert context.set_option("peer_publish_per_cta", 1).is_ok()
+    flags = dev.to_device(np.zeros(1, np.int32))
+    out = dev.to_device(np.zeros(rows, np.float32))
+    for call in range(3):
+        stat = backend.cuda_q8_matvec_device_f32_allgather(context, w, dx, width, [out], [flags],
+                                                           0, 0, rows)
+        assert stat.is_ok(), stat
+        assert context.synchronize().is_ok()
+        assert dev.int32s(flags, 1)[0] == (call + 1) << 20
     assert float(np.abs(dev.floats(out, rows) - expected).max()) <= l2_tolerance(expected)
 
 
@@ -87,7 +98,8 @@ def test_column_shards_sum_to_the_full_ffn(backend, context, dev, oracle):
     assert float(np.abs(total - expected).max()) <= 2 * l2_tolerance(expected)
 
 
-def test_fused_allgather_gives_up_when_a_peer_never_answers(backend, context, dev, oracle):
+@pytest.mark.parametrize("per_cta", [1, 0])
+def test_fused_allgather_gives_up_when_a_peer_never_answers(backend, context, dev, oracle, per_cta):
     """Failure detection without a fault: two "ranks" whose flag arrays are ordinary buffers
     on this GPU, the second rank's flag is never raised.  The wait runs out (a few
     milliseconds here), the kernel returns by itself, the next blocking call reports it, and
@@ -101,6 +113,7 @@ def test_fused_allgather_gives_up_when_a_peer_never_answers(backend, context, de
     outs = [dev.to_device(np.zeros(2 * rows, np.float32)) for _ in range(2)]
     flags = [dev.to_device(np.zeros(2, np.int32)) for _ in range(2)]
     assert context.set_option("peer_wait_clocks_millions", 5).is_ok()
+    assert context.set_option("peer_publish_per_cta", per_cta).is_ok()
     stat = backend.cuda_q8_matvec_device_f32_allgather(context, w, dx, width, outs, flags, 0, 0,
                                                        2 * rows)
     assert stat.is_ok(), stat               # enqueue only: the launch itself is fine
@@ -120,18 +133,41 @@ def test_fused_allgather_gives_up_when_a_peer_never_answers(backend, context, de
     assert float(np.abs(out - expected).max()) <= l2_tolerance(expected)
 
 
-def test_fused_allgather_refuses_graph_capture(backend, context, dev, oracle):
-    rows, width = 64, 256
-    w = dev.weights(oracle.make_weights(rows, width, seed=1), rows, width)
-    dx = dev.to_device(oracle.normal(width, seed=2))
+def test_fused_allgather_in_a_cuda_graph(backend, context, dev, oracle):
+    """The per-CTA protocol takes the call's number from the flag words, so a captured launch
+    can be replayed: every replay waits for its own number and adds 2^20.  The last-CTA
+    protocol carries the number as a launch argument and refuses capture."""
+    rows, width = 640, 2560
+    weights = oracle.make_weights(rows, width, seed=1)
+    x = oracle.normal(width, seed=2)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    w = dev.weights(weights, rows, width)
+    dx = dev.to_device(x)
     out = dev.to_device(np.zeros(rows, np.float32))
     flags = dev.to_device(np.zeros(1, np.int32))
+    assert context.set_option("peer_publish_per_cta", 1).is_ok()
     assert context.capture_begin().is_ok()
     stat = backend.cuda_q8_matvec_device_f32_allgather(context, w, dx, width, [out], [flags], 0,
                                                        0, rows)
-    assert not stat.is_ok()
-    assert "cannot be captured" in context.last_error()
+    assert stat.is_ok(), stat
     assert context.capture_end().is_ok()
+    for replay in range(3):
+        assert context.graph_launch().is_ok()
+        assert context.synchronize().is_ok()
+        assert dev.int32s(flags, 1)[0] == (replay + 1) << 20
+    assert float(np.abs(dev.floats(out, rows) - expected).max()) <= l2_tolerance(expected)
+    other = backend.cuda_q8_context_t()
+    assert other.create(0).is_ok()
+    w2 = backend.cuda_q8_weights_t()
+    assert w2.upload(other, weights, weights.size, rows, width).is_ok()
+    assert other.capture_begin().is_ok()
+    stat = backend.cuda_q8_matvec_device_f32_allgather(other, w2, dx, width, [out], [flags], 0, 0,
+                                                       rows)
+    assert not stat.is_ok()
+    assert "cannot be captured" in other.last_error()
+    assert other.capture_end().is_ok()
+    w2.destroy()
+    other.destroy()
 
 
 def test_27b_ffn_at_its_eight_way_shard_sizes(backend, context, dev, oracle):
@@ -157,6 +193,42 @@ def test_27b_ffn_at_its_eight_way_shard_sizes(backend, context, dev, oracle):
         total += dev.floats(dout, hidden)
         ffn.destroy()
     assert float(np.abs(total - expected).max()) <= 2 * l2_tolerance(expected)
+
+
+def test_allreduce_ffn_with_a_single_rank(backend, context, dev, oracle):
+    """World size 1: the exchange runs against this rank's own slot and flag arrays; two
+    consecutive calls use the two halves of the slot array."""
+    hidden, inner = 1024, 3840
+    gate = oracle.make_weights(inner, hidden, seed=41)
+    up = oracle.make_weights(inner, hidden, seed=42)
+    down = oracle.make_weights(hidden, inner, seed=43)
+    wg, wu, wd = (dev.weights(m, r, c) for m, r, c in ((gate, inner, hidden), (up, inner, hidden),
+                                                     (down, hidden, inner)))
+    slots = dev.to_device(np.zeros(2 * hidden, np.float32))
+    flags = dev.to_device(np.zeros(1, np.int32))
+    for call in range(3):
+        x = oracle.normal(hidden, seed=50 + call)
+        expected = oracle.ffn(gate, up, down, inner, hidden, hidden, x)
+        dout = dev.buffer(4 * hidden)
+        stat = backend.cuda_q8_ffn_device_allreduce(context, wg, wu, wd, dev.to_device(x), hidden,
+                                                    [slots], [flags], 0, dout, hidden)
+        assert stat.is_ok(), stat
+        assert context.synchronize().is_ok()
+        plain = dev.buffer(4 * hidden)
+        assert backend.cuda_q8_ffn_device(context, wg, wu, wd, dev.to_device(x), hidden, plain,
+                                          hidden).is_ok()
+        assert float(np.abs(dev.floats(dout, hidden) - expected).max()) <= 2 * l2_tolerance(expected)
+        check = dev.floats(dev_slots_half(dev, slots, call & 1, hidden), hidden)
+        assert np.array_equal(check, dev.floats(dout, hidden))       # one slot: the sum is the slot
+    # refused: a rank outside the peer list, missing arrays
+    assert not backend.cuda_q8_ffn_device_allreduce(context, wg, wu, wd, dev.to_device(x), hidden,
+                                                    [slots], [flags], 1, dout, hidden).is_ok()
+    assert not backend.cuda_q8_ffn_device_allreduce(context, wg, wu, wd, dev.to_device(x), hidden,
+                                                    [slots], [], 0, dout, hidden).is_ok()
+
+
+def dev_slots_half(dev, slots, half, hidden):
+    return slots + 4 * half * hidden
 
 
 def _rank_main(rank, world, port, result_path):
@@ -224,6 +296,36 @@ def _rank_main(rank, world, port, result_path):
     torch.cuda.synchronize()
     if float(np.abs(outf.cpu().numpy() - expected_ffn).max()) > 2e-5 * float(np.linalg.norm(expected_ffn)):
         failures.append("sharded FFN differs from the oracle")
+    try:
+        # the same with the partial vectors exchanged by the down GEMV itself, for both a
+        # pipelined-width shard (3840 / world) and consecutive calls (slot parity)
+        import torch.distributed._symmetric_memory as symm
+        slots = symm.empty(2 * world * hidden, dtype=torch.float32, device=torch.device("cuda", rank))
+        slots.zero_()
+        slot_handle = symm.rendezvous(slots, dist.group.WORLD)
+        ffn_flags = symm.empty(world, dtype=torch.int32, device=torch.device("cuda", rank))
+        ffn_flags.zero_()
+        ffn_flag_handle = symm.rendezvous(ffn_flags, dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ffn.attach([int(p) for p in slot_handle.buffer_ptrs],
+                   [int(p) for p in ffn_flag_handle.buffer_ptrs])
+        gathered = [torch.zeros(hidden, device="cuda") for _ in range(world)]
+        for call in range(3):
+            xc = o.normal(hidden, seed=20 + call)
+            want = o.ffn(gate, up, down, inner, hidden, hidden, xc)
+            fused = torch.zeros(hidden, device="cuda")
+            ffn.forward_fused(torch.from_numpy(xc).cuda(), fused)
+            torch.cuda.synchronize()
+            if not ctx.synchronize().is_ok():
+                failures.append("fused FFN reported a device-side timeout")
+            if float(np.abs(fused.cpu().numpy() - want).max()) > 2e-5 * float(np.linalg.norm(want)):
+                failures.append("fused sharded FFN differs from the oracle")
+            dist.all_gather(gathered, fused)
+            if any(not torch.equal(g, gathered[0]) for g in gathered):
+                failures.append("fused sharded FFN: ranks hold different bits")
+    except Exception as error:
+        failures.append(f"SKIP-PEERS {type(error).__name__}: {error}")
     shard.destroy()
     ffn.destroy()
     ctx.destroy()
