@@ -217,12 +217,27 @@ def run_reference_arm(args):
     return 0
 
 
-def workload_config(n_gpus):
+L2_BYTES = 126 * 1000 * 1000
+
+
+def shard_copies(n_gpus):
+    """How many copies of a rank's shard the steps go round: one when the shard is at least
+    twice the L2, else enough for three L2 sizes."""
+    shard = -(-ROWS // n_gpus) * BLOCKS * 34
+    return 1 if shard >= 2 * L2_BYTES else int(min(12, 3 * L2_BYTES // shard + 1))
+
+
+def workload_config(n_gpus, copies=None):
+    copies = shard_copies(n_gpus) if copies is None else copies
+    cache = "inputs larger than L2 (413 MB of weights per step, L2 is 126 MB)"
+    if copies > 1:
+        cache += (f"; a rank's shard is smaller than twice the L2, so the steps go round "
+                  f"{copies} copies of it and every step reads from HBM")
     return {
         "workload": f"lm_head Q8_0 GEMV {ROWS}x{WIDTH} batch 1 (headline configuration)",
         "rows": ROWS, "width": WIDTH, "weight_bytes": WEIGHT_BYTES,
         "sharding": "none" if n_gpus == 1 else f"rows/{n_gpus} per rank, fp32 logits reassembled on every rank",
-        "cache": "inputs larger than L2 (413 MB of weights per step, L2 is 126 MB)",
+        "cache": cache,
         "inputs": "weights ~N(0,0.02) quantized to Q8_0 on the device, activation ~N(0,1), seed 0",
     }
 
@@ -285,10 +300,24 @@ def run_gpu_arm(args):
     counts = [c for _, c in ranges]
     first_row, my_rows = ranges[rank]
     host_weights = make_device_weights(torch, backend, ctx, first_row, my_rows, WIDTH, seed=0)
-    weights = backend.cuda_q8_weights_t()
-    stat = weights.upload(ctx, host_weights, host_weights.size, my_rows, WIDTH)
-    if not stat.is_ok():
-        raise SystemExit(f"weight upload failed: {stat}")
+    # A shard smaller than twice the L2 would be served from L2 when the same bytes are read
+    # step after step (a quarter of the lm_head is 103 MB, L2 is 126 MB): such shards are
+    # uploaded several times and the steps go round the copies, so that every step streams
+    # its weights from HBM, as the single-GPU step does.
+    copies = shard_copies(world)
+    ring = []
+    for _ in range(copies):
+        handle = backend.cuda_q8_weights_t()
+        stat = handle.upload(ctx, host_weights, host_weights.size, my_rows, WIDTH)
+        if not stat.is_ok():
+            raise SystemExit(f"weight upload failed: {stat}")
+        ring.append(handle)
+    weights = ring[0]
+    turn = [0]
+
+    def next_weights():
+        turn[0] = (turn[0] + 1) % copies
+        return ring[turn[0]]
 
     gen = torch.Generator(device="cuda")
     gen.manual_seed(1)
@@ -303,11 +332,11 @@ def run_gpu_arm(args):
             import torch.distributed._symmetric_memory as symm
             logits = symm.empty(ROWS, dtype=torch.float32, device=torch.device("cuda", local_rank))
             symm_handle = symm.rendezvous(logits, dist.group.WORLD)
-            peer_ptrs = [int(p) for p in symm_handle.buffer_ptrs]
+            peer_ptrs = backend.pointer_array([int(p) for p in symm_handle.buffer_ptrs])
             flags = symm.empty(world, dtype=torch.int32, device=torch.device("cuda", local_rank))
             flags.zero_()
             flag_handle = symm.rendezvous(flags, dist.group.WORLD)
-            flag_ptrs = [int(p) for p in flag_handle.buffer_ptrs]
+            flag_ptrs = backend.pointer_array([int(p) for p in flag_handle.buffer_ptrs])
             torch.cuda.synchronize()
             dist.barrier()
         except Exception as error:  # no peer access on this box: fall back to NCCL
@@ -319,7 +348,7 @@ def run_gpu_arm(args):
     my_slice = logits[first_row:first_row + my_rows]
 
     def step_allgather(x=x):
-        stat = backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH,
+        stat = backend.cuda_q8_matvec_device_f32(ctx, next_weights(), x.data_ptr(), WIDTH,
                                                  my_slice.data_ptr(), my_rows)
         if not stat.is_ok():
             raise RuntimeError(f"matvec failed: {stat}")
@@ -327,14 +356,14 @@ def run_gpu_arm(args):
             sharded.all_gather_rows(dist, my_slice, counts, logits)
 
     def step_peers(x=x):
-        stat = backend.cuda_q8_matvec_device_f32_peers(ctx, weights, x.data_ptr(), WIDTH,
+        stat = backend.cuda_q8_matvec_device_f32_peers(ctx, next_weights(), x.data_ptr(), WIDTH,
                                                        peer_ptrs, first_row, ROWS)
         if not stat.is_ok():
             raise RuntimeError(f"peer matvec failed: {stat}")
         symm_handle.barrier(channel=0)
 
     def step_fused(x=x):
-        stat = backend.cuda_q8_matvec_device_f32_allgather(ctx, weights, x.data_ptr(), WIDTH,
+        stat = backend.cuda_q8_matvec_device_f32_allgather(ctx, next_weights(), x.data_ptr(), WIDTH,
                                                            peer_ptrs, flag_ptrs, rank, first_row,
                                                            ROWS)
         if not stat.is_ok():
@@ -463,14 +492,14 @@ def run_gpu_arm(args):
 
     # ---- kernel alone on this rank (no collective), for the roofline
     for _ in range(3):
-        backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH, my_slice.data_ptr(),
-                                          my_rows)
+        backend.cuda_q8_matvec_device_f32(ctx, next_weights(), x.data_ptr(), WIDTH,
+                                          my_slice.data_ptr(), my_rows)
     torch.cuda.synchronize()
     k_iters = max(20, min(args.steps, 2000))
     start.record(stream)
     for _ in range(k_iters):
-        backend.cuda_q8_matvec_device_f32(ctx, weights, x.data_ptr(), WIDTH, my_slice.data_ptr(),
-                                          my_rows)
+        backend.cuda_q8_matvec_device_f32(ctx, next_weights(), x.data_ptr(), WIDTH,
+                                          my_slice.data_ptr(), my_rows)
     stop.record(stream)
     torch.cuda.synchronize()
     kernel_ms = start.elapsed_time(stop) / k_iters
@@ -481,7 +510,7 @@ def run_gpu_arm(args):
             print(json.dumps({"kernel_only": True, "rows": ROWS, "kernel_ms": kernel_ms,
                               "weight_gbs": my_rows * BLOCKS * 34 / kernel_ms / 1e6,
                               "ms_per_step": elapsed_ms / args.steps}), flush=True)
-        ctx_cleanup(weights, ctx, dist)
+        ctx_cleanup(ring, ctx, dist)
         return 0
 
     # ---- end to end through the host-buffer entry point, pinned buffers
@@ -491,11 +520,11 @@ def run_gpu_arm(args):
     hx, ho = host_x.numpy(), host_out.numpy()
     e2e_steps = max(10, min(args.steps, 500))
     for _ in range(3):
-        backend.cuda_q8_matvec_host_f32(ctx, weights, hx, ho)
+        backend.cuda_q8_matvec_host_f32(ctx, next_weights(), hx, ho)
     barrier()
     te = time.perf_counter()
     for _ in range(e2e_steps):
-        _, stat = backend.cuda_q8_matvec_host_f32(ctx, weights, hx, ho)
+        _, stat = backend.cuda_q8_matvec_host_f32(ctx, next_weights(), hx, ho)
         if world > 1:
             my_slice.copy_(host_out, non_blocking=True)
             sharded.all_gather_rows(dist, my_slice, counts, logits)
@@ -515,7 +544,7 @@ def run_gpu_arm(args):
         mmq = bench_mmq(torch, backend, ctx)
 
     if rank != 0:
-        ctx_cleanup(weights, ctx, dist)
+        ctx_cleanup(ring, ctx, dist)
         return 0
 
     peaks, peak_kind = measured_peaks()
@@ -529,7 +558,7 @@ def run_gpu_arm(args):
         "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 scales", "data": "synthetic",
-        "config": workload_config(world),
+        "config": workload_config(world, copies),
         "exchange": {"used": exchange, "ms_per_step": exchange_ms, "verified": exchange_verified},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                      "frac": achieved / hbm_peak, "traffic": GEMV_DRAM_TRAFFIC_PER_ROW * my_rows,
@@ -553,7 +582,7 @@ def run_gpu_arm(args):
         xs = x.cpu().numpy()
         line["cpu_baseline"] = cpu_baseline_block(host_weights, xs)
     print(json.dumps(line), flush=True)
-    ctx_cleanup(weights, ctx, dist)
+    ctx_cleanup(ring, ctx, dist)
     return 0
 
 
@@ -889,14 +918,28 @@ def run_ffn(args):
     gate = make_device_weights(torch, backend, ctx, 0, inner, hidden, seed=40)
     up = make_device_weights(torch, backend, ctx, 0, inner, hidden, seed=41)
     down = make_device_weights(torch, backend, ctx, 0, hidden, inner, seed=42)
-    ffn = sharded.ShardedFfn(backend, ctx, gate, up, down, hidden, inner, rank, world)
+    # shards that would fit in L2 are uploaded several times; the steps go round the copies
+    shard_bytes = 3 * inner * (hidden // 32) * 34 // world
+    copies = 1 if shard_bytes >= 2 * L2_BYTES else int(min(12, 3 * L2_BYTES // shard_bytes + 1))
+    ffns = [sharded.ShardedFfn(backend, ctx, gate, up, down, hidden, inner, rank, world)
+            for _ in range(copies)]
+    turn = [0]
+
+    class Rotating:
+        """The next copy's method on every attribute access."""
+        def __getattr__(self, name):
+            turn[0] = (turn[0] + 1) % copies
+            return getattr(ffns[turn[0]], name)
+    ffn = Rotating()
     gen = torch.Generator(device="cuda")
     gen.manual_seed(2)
     x = torch.randn(hidden, generator=gen, device="cuda", dtype=torch.float32)
     out = torch.empty(hidden, device="cuda", dtype=torch.float32)
 
     def local_only():
-        stat = backend.cuda_q8_ffn_device(ctx, ffn.gate, ffn.up, ffn.down, x.data_ptr(), hidden,
+        one = ffns[turn[0]]
+        turn[0] = (turn[0] + 1) % copies
+        stat = backend.cuda_q8_ffn_device(ctx, one.gate, one.up, one.down, x.data_ptr(), hidden,
                                           out.data_ptr(), hidden)
         if not stat.is_ok():
             raise RuntimeError(f"FFN failed: {stat}")
@@ -939,8 +982,9 @@ def run_ffn(args):
             keep += [slots, slot_handle, flags, flag_handle]
             torch.cuda.synchronize()
             dist.barrier()
-            ffn.attach([int(p) for p in slot_handle.buffer_ptrs],
-                       [int(p) for p in flag_handle.buffer_ptrs])
+            for one in ffns:
+                one.attach([int(p) for p in slot_handle.buffer_ptrs],
+                           [int(p) for p in flag_handle.buffer_ptrs])
             fused_out = torch.empty(hidden, device="cuda", dtype=torch.float32)
             fused_ms = timed(lambda: ffn.forward_fused(x, fused_out), steps)
             stat = ctx.synchronize()
@@ -1002,9 +1046,11 @@ def run_ffn(args):
                                      "weight_bytes": nbytes,
                                      "sharding": f"gate/up rows/{world}, down columns/{world}, "
                                                  "fp32 all-reduce of 5120 floats per token",
-                                     "cache": "284 MB of weights per step in total"}}),
+                                     "cache": f"284 MB of weights per step in total; the steps go "
+                                              f"round {copies} copies of a rank's shard"}}),
               flush=True)
-    ffn.destroy()
+    for one in ffns:
+        one.destroy()
     ctx.destroy()
     if dist is not None:
         dist.destroy_process_group()
@@ -1161,7 +1207,7 @@ def run_reference_format(args):
     return 0 if correct else 1
 
 
-def ctx_cleanup(weights, ctx, dist):
+def ctx_cleanup(ring, ctx, dist):
     weights.destroy()
     ctx.destroy()
     if dist is not None:

@@ -70,6 +70,14 @@ def _host_ptr(array: np.ndarray) -> int:
     return array.ctypes.data
 
 
+def pointer_array(pointers):
+    """A C array of `void *` from a sequence of addresses.  Callers on a hot path build it once
+    and pass it in place of the list: the wrappers take either."""
+    if isinstance(pointers, ctypes.Array):
+        return pointers
+    return (c_void_p * len(pointers))(*[int(p) for p in pointers])
+
+
 def _as_bytes(array) -> np.ndarray:
     a = np.ascontiguousarray(array)
     return a.view(np.int8).reshape(-1)
@@ -668,7 +676,7 @@ def cuda_q8_matvec_device_f32_peers(context, weights, device_activation, activat
     if (not context.handle or not weights.handle or not device_activation or not peer_outputs):
         stat.set(FORTAI_INVALID, "invalid CUDA Q8 peer matvec")
         return stat
-    array = (c_void_p * len(peer_outputs))(*[c_void_p(p) for p in peer_outputs])
+    array = pointer_array(peer_outputs)
     code = _lib().fortai_cuda_q8_matvec_device_f32_peers(
         context.handle, weights.handle, device_activation, activation_elements, array,
         len(peer_outputs), int(first_row), int(output_elements))
@@ -686,8 +694,8 @@ def cuda_q8_matvec_device_f32_allgather(context, weights, device_activation, act
             len(peer_outputs) != len(peer_flags)):
         stat.set(FORTAI_INVALID, "invalid CUDA Q8 all-gather matvec")
         return stat
-    outs = (c_void_p * len(peer_outputs))(*[c_void_p(p) for p in peer_outputs])
-    flags = (c_void_p * len(peer_flags))(*[c_void_p(p) for p in peer_flags])
+    outs = pointer_array(peer_outputs)
+    flags = pointer_array(peer_flags)
     code = _lib().fortai_cuda_q8_matvec_device_f32_allgather(
         context.handle, weights.handle, device_activation, activation_elements, outs, flags,
         len(peer_outputs), int(my_rank), int(first_row), int(output_elements))
@@ -708,8 +716,8 @@ def cuda_q8_ffn_device_allreduce(context, gate, up, down, device_activation, act
             len(peer_slots) != len(peer_flags)):
         stat.set(FORTAI_INVALID, "invalid CUDA Q8 all-reduce FFN")
         return stat
-    slots = (c_void_p * len(peer_slots))(*[c_void_p(p) for p in peer_slots])
-    flags = (c_void_p * len(peer_flags))(*[c_void_p(p) for p in peer_flags])
+    slots = pointer_array(peer_slots)
+    flags = pointer_array(peer_flags)
     code = _lib().fortai_cuda_q8_ffn_device_allreduce(
         context.handle, gate.handle, up.handle, down.handle, device_activation,
         int(activation_elements), slots, flags, len(peer_slots), int(my_rank), device_output,

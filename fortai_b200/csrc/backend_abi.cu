@@ -1901,6 +1901,9 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_peers(fortai_cuda_q8_context *co
     p.peers = peer_count;
     p.peer_flush = context->peer_flush_rows;
     p.first_row = static_cast<int>(first_row);
+    // the kernel stores nothing anywhere before its own dependency wait, which ends only when
+    // everything earlier in this stream has completed: it may start under its predecessor
+    p.overlap_ok = context->peer_overlap;
     const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "peer-output matvec", error);
 }

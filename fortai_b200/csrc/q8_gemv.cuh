@@ -533,19 +533,19 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         warp_in_cta * ROWS * (2 * CPL * 16);
 
     // Row assignment.  Ordinary outputs: grid-stride over warps (warp g takes rows g,
-    // g + W, ...).  Peer outputs: each CTA takes one contiguous block of rows and each of
-    // its warps a contiguous run inside it; a warp keeps its results in its lanes (row i of
-    // the run in lane i mod 32) and stores them to every peer a group at a time, so that
-    // the link carries whole sectors or lines, spread over the kernel's duration.
+    // g + W, ...).  Peer outputs: warp g of the grid takes the contiguous run
+    // [g * R / W, (g + 1) * R / W) - run lengths differ by at most one row, as with the
+    // grid-stride order - keeps its results in its lanes (row i of the run in lane i mod 32)
+    // and stores them to every peer a group at a time, so that the link carries whole
+    // sectors or lines, spread over the kernel's duration.
     int row, row_step, row_end, warp_first = 0;
     if (EPI == kEpiPeers) {
-        const int per_cta = (p.total_rows + gridDim.x - 1) / gridDim.x;
-        const int per_warp = (per_cta + kGemvWarps - 1) / kGemvWarps;
-        const int cta_end = min(p.total_rows, (static_cast<int>(blockIdx.x) + 1) * per_cta);
-        warp_first = blockIdx.x * per_cta + warp_in_cta * per_warp;
+        const long long warps = static_cast<long long>(gridDim.x) * kGemvWarps;
+        const long long g = static_cast<long long>(blockIdx.x) * kGemvWarps + warp_in_cta;
+        warp_first = static_cast<int>(g * p.total_rows / warps);
         row = warp_first;
         row_step = 1;
-        row_end = min(cta_end, warp_first + per_warp);
+        row_end = static_cast<int>((g + 1) * p.total_rows / warps);
     } else {
         row = blockIdx.x * kGemvWarps + warp_in_cta;
         row_step = gridDim.x * kGemvWarps;

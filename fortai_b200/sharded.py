@@ -147,9 +147,11 @@ class PeerGatherMatvec(RowShardedMatvec):
 
     def attach(self, peer_output_ptrs: Sequence[int], barrier: Callable[[], None],
                peer_flag_ptrs: Sequence[int] = None):
-        self.peer_ptrs = list(peer_output_ptrs)
+        # C arrays built once: the calls are made once per decoded token
+        self.peer_ptrs = self.backend.pointer_array(list(peer_output_ptrs))
         self.barrier = barrier
-        self.flag_ptrs = list(peer_flag_ptrs) if peer_flag_ptrs is not None else None
+        self.flag_ptrs = (self.backend.pointer_array(list(peer_flag_ptrs))
+                          if peer_flag_ptrs is not None else None)
 
     def matvec_fused(self, activation: "torch.Tensor"):
         """Slice + all-gather in ONE kernel: the last CTA of every rank raises a flag in
@@ -205,8 +207,8 @@ class ShardedFfn:
     def attach(self, peer_slot_ptrs: Sequence[int], peer_flag_ptrs: Sequence[int]):
         """Slot arrays (2 * world * hidden floats per rank) and flag arrays (world words per
         rank, zeroed once) that every rank can reach, for `forward_fused`."""
-        self.slot_ptrs = list(peer_slot_ptrs)
-        self.flag_ptrs = list(peer_flag_ptrs)
+        self.slot_ptrs = self.backend.pointer_array(list(peer_slot_ptrs))
+        self.flag_ptrs = self.backend.pointer_array(list(peer_flag_ptrs))
 
     def forward_fused(self, activation: "torch.Tensor", out: "torch.Tensor"):
         """The same result without a collective call: partial vectors are exchanged by the
