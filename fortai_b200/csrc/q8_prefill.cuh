@@ -318,6 +318,67 @@ __device__ __forceinline__ uint4 ldg_early_16(const void *address) {
     return v;
 }
 
+// ---- work split ---------------------------------------------------------------------------
+// T tiles (256 weight rows x TN tokens, `blocks` units each) on P CTA pairs.  Pair p takes
+// the whole tiles p, p + P, ... (floor(T / P) of them: no other pair touches these, their
+// results are stored plainly) and then its share of the T mod P tiles that are left over, cut
+// into P equal runs of units whatever the tile borders ("split" tiles: their pieces are added
+// into zeroed output with atomics).  Every pair gets the same number of units to within one;
+// only the left-over tiles pay for zeroing, atomics and a second epilogue.  (Equal shares of
+// one long tile-major unit list split nearly every tile: 76 tiles on 74 pairs then cost 20 us
+// more than 74 tiles.)
+struct PfWalk {
+    int tile, kb, count;        // current segment: blocks kb .. kb + count - 1 of `tile`
+    int whole_left, pairs, blocks, rem_tile, rem_kb, rem_count;
+    bool rem_entered;
+};
+
+__host__ __device__ inline int pf_whole_tiles(int tiles, int pairs) {
+    return tiles / pairs * pairs;      // tiles below this index are never split
+}
+
+__device__ __forceinline__ void pf_walk_next_segment(PfWalk &w) {
+    if (w.whole_left > 0) {
+        --w.whole_left;
+        w.tile += w.pairs;
+        w.kb = 0;
+        w.count = w.blocks;
+        return;
+    }
+    if (!w.rem_entered) {
+        w.rem_entered = true;
+        w.tile = w.rem_tile;
+        w.kb = w.rem_kb;
+    } else {
+        ++w.tile;
+        w.kb = 0;
+    }
+    const int room = w.blocks - w.kb;
+    w.count = w.rem_count < room ? w.rem_count : room;
+    w.rem_count -= w.count;
+}
+
+// Positions `w` on the pair's first segment; returns the pair's number of units.
+__device__ __forceinline__ int pf_walk_begin(PfWalk &w, int tiles, int blocks, int pairs, int pair) {
+    const int whole = tiles / pairs;
+    const int rest = tiles - whole * pairs;
+    const long long rem_begin = static_cast<long long>(rest) * blocks * pair / pairs;
+    const long long rem_end = static_cast<long long>(rest) * blocks * (pair + 1) / pairs;
+    w.pairs = pairs;
+    w.blocks = blocks;
+    w.rem_tile = whole * pairs + static_cast<int>(rem_begin / blocks);
+    w.rem_kb = static_cast<int>(rem_begin % blocks);
+    w.rem_count = static_cast<int>(rem_end - rem_begin);
+    const int total = whole * blocks + w.rem_count;
+    w.whole_left = whole;
+    w.rem_entered = false;
+    w.tile = pair - pairs;
+    w.kb = 0;
+    w.count = 0;
+    pf_walk_next_segment(w);
+    return total;
+}
+
 template <int TN>
 __global__ void __launch_bounds__(kPfThreads, 1)
 q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
@@ -345,10 +406,11 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     const uint32_t rank = cluster_cta_rank();
     const int pair = blockIdx.x >> 1;
     const int pairs = gridDim.x >> 1;
-    const long long total_units = static_cast<long long>(p.tiles) * p.blocks;
-    const long long unit_begin = mmq_unit_begin(total_units, pairs, pair);
-    const long long unit_end = mmq_unit_begin(total_units, pairs, pair + 1);
-    const int unit_count = static_cast<int>(unit_end - unit_begin);
+    int unit_count;
+    {
+        PfWalk probe;
+        unit_count = pf_walk_begin(probe, p.tiles, p.blocks, pairs, pair);
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kPfStages; ++s) {
@@ -390,16 +452,19 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const int producer = warp == 0 ? 0 : 1;
                 bool ok = true;
                 int chunks = 0;         // raw weight loads armed so far
-                int tile = static_cast<int>(unit_begin / p.blocks);
-                int kb = static_cast<int>(unit_begin - static_cast<long long>(tile) * p.blocks);
+                PfWalk walk;
+                pf_walk_begin(walk, p.tiles, p.blocks, pairs, pair);
+                int kb = walk.kb, left = walk.count;
+                bool segment_first = true;
                 const uint32_t empty_bar = smem_u32(&sh->empty[0]);
                 const uint32_t raw_empty_bar = smem_u32(&sh->raw_empty[0]);
                 int armed = 0;
                 for (; armed < unit_count && ok; ++armed) {
                     const bool mine = (armed & 1) == producer;
+                    const int tile = walk.tile;
                     const int row0 = (tile % p.tiles_n) * kPfPairRows + rank * kPfTileRows;
                     const int token0 = (tile / p.tiles_n) * TN + rank * (TN / 2);
-                    if (armed == 0 || (kb & (kPfRawBlocks - 1)) == 0) {
+                    if (segment_first || (kb & (kPfRawBlocks - 1)) == 0) {
                         if (mine) {
                             const int rb = chunks % kPfRawBuffers;
                             const int use = chunks / kPfRawBuffers;
@@ -422,9 +487,14 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                             token0, &sh->full[s]);
                         if (producer == 0) PF_STAMP(0, armed >> 1, 1);
                     }
-                    if (++kb == p.blocks) {
-                        kb = 0;
-                        ++tile;
+                    if (--left == 0) {
+                        pf_walk_next_segment(walk);
+                        kb = walk.kb;
+                        left = walk.count;
+                        segment_first = true;
+                    } else {
+                        ++kb;
+                        segment_first = false;
                     }
                 }
                 if (!ok) {
@@ -528,22 +598,23 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
             const uint32_t empty_bar = smem_u32(&sh->empty[0]);
             const uint32_t full_bar = smem_u32(&sh->full[0]);
             const uint32_t converted_bar = smem_u32(&sh->converted[0]);
-            int tile = static_cast<int>(unit_begin / p.blocks);
-            int kb = static_cast<int>(unit_begin - static_cast<long long>(tile) * p.blocks);
+            PfWalk walk;
+            pf_walk_begin(walk, p.tiles, p.blocks, pairs, pair);
+            int kb = walk.kb, left = walk.count;
+            bool segment_first = true;
             int chunks = 0;             // raw weight loads seen so far
             bool own_in_chunk = false;  // this warp has converted a block of the current load
             bool ok = true;
             for (int n = 0; n < unit_count && ok; ++n) {
                 const bool mine = (n & (kPfConverterWarps - 1)) == cw;
-                if (n == 0 || (kb & (kPfRawBlocks - 1)) == 0) {
+                if (segment_first || (kb & (kPfRawBlocks - 1)) == 0) {
                     ++chunks;
                     own_in_chunk = false;
                 }
                 const int rb = (chunks - 1) % kPfRawBuffers;
                 const uint32_t raw_parity = ((chunks - 1) / kPfRawBuffers) & 1;
                 const int j = kb & (kPfRawBlocks - 1);
-                const bool chunk_last = j == kPfRawBlocks - 1 || kb == p.blocks - 1 ||
-                    n == unit_count - 1;
+                const bool chunk_last = j == kPfRawBlocks - 1 || left == 1;
                 if (mine) {
                     if (cw == 0) PF_STAMP(2, n >> 2, 0);
                     const int s = n % kPfStages;
@@ -611,9 +682,14 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                     if (lane == 0) mbar_arrive(&sh->raw_empty[rb]);
                 }
                 if (chunk_last) own_in_chunk = true;    // nothing more is owed for this load
-                if (++kb == p.blocks) {
-                    kb = 0;
-                    ++tile;
+                if (--left == 0) {
+                    pf_walk_next_segment(walk);
+                    kb = walk.kb;
+                    left = walk.count;
+                    segment_first = true;
+                } else {
+                    ++kb;
+                    segment_first = false;
                 }
             }
         }
@@ -632,11 +708,13 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
         bool failed = false;
 
         int drained = 0;        // blocks drained (TMEM ring position)
-        for (long long u = unit_begin; u < unit_end && !failed;) {
-            const int tile = static_cast<int>(u / p.blocks);
-            const int first_block = static_cast<int>(u - static_cast<long long>(tile) * p.blocks);
-            const long long tile_end = static_cast<long long>(tile + 1) * p.blocks;
-            const int count = static_cast<int>((tile_end < unit_end ? tile_end : unit_end) - u);
+        PfWalk walk;
+        pf_walk_begin(walk, p.tiles, p.blocks, pairs, pair);
+        const int whole_tiles = pf_whole_tiles(p.tiles, pairs);
+        for (int done = 0; done < unit_count && !failed;) {
+            const int tile = walk.tile;
+            const int first_block = walk.kb;
+            const int count = walk.count;
             const int row0 = (tile % p.tiles_n) * kPfPairRows + rank * kPfTileRows;
             const int token0 = (tile / p.tiles_n) * TN;
             const int row = row0 + quadrant * 32 + lane;
@@ -716,7 +794,7 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 if (et == 0) PF_STAMP(3, drained, 3);
             }
             if (!failed && row_ok) {
-                const bool split = count != p.blocks;
+                const bool split = tile >= whole_tiles;
 #pragma unroll
                 for (int e = 0; e < kPairs; ++e) {
                     const int t = token0 + col0 + 2 * e;
@@ -733,7 +811,8 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                     }
                 }
             }
-            u += count;
+            done += count;
+            pf_walk_next_segment(walk);
         }
     }
 
@@ -762,6 +841,106 @@ __device__ __forceinline__ void pf_split_store(float value, float up, __half &hi
     lo = __float2half_rn(scaled - __half2float(hi));        // exact difference, fits binary16
 }
 
+// Split tiles take their pieces as atomic adds: zero them first.  All CTAs of the grid share
+// the work (one CTA per tile took 17 us for a 256 x 256 tile, and the product kernel waits for
+// this grid): four consecutive rows per thread and step.
+__device__ __forceinline__ void pf_zero_split_tiles(float *__restrict__ output, int rows, int tokens,
+    int tile_tokens, int tiles_n, int tiles, int product_grid) {
+    if (!output) return;
+    const int first_split = pf_whole_tiles(tiles, product_grid);
+    const int per_tile = (kPfPairRows / 4) * tile_tokens;           // groups of four rows
+    const long long total = static_cast<long long>(tiles - first_split) * per_tile;
+    const bool vector = (rows & 3) == 0 && (reinterpret_cast<uintptr_t>(output) & 15) == 0;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const int tile = first_split + static_cast<int>(i / per_tile);
+        const int within = static_cast<int>(i % per_tile);
+        const int r = (tile % tiles_n) * kPfPairRows + (within % (kPfPairRows / 4)) * 4;
+        const int t = (tile / tiles_n) * tile_tokens + within / (kPfPairRows / 4);
+        if (t >= tokens || r >= rows) continue;
+        float *dst = output + static_cast<size_t>(t) * rows + r;
+        if (vector) {                                  // rows % 4 == 0: r + 3 < rows
+            *reinterpret_cast<float4 *>(dst) = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        } else {
+            for (int k = 0; k < 4 && r + k < rows; ++k) dst[k] = 0.0f;
+        }
+    }
+}
+
+// fp32 activations, the fast form: one CTA per token, blockDim.x * ITEMS >= width / 4.  A thread
+// requests its ITEMS float4 at once and keeps them in registers through both steps (largest
+// block scale of the token, then quantize + split), so the kernel costs one trip to memory
+// instead of six in a row.
+template <int ITEMS>
+__global__ void __launch_bounds__(1024)
+pf_prepare_f32_kernel(const float *__restrict__ activation, int tokens, int padded_tokens,
+    int width, __half *__restrict__ image, float *__restrict__ unscale, float *__restrict__ output,
+    int rows, int tile_tokens, int tiles_n, int tiles, int product_grid) {
+    grid_dependents_may_launch();
+    __shared__ float warp_max[32];
+    const int lane = threadIdx.x & 31;
+    const int quads = width >> 2;
+    for (int token = blockIdx.x; token < padded_tokens; token += gridDim.x) {
+        const bool real = token < tokens;
+        const float4 *x4 = reinterpret_cast<const float4 *>(activation) +
+            static_cast<size_t>(token) * quads;
+        float4 v[ITEMS];
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int g = i * blockDim.x + threadIdx.x;
+            v[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (real && g < quads) v[i] = x4[g];
+        }
+        // eight lanes per block (trip counts are warp-uniform: the shuffles are safe)
+        float amax[ITEMS], scale_max = 0.0f;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            float a = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+            a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+            amax[i] = a;
+            scale_max = fmaxf(scale_max, __half2float(__float2half_rn(__fdiv_rn(a, 127.0f))));
+        }
+#pragma unroll
+        for (int offset = 16; offset; offset >>= 1)
+            scale_max = fmaxf(scale_max, __shfl_xor_sync(0xffffffffu, scale_max, offset));
+        __syncthreads();            // the previous token's maxima have been read by everyone
+        if (lane == 0) warp_max[threadIdx.x >> 5] = scale_max;
+        __syncthreads();
+        float m = 0.0f;
+        for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) m = fmaxf(m, warp_max[w]);
+        // E = exponent of m; binary16 scales lie in [2^-24, 2^16), infinities clamp
+        int e = m > 0.0f ? ((__float_as_int(m) >> 23) & 0xff) - 127 : 7;
+        e = max(-30, min(e, 30));
+        const float up = __int_as_float((127 + 7 - e) << 23);
+        if (threadIdx.x == 0) unscale[token] = real ? __int_as_float((127 - 7 + e) << 23) : 0.0f;
+        __half *row = image + static_cast<size_t>(token) * width * 2;
+#pragma unroll
+        for (int i = 0; i < ITEMS; ++i) {
+            const int g = i * blockDim.x + threadIdx.x;
+            if (g >= quads) continue;
+            const float da = __half2float(__float2half_rn(__fdiv_rn(amax[i], 127.0f)));
+            const float inverse = amax[i] != 0.0f ? __fdiv_rn(127.0f, amax[i]) : 0.0f;
+            const float q0 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v[i].x, inverse)))));
+            const float q1 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v[i].y, inverse)))));
+            const float q2 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v[i].z, inverse)))));
+            const float q3 = static_cast<float>(max(-128, min(127, __float2int_rn(__fmul_rn(v[i].w, inverse)))));
+            __half h[4], l[4];
+            pf_split_store(__fmul_rn(da, q0), up, h[0], l[0]);
+            pf_split_store(__fmul_rn(da, q1), up, h[1], l[1]);
+            pf_split_store(__fmul_rn(da, q2), up, h[2], l[2]);
+            pf_split_store(__fmul_rn(da, q3), up, h[3], l[3]);
+            // block g / 8, elements 4 * (g % 8) .. + 3
+            __half *block = row + (g >> 3) * 64 + (g & 7) * 4;
+            *reinterpret_cast<uint2 *>(block) = *reinterpret_cast<const uint2 *>(h);
+            *reinterpret_cast<uint2 *>(block + 32) = *reinterpret_cast<const uint2 *>(l);
+        }
+    }
+    pf_zero_split_tiles(output, rows, tokens, tile_tokens, tiles_n, tiles, product_grid);
+}
+
+// Any width, fp32 or Q8_0 input: two passes over the token.
 template <int ACT>
 __global__ void __launch_bounds__(256)
 pf_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_tokens, int width,
@@ -867,18 +1046,7 @@ pf_prepare_kernel(const void *__restrict__ activation, int tokens, int padded_to
             }
         }
     }
-    if (!output) return;
-    const long long total_units = static_cast<long long>(tiles) * blocks;
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-        if (!mmq_tile_is_split(total_units, product_grid, blocks, tile)) continue;
-        const int row0 = (tile % tiles_n) * kPfPairRows;
-        const int token0 = (tile / tiles_n) * tile_tokens;
-        for (int i = threadIdx.x; i < kPfPairRows * tile_tokens; i += blockDim.x) {
-            const int r = row0 + (i & (kPfPairRows - 1));
-            const int t = token0 + i / kPfPairRows;
-            if (r < rows && t < tokens) output[static_cast<size_t>(t) * rows + r] = 0.0f;
-        }
-    }
+    pf_zero_split_tiles(output, rows, tokens, tile_tokens, tiles_n, tiles, product_grid);
 }
 
 // ---- host side ----------------------------------------------------------------
@@ -990,7 +1158,19 @@ inline cudaError_t pf_enqueue(cudaStream_t stream, int sm_count, int *status, Pf
     const int grid = 2 * pairs;
     {
         const int prep_grid = std::min(padded, sm_count * 8);
-        if (act == 1)
+        const int quads = width / 4;
+        const bool aligned = (reinterpret_cast<uintptr_t>(activation) & 15) == 0;
+        if (act == 1 && aligned && quads <= 3 * 1024) {
+            const int threads = std::min(1024, ((quads + 2) / 3 + 31) / 32 * 32);
+            pf_prepare_f32_kernel<3><<<padded, threads, 0, stream>>>(
+                static_cast<const float *>(activation), tokens, padded, width, image, unscale,
+                output, rows, tn, p.tiles_n, p.tiles, pairs);
+        } else if (act == 1 && aligned && quads <= 5 * 1024) {
+            const int threads = std::min(1024, ((quads + 4) / 5 + 31) / 32 * 32);
+            pf_prepare_f32_kernel<5><<<padded, threads, 0, stream>>>(
+                static_cast<const float *>(activation), tokens, padded, width, image, unscale,
+                output, rows, tn, p.tiles_n, p.tiles, pairs);
+        } else if (act == 1)
             pf_prepare_kernel<1><<<prep_grid, 256, 0, stream>>>(activation, tokens, padded, width,
                 image, unscale, output, rows, tn, p.tiles_n, p.tiles, pairs);
         else
