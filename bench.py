@@ -1208,7 +1208,8 @@ def run_reference_format(args):
 
 
 def ctx_cleanup(ring, ctx, dist):
-    weights.destroy()
+    for handle in ring:
+        handle.destroy()
     ctx.destroy()
     if dist is not None:
         dist.destroy_process_group()

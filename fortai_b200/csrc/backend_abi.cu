@@ -426,7 +426,9 @@ bool launch_slice(fortai_cuda_q8_context *c, const GemvParams &p, cudaError_t *e
     int split = c->gemv_split;
     if (split == 0) {
         if (granules < 16 || p.total_rows > 2 * c->sm_count * 4 * kGemvWarps) return false;
-        split = (granules + 3) / 4 <= 9 ? 4 : 8;
+        // measured: 34 granules 17.1 us with 8 warps per row against 17.8 with 4; 19 granules
+        // 7.7 us with 4 against 8.1 with 8
+        split = granules >= 24 ? 8 : 4;
     }
     const int most = (granules + split - 1) / split;
     if (most > 9 || granules < split) return false;
