@@ -160,29 +160,49 @@ bool read_value(Cursor &in, int32_t type, Meta &m) {
     return in.ok;
 }
 
-int64_t element_count(const Tensor &t) {
+// Product of the shape; false when it does not fit 63 bits (a file cannot hold such a tensor,
+// and a wrapped product would pass the range check against the file size).
+bool element_count(const Tensor &t, int64_t *count) {
     int64_t n = 1;
-    for (int i = 0; i < t.rank; ++i) n *= t.shape[i];
-    return n;
+    for (int i = 0; i < t.rank; ++i)
+        if (t.shape[i] < 0 || __builtin_mul_overflow(n, t.shape[i], &n)) return false;
+    *count = n;
+    return true;
+}
+
+int64_t element_count(const Tensor &t) {
+    int64_t n = 0;
+    return element_count(t, &n) ? n : 0;
 }
 
 // Size of a tensor's data; the reference's rules and messages.
 int tensor_bytes(const Tensor &t, int64_t *bytes, const char **why) {
-    const int64_t elements = element_count(t);
+    int64_t elements = 0;
+    if (!element_count(t, &elements)) {
+        *why = "GGUF tensor shape overflows";
+        return FORTAI_GGUF_INVALID;
+    }
     switch (t.type) {
-    case FORTAI_GGML_TYPE_F32: *bytes = 4 * elements; return FORTAI_GGUF_OK;
-    case FORTAI_GGML_TYPE_F16: *bytes = 2 * elements; return FORTAI_GGUF_OK;
+    case FORTAI_GGML_TYPE_F32:
+        if (__builtin_mul_overflow(elements, static_cast<int64_t>(4), bytes)) break;
+        return FORTAI_GGUF_OK;
+    case FORTAI_GGML_TYPE_F16:
+        if (__builtin_mul_overflow(elements, static_cast<int64_t>(2), bytes)) break;
+        return FORTAI_GGUF_OK;
     case FORTAI_GGML_TYPE_Q8_0:
         if (t.shape[0] <= 0 || t.shape[0] % 32 != 0) {
             *why = "Q8_0 tensor width is not a multiple of 32";
             return FORTAI_GGUF_INVALID;
         }
-        *bytes = (elements / t.shape[0]) * (t.shape[0] / 32) * 34;
+        // blocks * 34 <= elements * 34 / 32: check the larger product
+        if (__builtin_mul_overflow(elements / 32, static_cast<int64_t>(34), bytes)) break;
         return FORTAI_GGUF_OK;
     default:
         *why = "GGUF tensor quantization is not supported";
         return FORTAI_GGUF_UNSUPPORTED;
     }
+    *why = "GGUF tensor shape overflows";
+    return FORTAI_GGUF_INVALID;
 }
 
 float half_to_float(uint16_t raw) {
@@ -272,6 +292,10 @@ extern "C" int fortai_gguf_open(const char *path, fortai_gguf_file **file, char 
         }
         created->alignment = fortai_gguf_meta_int(created, "general.alignment", 32);
         if (created->alignment <= 0) created->alignment = 32;
+        // a power of two of at most 1 MiB: anything else cannot be a GGUF alignment, and a huge
+        // value would overflow the rounding of the data offset below
+        if ((created->alignment & (created->alignment - 1)) != 0 || created->alignment > (1 << 20))
+            return give_up(FORTAI_GGUF_INVALID, "invalid GGUF alignment");
         created->tensors.resize(static_cast<size_t>(created->tensor_count));
         for (Tensor &t : created->tensors) {
             const char *text = nullptr;

@@ -278,7 +278,8 @@ __device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigne
     return r;
 }
 
-// 18 warps are allocated registers like 20 (groups of four), so 96 per thread is the cap.
+// Ten warps (TMA, MMA, eight epilogue warps of 64 columns): up to 168 registers per thread.  A
+// sixteen-warp epilogue would be 18 warps, allocated like 20 (groups of four): 96 per thread.
 template <bool DOTS>
 __global__ void __launch_bounds__(kMmqThreads, 1)
 q8_mmq_kernel(const __grid_constant__ CUtensorMap weights_map,

@@ -435,9 +435,10 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     cluster_sync_all();         // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = sh->tmem_base;
-    // everything above may run under the prepare kernel; the activation image and the
-    // zeroed split tiles are that kernel's output
-    grid_dependency_wait();
+    // Everything above may run under the prepare kernel.  What that kernel writes - the
+    // activation image, the token scales, the zeroed split tiles - is touched by the TMA
+    // producers' activation loads and by the drain only: those wait for it where they start.
+    // The first weight load and its conversion do not (weights are nobody's output).
 
     if (warp < kPfFrontWarps) {
         if (warp < 4) regs_release<kPfProducerRegs>();
@@ -452,6 +453,7 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                 const int producer = warp == 0 ? 0 : 1;
                 bool ok = true;
                 int chunks = 0;         // raw weight loads armed so far
+                bool image_ready = false;
                 PfWalk walk;
                 pf_walk_begin(walk, p.tiles, p.blocks, pairs, pair);
                 int kb = walk.kb, left = walk.count;
@@ -482,6 +484,10 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
                         if (producer == 0) PF_STAMP(0, armed >> 1, 0);
                         if (use > 0) ok = pf_wait(empty_bar + 8 * s, (use - 1) & 1);
                         if (!ok) break;
+                        if (!image_ready) {
+                            grid_dependency_wait();
+                            image_ready = true;
+                        }
                         mbar_arrive_expect_tx(&sh->full[s], kStageTx);
                         tma_load_2d(smem + s * kStageBytes + kPfW16Bytes, &act_map, kb * 64,
                             token0, &sh->full[s]);
@@ -696,6 +702,7 @@ q8_prefill_kernel(const __grid_constant__ CUtensorMap weights_map,
     } else {
         // ------------------------------ drain ------------------------------------------
         regs_claim<kPfEpilogueRegs>();
+        grid_dependency_wait();     // token scales and zeroed split tiles
         const int ew = warp - kPfFrontWarps;
         const int et = threadIdx.x - kPfFrontWarps * 32;    // 0 .. 511
         const int quadrant = warp & 3;              // TMEM lanes this warp may touch

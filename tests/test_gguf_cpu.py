@@ -125,6 +125,10 @@ def test_bad_tensor_entries(tmp_path):
         ([("t", 2, [32, 2], b"\0" * 36)], 2, "GGUF tensor quantization is not supported"),
         ([("t", 0, [2, 2, 2, 2, 2], b"\0" * 128)], 1, "invalid GGUF tensor rank"),
         ([("t", 0, [], b"")], 1, "invalid GGUF tensor rank"),
+        # shapes whose element or byte count wraps 64 bits must not pass the range check
+        ([("t", 8, [32, 2 ** 59 + 1], b"\0" * 68)], 1, "GGUF tensor shape overflows"),
+        ([("t", 0, [2 ** 31, 2 ** 31, 2 ** 31, 4], b"\0" * 64)], 1, "GGUF tensor shape overflows"),
+        ([("t", 0, [2 ** 61, 2], b"\0" * 64)], 1, "GGUF tensor shape overflows"),
     ]
     for index, (tensors, code, text) in enumerate(cases):
         path = str(tmp_path / f"bad{index}.gguf")
@@ -140,6 +144,13 @@ def test_bad_tensor_entries(tmp_path):
     assert (stat.code, stat.message) == (3, "could not read GGUF tensor data")
     stat = f.open(str(tmp_path / "missing.gguf"))
     assert (stat.code, stat.message) == (3, "could not open GGUF model")
+    # an alignment that is no power of two, or absurdly large, is refused
+    for index, value in enumerate((48, 2 ** 30)):
+        path = str(tmp_path / f"align{index}.gguf")
+        gw.write_gguf(path, [("general.alignment", gw.U32, value)],
+                      [("t", 0, [4], np.zeros(4, np.float32).tobytes())])
+        stat = f.open(path)
+        assert (stat.code, stat.message) == (1, "invalid GGUF alignment")
 
 
 def test_null_handles_are_harmless():
