@@ -93,7 +93,8 @@ def test_few_tokens_agree_with_the_batch1_kernel(backend, context, dev, oracle):
     assert np.abs(out[5] - single).max() <= l2_tolerance(single)
 
 
-@pytest.mark.parametrize("tokens,hidden,inner", [(8, 1024, 3840), (3, 256, 512), (40, 512, 1024)])
+@pytest.mark.parametrize("tokens,hidden,inner", [(8, 1024, 3840), (3, 256, 512), (40, 512, 1024),
+                                                 (8, 5120, 17408)])   # the last: 27B class, batch 8
 def test_batched_ffn_equals_the_single_token_ffn(backend, context, dev, oracle, tokens, hidden,
                                                  inner):
     gate = oracle.make_weights(inner, hidden, seed=1)
@@ -108,7 +109,10 @@ def test_batched_ffn_equals_the_single_token_ffn(backend, context, dev, oracle, 
     assert stat.is_ok(), stat
     got = dev.floats(dout, tokens * hidden).reshape(tokens, hidden)
     flipped = 0
-    for t in range(tokens):
+    # (the 27B-class case checks its first and last token: the comparison itself is a
+    # 5120 x 17408 float64 projection per token)
+    checked = range(tokens) if inner < 10000 else (0, tokens - 1)
+    for t in checked:
         expected = oracle.ffn(gate, up, down, inner, hidden, hidden, x[t])
         # the hidden vector is re-quantized between the halves: what is left of the error
         # after removing single-step quant flips must meet the single-token FFN's bound
@@ -116,7 +120,7 @@ def test_batched_ffn_equals_the_single_token_ffn(backend, context, dev, oracle, 
                                                             down, inner, hidden, x[t])
         assert largest <= 1 and left <= 2 * l2_tolerance(expected), (t, count, largest, left)
         flipped += count
-    assert flipped <= max(2, tokens * inner // 2000), flipped
+    assert flipped <= max(2, len(checked) * inner // 2000), flipped
     # the shape rule of the single-token entry point, and the output size
     assert not backend.cuda_q8_ffn_batch_device(context, wg, wu, wg, dx, tokens, dout,
                                                 tokens * hidden).is_ok()
