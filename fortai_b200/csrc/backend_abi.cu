@@ -63,7 +63,7 @@ struct fortai_cuda_q8_context {
     int gemv_split = 0;        // slice kernel: 0 automatic, 1 off, 4 or 8 warps per row
     int gemv_balance = 0;      // 1 = trim the grid so that the last round of rows is full
     int peer_wait_clocks_millions = 2000;   // fused all-gather: wait for a peer's flag, in 1e6 SM clocks
-    int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 33)
+    int mmq_min_tokens = 0;    // first token count of the tcgen05 kernel (0 = 65)
     int prefill_kind = 0;      // tcgen05 kernel: 0 = kind::f16, activation scale folded into the operand; 1 = kind::i8, scaled per block
     int fewtok_splits = 0;     // K ranges of the few-token kernel (0 = as few as fit)
     int fewtok_threads = 0;    // its CTA size (0 = 256)
@@ -2027,7 +2027,7 @@ cudaError_t launch_fewtok(fortai_cuda_q8_context *c, const FewTokParams &p, cons
     }
 }
 
-// 2..32 tokens: activation image, zeroed output, one pass over the weights.
+// 2..64 tokens: activation image, zeroed output, one pass over the weights.
 cudaError_t enqueue_fewtok(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
     const void *activation, int act, int tokens, float *output, int32_t *block_dots) {
     const int padded = fewtok_padded_tokens(tokens);
@@ -2080,11 +2080,12 @@ cudaError_t enqueue_fewtok(fortai_cuda_q8_context *c, const fortai_cuda_q8_weigh
     const bool dots = block_dots != nullptr;
     if (padded == 8) return launch_fewtok<1>(c, p, plan, dots);
     if (padded == 16) return launch_fewtok<2>(c, p, plan, dots);
-    return launch_fewtok<4>(c, p, plan, dots);
+    if (padded == 32) return launch_fewtok<4>(c, p, plan, dots);
+    return launch_fewtok<8>(c, p, plan, dots);
 }
 
-// Batched product, any token count: the tcgen05 kernel above 32 tokens, the few-token
-// kernel below that (in groups of up to 32 where the tcgen05 kernel does not take the
+// Batched product, any token count: the tcgen05 kernel above 64 tokens, the few-token
+// kernel below that (in groups of up to 64 where the tcgen05 kernel does not take the
 // width), one GEMV per token as the last resort.  Exactly one of output / block_dots.
 cudaError_t enqueue_matmul(fortai_cuda_q8_context *c, const fortai_cuda_q8_weights *w,
     const void *activation, int act, int tokens, float *output, int32_t *block_dots) {

@@ -1,4 +1,4 @@
-// Q8_0 product for a few tokens at a time (2..32): batched decode, speculative decoding,
+// Q8_0 product for a few tokens at a time (2..64): batched decode, speculative decoding,
 // the small end of prefill.  The reference has no such form (it runs one GEMV per token,
 // backend/cuda/fortai_cuda_backend.cu:64-147); semantics are those of its matvec applied
 // to every token: exact int32 block dots, fmaf((dw * da), float(dot), acc) per block.
@@ -8,8 +8,9 @@
 // eight or more tokens would make the kernel ALU-bound.  So the dots go to the tensor
 // cores through warp-level mma.sync.m16n8k32 (int8 x int8 -> int32; one Q8_0 block is
 // exactly K = 32), which leaves the CUDA cores one convert and one FMA per (row, token,
-// block).  The tcgen05 kernel takes over above 32 tokens; below that its 128-token tile
-// would be mostly padding.
+// block).  The tcgen05 kernel takes over above 64 tokens (measured on 9728 x 2560 at 64 tokens:
+// 22.6 us here against 30.8 us there, whose four MMAs per block take the same 512 cycles for 64
+// token columns as for 256).
 //
 // Mapping.  A warp step is a tile of 16 weight rows x CB bytes (CB = 512: 16 blocks).  The
 // warp copies it global -> shared with 16-byte cp.async, one instruction per row, so every
@@ -40,7 +41,7 @@
 
 namespace fortai_b200 {
 
-constexpr int kFewTokMaxTokens = 32;
+constexpr int kFewTokMaxTokens = 64;
 constexpr int kFewTokMaxWarps = 16;
 
 struct FewTokParams {
@@ -60,7 +61,7 @@ inline bool fewtok_supported(int rows, int width, int tokens) {
 }
 
 inline int fewtok_padded_tokens(int tokens) {
-    return tokens <= 8 ? 8 : tokens <= 16 ? 16 : 32;
+    return tokens <= 8 ? 8 : tokens <= 16 ? 16 : tokens <= 32 ? 32 : 64;
 }
 
 // Bytes between two tokens of the shared-memory image.  A half-warp reads 32 contiguous

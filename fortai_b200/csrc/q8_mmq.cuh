@@ -99,7 +99,7 @@ inline size_t mmq_scratch_bytes(int width, int tokens) {
 }
 
 inline bool mmq_supported(int rows, int width, int tokens, int min_tokens) {
-    const int threshold = min_tokens > 0 ? min_tokens : 33;
+    const int threshold = min_tokens > 0 ? min_tokens : 65;
     return tokens >= threshold && width % (kMmqStageBlocks * kBlockElems) == 0 && rows >= 1;
 }
 

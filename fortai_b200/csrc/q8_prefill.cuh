@@ -109,7 +109,7 @@ inline size_t pf_scratch_bytes(int width, int tokens) {
 }
 
 inline bool pf_supported(int rows, int width, int tokens, int min_tokens) {
-    const int threshold = min_tokens > 0 ? min_tokens : 33;
+    const int threshold = min_tokens > 0 ? min_tokens : 65;
     return tokens >= threshold && width % kBlockElems == 0 && width <= 65536 && rows >= 1;
 }
 

@@ -205,7 +205,7 @@ int fortai_cuda_q8_context_synchronize(fortai_cuda_q8_context *context);
  * "gemv_depth", "gemv_balance", "host_flush_rows" and "peer_flush_rows" (rows per store group
  * of a GEMV that writes a page-locked host vector / peers' vectors: a power of two up to 32),
  * "gemv_rows_per_warp", "mmq_min_tokens" (first token count that
- * goes to the tcgen05 prefill kernel, default 33), "prefill_kind" (0 = kind::f16 MMAs with the
+ * goes to the tcgen05 prefill kernel, default 65: up to 64 tokens the few-token kernel is faster), "prefill_kind" (0 = kind::f16 MMAs with the
  * activation scale folded into the operand, the default; 1 = kind::i8 MMAs scaled per block on
  * the CUDA cores, the kernel that also serves the block-dot probe), "peer_wait_clocks_millions".
  * Zero means automatic.  Unknown names return INVALID. */
@@ -253,7 +253,7 @@ int fortai_cuda_q8_matvec_host_f32(fortai_cuda_q8_context *context,
 
 /* Batched product (batched decode, speculative decoding, prefill): `tokens` rows of
  * `width` floats in, tokens x rows floats out (token-major: out[t * rows + r]).  Each
- * token row is quantized to Q8_0 exactly as a single activation would be.  2..32 tokens
+ * token row is quantized to Q8_0 exactly as a single activation would be.  2..64 tokens
  * stream the weights once through a warp-level int8 MMA kernel, more go to the tcgen05
  * kernel; the reference runs one GEMV per token.  Enqueue only. */
 int fortai_cuda_q8_matmul_device_f32(fortai_cuda_q8_context *context,

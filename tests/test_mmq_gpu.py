@@ -19,10 +19,12 @@ def check_rows(actual, expected):
         assert err <= l2_tolerance(expected[t]), (t, err, l2_tolerance(expected[t]))
 
 
-@pytest.mark.parametrize("tokens", [16, 64, 128, 512])
-def test_prefill_config_shapes(backend, context, dev, oracle, tokens):
-    """The prefill configuration: M in {16, 64, 128, 512} x K=2560 x N=9728."""
+@pytest.mark.parametrize("tokens,tensor_from", [(16, 0), (64, 0), (64, 33), (128, 0), (512, 0)])
+def test_prefill_config_shapes(backend, context, dev, oracle, tokens, tensor_from):
+    """The prefill configuration: M in {16, 64, 128, 512} x K=2560 x N=9728; 64 tokens through
+    the few-token kernel (the default up to 64) and through the tcgen05 kernel's 64-token tile."""
     rows, width = 9728, 2560
+    context.set_option("mmq_min_tokens", tensor_from)
     weights = oracle.make_weights(rows, width, seed=2)
     x = oracle.normal(tokens * width, seed=3).reshape(tokens, width)
     expected = oracle.matmul(weights, rows, width, x)[0]
