@@ -327,7 +327,7 @@ def run_gpu_arm(args):
     # epilogue can store this rank's slice straight into every rank's copy.
     peer_ptrs, symm_handle, flag_ptrs = None, None, None
     logits = None
-    if world > 1 and args.exchange in ("auto", "peers", "fused"):
+    if world > 1 and args.exchange in ("auto", "peers", "fused", "pairs"):
         try:
             import torch.distributed._symmetric_memory as symm
             logits = symm.empty(ROWS, dtype=torch.float32, device=torch.device("cuda", local_rank))
@@ -337,10 +337,14 @@ def run_gpu_arm(args):
             flags.zero_()
             flag_handle = symm.rendezvous(flags, dist.group.WORLD)
             flag_ptrs = backend.pointer_array([int(p) for p in flag_handle.buffer_ptrs])
+            pair_buffer = symm.empty(4 * ROWS, dtype=torch.int32, device=torch.device("cuda", local_rank))
+            pair_buffer.zero_()
+            pair_handle = symm.rendezvous(pair_buffer, dist.group.WORLD)
+            pair_ptrs = backend.pointer_array([int(p) for p in pair_handle.buffer_ptrs])
             torch.cuda.synchronize()
             dist.barrier()
         except Exception as error:  # no peer access on this box: fall back to NCCL
-            if args.exchange in ("peers", "fused"):
+            if args.exchange in ("peers", "fused", "pairs"):
                 raise SystemExit(f"symmetric memory unavailable: {error}")
             peer_ptrs, symm_handle, logits = None, None, None
     if logits is None:
@@ -368,6 +372,13 @@ def run_gpu_arm(args):
                                                            ROWS)
         if not stat.is_ok():
             raise RuntimeError(f"all-gather matvec failed: {stat}")
+
+    def step_pairs(x=x):
+        stat = backend.cuda_q8_matvec_device_f32_allgather_ll(ctx, next_weights(), x.data_ptr(),
+                                                              WIDTH, pair_ptrs, rank, first_row,
+                                                              logits.data_ptr(), ROWS)
+        if not stat.is_ok():
+            raise RuntimeError(f"all-gather matvec (pairs) failed: {stat}")
 
     def time_steps(fn, n):
         for _ in range(5):
@@ -422,13 +433,14 @@ def run_gpu_arm(args):
         if peer_ptrs is not None:
             candidates["peers"] = step_peers
             candidates["fused"] = step_fused
+            candidates["pairs"] = step_pairs
         for name, fn in candidates.items():
             exchange_verified[name] = verify(fn)
             exchange_ms[name] = time_steps(fn, 200)
         eligible = {k: v for k, v in exchange_ms.items() if exchange_verified[k]}
         if not eligible:
             raise SystemExit(f"no exchange mode reproduced the gathered logits: {exchange_verified}")
-        if args.exchange in ("peers", "fused") and args.exchange in eligible:
+        if args.exchange in ("peers", "fused", "pairs") and args.exchange in eligible:
             exchange = args.exchange
         else:
             exchange = min(eligible, key=eligible.get)
@@ -973,18 +985,14 @@ def run_ffn(args):
         try:
             import torch.distributed._symmetric_memory as symm
             device = torch.device("cuda", local_rank)
-            slots = symm.empty(2 * world * hidden, dtype=torch.float32, device=device)
-            slots.zero_()
-            slot_handle = symm.rendezvous(slots, dist.group.WORLD)
-            flags = symm.empty(world, dtype=torch.int32, device=device)
-            flags.zero_()
-            flag_handle = symm.rendezvous(flags, dist.group.WORLD)
-            keep += [slots, slot_handle, flags, flag_handle]
+            pairs = symm.empty(4 * world * hidden, dtype=torch.int32, device=device)
+            pairs.zero_()
+            pair_handle = symm.rendezvous(pairs, dist.group.WORLD)
+            keep += [pairs, pair_handle]
             torch.cuda.synchronize()
             dist.barrier()
             for one in ffns:
-                one.attach([int(p) for p in slot_handle.buffer_ptrs],
-                           [int(p) for p in flag_handle.buffer_ptrs])
+                one.attach([int(p) for p in pair_handle.buffer_ptrs])
             fused_out = torch.empty(hidden, device="cuda", dtype=torch.float32)
             fused_ms = timed(lambda: ffn.forward_fused(x, fused_out), steps)
             stat = ctx.synchronize()
@@ -1221,7 +1229,7 @@ def main():
     parser.add_argument("--steps", type=int, default=20000)
     parser.add_argument("--warmup", type=int, default=200)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    parser.add_argument("--exchange", default="auto", choices=["auto", "allgather", "peers", "fused"],
+    parser.add_argument("--exchange", default="auto", choices=["auto", "allgather", "peers", "fused", "pairs"],
                         help="how row shards are reassembled when --gpus > 1")
     parser.add_argument("--rows", type=int, default=ROWS,
                         help="row count of the GEMV (smaller cases are for profiler captures)")

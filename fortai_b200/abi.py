@@ -85,7 +85,9 @@ SIGNATURES = {
                                                        c_size_t, c_size_t]),
     "fortai_cuda_q8_matvec_device_f32_allgather": (c_int, [_P, _P, _P, c_size_t, _PP, _PP, c_int,
                                                            c_int, c_size_t, c_size_t]),
-    "fortai_cuda_q8_ffn_device_allreduce": (c_int, [_P, _P, _P, _P, _P, c_size_t, _PP, _PP, c_int,
+    "fortai_cuda_q8_matvec_device_f32_allgather_ll": (c_int, [_P, _P, _P, c_size_t, _PP, c_int, c_int,
+                                                              c_size_t, _P, c_size_t]),
+    "fortai_cuda_q8_ffn_device_allreduce": (c_int, [_P, _P, _P, _P, _P, c_size_t, _PP, c_int,
                                                     c_int, _P, c_size_t]),
     "fortai_cuda_q8_ffn_device_noalloc": (c_int, [_P, _P, _P, _P, _P, c_size_t, _P, c_size_t]),
     "fortai_cuda_q8_ffn_batch_device": (c_int, [_P, _P, _P, _P, _P, c_int, _P, c_size_t]),

@@ -704,23 +704,41 @@ def cuda_q8_matvec_device_f32_allgather(context, weights, device_activation, act
     return stat
 
 
+def cuda_q8_matvec_device_f32_allgather_ll(context, weights, device_activation,
+                                           activation_elements, peer_pairs, my_rank, first_row,
+                                           device_output, output_elements) -> status_t:
+    """Row shard + all-gather in one kernel, the data carrying its own flag: results travel as
+    (value, call number) pairs into every rank's pair array and are collected into
+    `device_output` (output_elements floats on this rank)."""
+    stat = status_t()
+    if (not context.handle or not weights.handle or not device_activation or not peer_pairs or
+            not device_output):
+        stat.set(FORTAI_INVALID, "invalid CUDA Q8 all-gather matvec (pairs)")
+        return stat
+    pairs = pointer_array(peer_pairs)
+    code = _lib().fortai_cuda_q8_matvec_device_f32_allgather_ll(
+        context.handle, weights.handle, device_activation, activation_elements, pairs,
+        len(peer_pairs), int(my_rank), int(first_row), device_output, int(output_elements))
+    if code != FORTAI_CUDA_OK:
+        return _failed(stat, context, "CUDA Q8 all-gather matvec (pairs) failed")
+    return stat
+
+
 def cuda_q8_ffn_device_allreduce(context, gate, up, down, device_activation, activation_elements,
-                                 peer_slots, peer_flags, my_rank, device_output,
-                                 output_elements) -> status_t:
+                                 peer_pairs, my_rank, device_output, output_elements) -> status_t:
     """Sharded FFN with the sum over ranks inside the call: the down GEMV stores this rank's
-    partial vector into every rank's slot array, exchanges flags, and the slots are added in
-    rank order.  peer_slots[p]: 2 * world * hidden floats in rank p's memory."""
+    partial vector as (value, call number) pairs into every rank's pair array and adds the
+    slots in rank order as they arrive.  peer_pairs[p]: 2 * world * hidden pairs of 8 bytes in
+    rank p's memory, zeroed once."""
     stat = status_t()
     if (not context.handle or not gate.handle or not up.handle or not down.handle or
-            not device_activation or not device_output or not peer_slots or
-            len(peer_slots) != len(peer_flags)):
+            not device_activation or not device_output or not peer_pairs):
         stat.set(FORTAI_INVALID, "invalid CUDA Q8 all-reduce FFN")
         return stat
-    slots = pointer_array(peer_slots)
-    flags = pointer_array(peer_flags)
+    pairs = pointer_array(peer_pairs)
     code = _lib().fortai_cuda_q8_ffn_device_allreduce(
         context.handle, gate.handle, up.handle, down.handle, device_activation,
-        int(activation_elements), slots, flags, len(peer_slots), int(my_rank), device_output,
+        int(activation_elements), pairs, len(peer_pairs), int(my_rank), device_output,
         int(output_elements))
     if code != FORTAI_CUDA_OK:
         return _failed(stat, context, "CUDA Q8 all-reduce FFN failed")

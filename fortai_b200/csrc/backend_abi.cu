@@ -45,6 +45,8 @@ struct fortai_cuda_q8_context {
     unsigned allgather_sequence = 0;   // fused all-gather launches so far (wraps)
     unsigned host_sequence = 0;        // host-call completions so far (wraps)
     unsigned ffn_exchange_calls = 0;   // all-reduce FFN calls so far (slot parity)
+    unsigned ll_calls = 0;             // pair all-gather calls so far (half of the pair arrays)
+    unsigned ll_sequence = 0;          // their call number (never zero)
     int *status_host = nullptr;              // pinned + mapped: kernels write, host reads
     int *status_device = nullptr;
     unsigned *done_host = nullptr;           // pinned + mapped: completion word of host calls
@@ -755,29 +757,27 @@ struct Glue {
 };
 
 // A column-sharded down projection whose ranks exchange their partial output vectors inside
-// the GEMV: rank r's partial goes to slot r of every rank's slot array, then the flag
-// exchange of the fused all-gather.
+// the GEMV: rank r's partial travels as (value, call number) pairs into slot r of every rank's
+// pair array, and the kernel's tail adds the slots in rank order into the output.
 struct FfnExchange {
-    float *slots[kMaxPeers] = {};      // every rank's slot array (peers x hidden floats)
-    unsigned *flags[kMaxPeers] = {};
+    float *pairs[kMaxPeers] = {};      // every rank's pair array, at the half this call uses
     int peers = 0;
     int rank = 0;
+    float *output = nullptr;           // this rank's sum
 };
 
 void attach_exchange(fortai_cuda_q8_context *c, GemvParams *d, const FfnExchange &x, int hidden) {
-    for (int i = 0; i < x.peers; ++i) {
-        d->peer_outputs[i] = x.slots[i];
-        d->peer_flags[i] = x.flags[i];
-    }
+    for (int i = 0; i < x.peers; ++i) d->peer_outputs[i] = x.pairs[i];
     d->outputs[0] = nullptr;
     d->peers = x.peers;
     d->peer_flush = c->peer_flush_rows;
     d->first_row = x.rank * hidden;
-    d->my_flags = x.flags[x.rank];
-    d->cta_counter = c->cta_counter;
     d->my_rank = x.rank;
-    d->sequence = ++c->allgather_sequence;
-    d->exchange = c->peer_publish_per_cta ? kExchangeCounters : kExchangeLastCta;
+    if (++c->ll_sequence == 0) ++c->ll_sequence;
+    d->ll_sequence = c->ll_sequence;
+    d->ll_output = x.output;
+    d->ll_total = hidden;
+    d->ll_reduce = x.peers;
     d->flag_wait_clocks = static_cast<long long>(c->peer_wait_clocks_millions) * 1000000LL;
     d->overlap_ok = c->peer_overlap;
 }
@@ -1234,49 +1234,44 @@ extern "C" int fortai_cuda_q8_ffn_device(fortai_cuda_q8_context *context,
 extern "C" int fortai_cuda_q8_ffn_device_allreduce(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
     const fortai_cuda_q8_weights *down_weights, const void *device_activation,
-    size_t activation_elements, void *const *peer_slots, void *const *peer_flags, int peer_count,
-    int my_rank, void *device_output, size_t output_elements) {
+    size_t activation_elements, void *const *peer_pairs, int peer_count, int my_rank,
+    void *device_output, size_t output_elements) {
     if (!context || !gate_weights || !up_weights || !down_weights || !device_activation ||
-        !device_output || !peer_slots || !peer_flags || peer_count <= 0 ||
-        peer_count > kMaxPeers || my_rank < 0 || my_rank >= peer_count)
+        !device_output || !peer_pairs || peer_count <= 0 || peer_count > kMaxPeers ||
+        my_rank < 0 || my_rank >= peer_count)
         return FORTAI_CUDA_INVALID;
     if (!ffn_shapes_ok(context, gate_weights, up_weights, down_weights) ||
         activation_elements != static_cast<size_t>(gate_weights->blocks) * kBlockElems ||
         output_elements < static_cast<size_t>(down_weights->rows)) return FORTAI_CUDA_INVALID;
     for (int i = 0; i < peer_count; ++i)
-        if (!peer_slots[i] || !peer_flags[i]) return FORTAI_CUDA_INVALID;
+        if (!peer_pairs[i] || reinterpret_cast<uintptr_t>(peer_pairs[i]) % 8 != 0)
+            return FORTAI_CUDA_INVALID;
     cudaSetDevice(context->device);
     cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(context->stream, &capture) == cudaSuccess &&
         capture != cudaStreamCaptureStatusNone) {
-        // (the slot parity below is a host counter, whichever flag protocol is in use)
         fail(context, "all-reduce FFN cannot be captured into a CUDA graph "
-                      "(its slot parity is a launch argument)");
+                      "(its call number is a launch argument)");
         return FORTAI_CUDA_INVALID;
     }
     const int hidden = down_weights->rows;
-    // two sets of slots, used alternately: a rank that runs ahead stores call n+1's partial
-    // while a peer may still be summing call n's; it cannot reach call n+2 before that peer
-    // has raised its flag for call n+1, which comes after its sum of call n in stream order
-    const size_t parity_offset = static_cast<size_t>(context->ffn_exchange_calls++ & 1u) *
-        peer_count * hidden;
+    // two halves of the pair arrays, used alternately: a rank that runs ahead stores call
+    // n+1's partial while a peer may still be adding call n's; it cannot reach call n+2 before
+    // that peer has sent its own partial of call n+1, which it does after adding call n
+    const size_t half = static_cast<size_t>(context->ffn_exchange_calls++ & 1u) * peer_count *
+        hidden;
     FfnExchange exchange;
-    for (int i = 0; i < peer_count; ++i) {
-        exchange.slots[i] = static_cast<float *>(peer_slots[i]) + parity_offset;
-        exchange.flags[i] = static_cast<unsigned *>(peer_flags[i]);
-    }
+    for (int i = 0; i < peer_count; ++i)
+        exchange.pairs[i] = reinterpret_cast<float *>(static_cast<uint2 *>(peer_pairs[i]) + half);
     exchange.peers = peer_count;
     exchange.rank = my_rank;
+    exchange.output = static_cast<float *>(device_output);
     cudaError_t error = ensure_scratch(context,
         static_cast<size_t>(down_weights->blocks) * kBlockBytes,
         static_cast<size_t>(gate_weights->rows) * sizeof(float));
     if (error == cudaSuccess)
         error = enqueue_ffn(context, gate_weights, up_weights, down_weights, device_activation,
             kActF32, nullptr, Glue(), &exchange);
-    if (error == cudaSuccess)
-        error = launch_overlapped(context, q8_sum_slots_kernel, (hidden + 255) / 256, 256, 0,
-            static_cast<const float *>(exchange.slots[my_rank]), peer_count, hidden,
-            static_cast<const float *>(nullptr), static_cast<float *>(device_output));
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-reduce FFN", error);
 }
 
@@ -1956,6 +1951,49 @@ extern "C" int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context
     p.overlap_ok = context->peer_overlap;
     const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
     return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-gather matvec", error);
+}
+
+extern "C" int fortai_cuda_q8_matvec_device_f32_allgather_ll(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_pairs, int peer_count, int my_rank,
+    size_t first_row, void *device_output, size_t output_elements) {
+    if (!owned(context, weights) || !device_activation || !peer_pairs || !device_output ||
+        peer_count <= 0 || peer_count > kMaxPeers || my_rank < 0 || my_rank >= peer_count ||
+        activation_elements != static_cast<size_t>(weights->blocks) * kBlockElems ||
+        first_row + static_cast<size_t>(weights->rows) > output_elements ||
+        output_elements > static_cast<size_t>(INT32_MAX)) return FORTAI_CUDA_INVALID;
+    for (int i = 0; i < peer_count; ++i)
+        if (!peer_pairs[i] || reinterpret_cast<uintptr_t>(peer_pairs[i]) % 8 != 0)
+            return FORTAI_CUDA_INVALID;
+    cudaSetDevice(context->device);
+    // the call's number and the half of the pair arrays it uses are launch arguments taken
+    // from host counters: a captured launch would replay them
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(context->stream, &capture) == cudaSuccess &&
+        capture != cudaStreamCaptureStatusNone) {
+        fail(context, "all-gather matvec (pairs) cannot be captured into a CUDA graph "
+                      "(its call number is a launch argument)");
+        return FORTAI_CUDA_INVALID;
+    }
+    GemvParams p = single_params(context, weights, device_activation, nullptr);
+    // two halves used alternately: a rank that runs ahead writes call n+1's pairs while a
+    // peer may still collect call n's; it cannot reach call n+2 before that peer has sent its
+    // own pairs of call n+1, which it does after collecting call n
+    const size_t half = static_cast<size_t>(context->ll_calls++ & 1u) * output_elements;
+    for (int i = 0; i < peer_count; ++i)
+        p.peer_outputs[i] = reinterpret_cast<float *>(static_cast<uint2 *>(peer_pairs[i]) + half);
+    p.peers = peer_count;
+    p.peer_flush = context->peer_flush_rows;
+    p.first_row = static_cast<int>(first_row);
+    p.my_rank = my_rank;
+    if (++context->ll_sequence == 0) ++context->ll_sequence;   // zero is "nothing has arrived"
+    p.ll_sequence = context->ll_sequence;
+    p.ll_output = static_cast<float *>(device_output);
+    p.ll_total = static_cast<int>(output_elements);
+    p.flag_wait_clocks = static_cast<long long>(context->peer_wait_clocks_millions) * 1000000LL;
+    p.overlap_ok = context->peer_overlap;
+    const cudaError_t error = launch_gemv(context, p, kActF32, kEpiPeers);
+    return error == cudaSuccess ? FORTAI_CUDA_OK : fail(context, "all-gather matvec (pairs)", error);
 }
 
 // ---------------------------------------------------------------------------

@@ -83,6 +83,14 @@ struct GemvParams {
     int my_rank;
     long long flag_wait_clocks;        // how long the tail waits for a peer's flag (SM clocks)
     int overlap_ok;                    // the only "peer" is this process: dependent launch allowed
+    // all-gather without flags (ll_sequence != 0): peer_outputs[p] is rank p's array of
+    // (value, call number) pairs, ll_output this rank's plain vector of ll_total floats
+    unsigned ll_sequence;
+    float *ll_output;
+    int ll_total;
+    // ll_reduce > 0: the pair arrays hold ll_reduce slots of ll_total pairs, slot r filled by
+    // rank r (this rank's own slot too); the tail adds the slots in order into ll_output
+    int ll_reduce;
     // peer outputs of the pipelined kernel: a warp stores its results every `peer_flush`
     // finished rows (a power of two up to 32; 0 = 32).  32 rows make one 128-byte line per
     // store (NVLink peers); 8 keep a slow link (a page-locked host vector behind PCIe) busy
@@ -203,6 +211,77 @@ __device__ __forceinline__ void peer_allgather_tail(const GemvParams &p) {
     }
     if (threadIdx.x == 0) *p.cta_counter = 0;         // ready for the next launch in the stream
     if (threadIdx.x < p.peers) peer_wait_word(p, p.my_flags + threadIdx.x, p.sequence);
+}
+
+// All-gather in which the data carries its own flag (the scheme of NCCL's low-latency
+// protocol): a result travels as one aligned 8-byte store of (value bits, call number), which
+// arrives whole, so the sender needs no fence and raises no flag, and the receiver knows a
+// value has arrived when the number beside it is this call's.  After its rows every CTA helps
+// to collect: it polls the pairs of the other ranks' slices in this rank's own array (bounded:
+// a pair that does not arrive ends in a status word) and writes the values into the plain
+// output vector.  The own slice goes there directly.  After the last row the critical path is
+// one trip over the link.
+__device__ __forceinline__ void ll_store(float *pairs, int index, float value, unsigned sequence) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(
+                     reinterpret_cast<uint2 *>(pairs) + index),
+                 "r"(__float_as_uint(value)), "r"(sequence)
+                 : "memory");
+}
+
+// One result of this rank into every rank's memory: pairs for the others, the plain vector here.
+__device__ __forceinline__ void peer_store(const GemvParams &p, int index, float value) {
+    if (p.ll_sequence == 0) {
+        for (int peer = 0; peer < p.peers; ++peer) p.peer_outputs[peer][index] = value;
+        return;
+    }
+    for (int peer = 0; peer < p.peers; ++peer) {
+        if (peer == p.my_rank && p.ll_reduce == 0) p.ll_output[index] = value;
+        else ll_store(p.peer_outputs[peer], index, value, p.ll_sequence);
+    }
+}
+
+// Bounded wait for pair `index` of this rank's own array; false when it ran out.
+__device__ __forceinline__ bool ll_wait(const GemvParams &p, const uint2 *pairs, int index,
+    long long start, float *value) {
+    unsigned bits, number;
+    for (;;) {
+        asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];"
+                     : "=r"(bits), "=r"(number) : "l"(pairs + index) : "memory");
+        if (number == p.ll_sequence) break;
+        if (clock64() - start > p.flag_wait_clocks) {
+            atomicExch(p.status, kStatusPeerFlagTimeout);
+            return false;
+        }
+    }
+    *value = __uint_as_float(bits);
+    return true;
+}
+
+__device__ __forceinline__ void ll_gather_tail(const GemvParams &p) {
+    const long long start = clock64();
+    const uint2 *pairs = reinterpret_cast<const uint2 *>(p.peer_outputs[p.my_rank]);
+    if (p.ll_reduce > 0) {
+        // partial vectors: out[i] = slot 0 + slot 1 + ... in slot order, the same on every rank
+        for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.ll_total;
+             i += gridDim.x * blockDim.x) {
+            float total = 0.0f;
+            for (int slot = 0; slot < p.ll_reduce; ++slot) {
+                float value;
+                if (!ll_wait(p, pairs, slot * p.ll_total + i, start, &value)) return;
+                total = slot == 0 ? value : total + value;
+            }
+            p.ll_output[i] = total;
+        }
+        return;
+    }
+    const int own_begin = p.first_row, own_end = p.first_row + p.total_rows;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < p.ll_total;
+         i += gridDim.x * blockDim.x) {
+        if (i >= own_begin && i < own_end) continue;
+        float value;
+        if (!ll_wait(p, pairs, i, start, &value)) return;
+        p.ll_output[i] = value;
+    }
 }
 
 // Shared-memory image of the activation: `width` int8 quants, then `blocks`
@@ -432,14 +511,16 @@ q8_gemv_direct_kernel(const __grid_constant__ GemvParams p) {
                             p.conv_kernel, row, value);
                     *out[r] = value;
                 } else if (EPI == kEpiPeers) {
-                    for (int peer = 0; peer < p.peers; ++peer)
-                        p.peer_outputs[peer][p.first_row + row] = total;
+                    peer_store(p, p.first_row + row, total);
                 }
             }
         }
     }
     grid_dependents_may_launch();
-    if (EPI == kEpiPeers) peer_allgather_tail(p);
+    if (EPI == kEpiPeers) {
+        if (p.ll_sequence) ll_gather_tail(p);
+        else peer_allgather_tail(p);
+    }
 }
 
 // --------------------------------------------------------------------------
@@ -612,8 +693,7 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
             if ((done & flush_mask) == 0 || row >= row_end) {
                 const int mine = flushed + ((lane - flushed) & 31);
                 if (mine < done) {
-                    for (int peer = 0; peer < p.peers; ++peer)
-                        p.peer_outputs[peer][p.first_row + warp_first + mine] = held;
+                    peer_store(p, p.first_row + warp_first + mine, held);
                 }
                 flushed = done;
             }
@@ -641,7 +721,10 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         }
     }
     grid_dependents_may_launch();
-    if (EPI == kEpiPeers) peer_allgather_tail(p);
+    if (EPI == kEpiPeers) {
+        if (p.ll_sequence) ll_gather_tail(p);
+        else peer_allgather_tail(p);
+    }
 }
 
 // --------------------------------------------------------------------------
@@ -741,8 +824,7 @@ q8_gemv_slice_kernel(const __grid_constant__ GemvParams p) {
             for (int s = 1; s < SPLIT; ++s) total += partial[round & 1][warp + s];
             if (EPI == kEpiPeers) {
                 // few rows (a partial output vector): one word per row and peer
-                for (int peer = 0; peer < p.peers; ++peer)
-                    p.peer_outputs[peer][p.first_row + finished] = total;
+                peer_store(p, p.first_row + finished, total);
             } else {
                 p.outputs[0][finished] = p.residual ? total + p.residual[finished] : total;
             }
@@ -750,22 +832,10 @@ q8_gemv_slice_kernel(const __grid_constant__ GemvParams p) {
         ++round;
     }
     grid_dependents_may_launch();
-    if (EPI == kEpiPeers) peer_allgather_tail(p);
-}
-
-// out[i] = slots[0][i] + slots[1][i] + ... in slot order (+ residual[i]): the reduction of
-// the partial output vectors that a column-sharded projection's ranks stored into one
-// another's slot arrays, the same order on every rank.
-__global__ void __launch_bounds__(256)
-q8_sum_slots_kernel(const float *__restrict__ slots, int slot_count, int elements,
-    const float *__restrict__ residual, float *__restrict__ out) {
-    grid_dependents_may_launch();
-    grid_dependency_wait();
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= elements) return;
-    float total = slots[i];
-    for (int s = 1; s < slot_count; ++s) total += slots[static_cast<size_t>(s) * elements + i];
-    out[i] = residual ? total + residual[i] : total;
+    if (EPI == kEpiPeers) {
+        if (p.ll_sequence) ll_gather_tail(p);
+        else peer_allgather_tail(p);
+    }
 }
 
 // `count` 16-byte pieces from page-locked host memory (through its device alias) into

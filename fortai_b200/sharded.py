@@ -162,6 +162,20 @@ class PeerGatherMatvec(RowShardedMatvec):
         if not stat.is_ok():
             raise RuntimeError(f"fused all-gather matvec failed: {stat}")
 
+    def attach_pairs(self, peer_pair_ptrs: Sequence[int]):
+        """Pair arrays (2 * rows pairs of 8 bytes per rank, zeroed once) that every rank can
+        reach, for `matvec_pairs`."""
+        self.pair_ptrs = self.backend.pointer_array(list(peer_pair_ptrs))
+
+    def matvec_pairs(self, activation: "torch.Tensor", out: "torch.Tensor"):
+        """Slice + all-gather in ONE kernel without flags: results travel as (value, call
+        number) pairs and are collected into `out` (this rank's memory)."""
+        stat = self.backend.cuda_q8_matvec_device_f32_allgather_ll(
+            self.context, self.weights, activation.data_ptr(), self.width, self.pair_ptrs,
+            self.rank, self.first, out.data_ptr(), self.rows)
+        if not stat.is_ok():
+            raise RuntimeError(f"all-gather matvec (pairs) failed: {stat}")
+
     def matvec_peers(self, activation: "torch.Tensor"):
         stat = self.backend.cuda_q8_matvec_device_f32_peers(
             self.context, self.weights, activation.data_ptr(), self.width, self.peer_ptrs,
@@ -204,18 +218,17 @@ class ShardedFfn:
             raise RuntimeError(f"sharded FFN failed: {stat}")
         return all_reduce_sum(dist, out, self.world)
 
-    def attach(self, peer_slot_ptrs: Sequence[int], peer_flag_ptrs: Sequence[int]):
-        """Slot arrays (2 * world * hidden floats per rank) and flag arrays (world words per
-        rank, zeroed once) that every rank can reach, for `forward_fused`."""
-        self.slot_ptrs = self.backend.pointer_array(list(peer_slot_ptrs))
-        self.flag_ptrs = self.backend.pointer_array(list(peer_flag_ptrs))
+    def attach(self, peer_pair_ptrs: Sequence[int]):
+        """Pair arrays (2 * world * hidden pairs of 8 bytes per rank, zeroed once) that every
+        rank can reach, for `forward_fused`."""
+        self.pair_ptrs = self.backend.pointer_array(list(peer_pair_ptrs))
 
     def forward_fused(self, activation: "torch.Tensor", out: "torch.Tensor"):
         """The same result without a collective call: partial vectors are exchanged by the
         down GEMV itself and added in rank order (the same bits on every rank)."""
         stat = self.backend.cuda_q8_ffn_device_allreduce(
             self.context, self.gate, self.up, self.down, activation.data_ptr(), self.hidden,
-            self.slot_ptrs, self.flag_ptrs, self.rank, out.data_ptr(), self.hidden)
+            self.pair_ptrs, self.rank, out.data_ptr(), self.hidden)
         if not stat.is_ok():
             raise RuntimeError(f"fused sharded FFN failed: {stat}")
         return out

@@ -347,21 +347,38 @@ int fortai_cuda_q8_matvec_device_f32_allgather(fortai_cuda_q8_context *context,
     size_t activation_elements, void *const *peer_outputs, void *const *peer_flags,
     int peer_count, int my_rank, size_t first_row, size_t output_elements);
 
+/* The all-gather matvec without flags: a result travels to the other ranks as one aligned
+ * 8-byte store of (value bits, call number), which arrives whole, so the sender fences nothing
+ * and raises no flag, and the receiver knows a value by the number beside it (the scheme of
+ * low-latency collectives).  peer_pairs[p] is rank p's pair array: 2 * output_elements pairs of
+ * 8 bytes, 8-byte aligned, zeroed once, reachable from every rank; its two halves alternate
+ * between consecutive calls.  After its rows, every CTA collects the other ranks' slices from
+ * this rank's own pair array into device_output (output_elements floats, this rank's memory;
+ * the own slice is stored there directly).  Waits are bounded as in the flag form (same option,
+ * same RUNTIME_ERROR).  Every rank must make the same sequence of these calls, each on its own
+ * GPU, on pair arrays used for nothing else.  Not capturable (INVALID during capture).
+ * Measured on the lm_head: see the scaling profile.  Enqueue only. */
+int fortai_cuda_q8_matvec_device_f32_allgather_ll(fortai_cuda_q8_context *context,
+    const fortai_cuda_q8_weights *weights, const void *device_activation,
+    size_t activation_elements, void *const *peer_pairs, int peer_count, int my_rank,
+    size_t first_row, void *device_output, size_t output_elements);
+
 /* The FFN of fortai_cuda_q8_ffn_device for ranks that hold gate/up row shards and the
  * matching column shard of down, with the sum over ranks inside the call (no reference
- * counterpart: the reference is single-GPU).  peer_slots[p] is rank p's slot array of
- * 2 * peer_count * hidden floats, peer_flags[p] its flag array (peer_count words, zeroed
- * once), both reachable from every rank (peer access or symmetric memory).  The down GEMV
- * stores this rank's partial vector into slot my_rank of every rank's array (the two halves
- * of the array alternate between consecutive calls), exchanges flags as the all-gather
- * matvec does (same options, same bounded wait), and a small kernel then adds the slots in
- * rank order into device_output: every rank gets the same bits.  Every rank must make the
- * same sequence of these calls, each on its own GPU.  Not capturable.  Enqueue only. */
+ * counterpart: the reference is single-GPU).  peer_pairs[p] is rank p's pair array:
+ * 2 * peer_count * hidden pairs of 8 bytes, 8-byte aligned, zeroed once, reachable from every
+ * rank (peer access or symmetric memory), used for nothing else.  The down GEMV stores this
+ * rank's partial vector as (value bits, call number) pairs into slot my_rank of every rank's
+ * array (the two halves of the array alternate between consecutive calls), and its tail adds
+ * the slots in rank order into device_output as they arrive: no flags, no fence, no collective
+ * library, and every rank gets the same bits.  Waits are bounded as in the all-gather matvec
+ * (same option, same RUNTIME_ERROR).  Every rank must make the same sequence of pair-exchanging
+ * calls, each on its own GPU.  Not capturable.  Enqueue only. */
 int fortai_cuda_q8_ffn_device_allreduce(fortai_cuda_q8_context *context,
     const fortai_cuda_q8_weights *gate_weights, const fortai_cuda_q8_weights *up_weights,
     const fortai_cuda_q8_weights *down_weights, const void *device_activation,
-    size_t activation_elements, void *const *peer_slots, void *const *peer_flags, int peer_count,
-    int my_rank, void *device_output, size_t output_elements);
+    size_t activation_elements, void *const *peer_pairs, int peer_count, int my_rank,
+    void *device_output, size_t output_elements);
 
 /* ----------------------------------------------------------------------- *
  * Device groups: the sharded path for hosts that drive several GPUs of one box from one

@@ -77,6 +77,72 @@ def test_fused_allgather_with_a_single_rank(backend, context, dev, oracle):
     assert float(np.abs(dev.floats(out, rows) - expected).max()) <= l2_tolerance(expected)
 
 
+def test_pair_allgather_with_a_single_rank(backend, context, dev, oracle):
+    """World size 1: the own slice goes straight into the output; consecutive calls alternate
+    the halves of the pair array and carry growing call numbers."""
+    rows, width = 777, 2560
+    weights = oracle.make_weights(rows, width, seed=5)
+    w = dev.weights(weights, rows, width)
+    pairs = dev.to_device(np.zeros(4 * rows, np.int32))      # 2 halves x rows pairs of 8 bytes
+    for call in range(3):
+        x = oracle.normal(width, seed=60 + call)
+        expected = oracle.matvec(weights, rows, width, x)[0]
+        out = dev.to_device(np.zeros(rows, np.float32))
+        stat = backend.cuda_q8_matvec_device_f32_allgather_ll(context, w, dev.to_device(x), width,
+                                                              [pairs], 0, 0, out, rows)
+        assert stat.is_ok(), stat
+        assert context.synchronize().is_ok()
+        assert float(np.abs(dev.floats(out, rows) - expected).max()) <= l2_tolerance(expected)
+    # refused: unaligned pair array, rank outside the list, capture
+    assert not backend.cuda_q8_matvec_device_f32_allgather_ll(context, w, dev.to_device(x), width,
+                                                              [pairs + 4], 0, 0, out, rows).is_ok()
+    assert not backend.cuda_q8_matvec_device_f32_allgather_ll(context, w, dev.to_device(x), width,
+                                                              [pairs], 1, 0, out, rows).is_ok()
+
+
+def test_pair_allgather_collects_what_a_peer_sent_and_gives_up_on_what_it_did_not(
+        backend, context, dev, oracle):
+    """Two "ranks" on this GPU, run one after the other (their kernels do not wait for each
+    other's launch: rank 1 sends first, rank 0 then finds its pairs).  Rank 0's slice comes
+    from its own rows, rank 1's from the pairs rank 1 stored.  Then a call whose peer never
+    sends: the wait runs out, the kernel returns by itself and the next blocking call reports
+    it."""
+    rows, width = 512, 1024            # two slices of 256 rows
+    weights = oracle.make_weights(rows, width, seed=11)
+    x = oracle.normal(width, seed=12)
+    expected = oracle.matvec(weights, rows, width, x)[0]
+    half = rows // 2
+    flat = weights.view(np.int8).reshape(rows, -1)
+    w0 = dev.weights(np.ascontiguousarray(flat[:half]).reshape(-1), half, width)
+    w1 = dev.weights(np.ascontiguousarray(flat[half:]).reshape(-1), half, width)
+    pairs = [dev.to_device(np.zeros(4 * rows, np.int32)) for _ in range(2)]
+    outs = [dev.to_device(np.zeros(rows, np.float32)) for _ in range(2)]
+    dx = dev.to_device(x)
+    other = backend.cuda_q8_context_t()         # rank 1's context: its own call counters
+    assert other.create(0).is_ok()
+    w1b = backend.cuda_q8_weights_t()
+    assert w1b.upload(other, np.ascontiguousarray(flat[half:]).reshape(-1), half * (width // 32) * 34,
+                      half, width).is_ok()
+    assert other.set_option("peer_wait_clocks_millions", 5).is_ok()
+    assert context.set_option("peer_wait_clocks_millions", 5).is_ok()
+    # rank 1 sends its slice and fails to collect rank 0's (rank 0 has not run): reported
+    stat = backend.cuda_q8_matvec_device_f32_allgather_ll(other, w1b, dx, width, pairs, 1, half,
+                                                          outs[1], rows)
+    assert stat.is_ok(), stat
+    stat = other.synchronize()
+    assert not stat.is_ok() and "gave up waiting" in other.last_error()
+    # rank 0 now finds rank 1's pairs and completes
+    stat = backend.cuda_q8_matvec_device_f32_allgather_ll(context, w0, dx, width, pairs, 0, 0,
+                                                          outs[0], rows)
+    assert stat.is_ok(), stat
+    assert context.synchronize().is_ok()
+    assert float(np.abs(dev.floats(outs[0], rows) - expected).max()) <= l2_tolerance(expected)
+    # the context that reported the timeout works again
+    assert other.synchronize().is_ok()
+    w1b.destroy()
+    other.destroy()
+
+
 def test_column_shards_sum_to_the_full_ffn(backend, context, dev, oracle):
     from fortai_b200 import sharded
     hidden, inner, world = 1024, 3840, 4
@@ -196,39 +262,38 @@ def test_27b_ffn_at_its_eight_way_shard_sizes(backend, context, dev, oracle):
 
 
 def test_allreduce_ffn_with_a_single_rank(backend, context, dev, oracle):
-    """World size 1: the exchange runs against this rank's own slot and flag arrays; two
-    consecutive calls use the two halves of the slot array."""
+    """World size 1: the exchange runs against this rank's own pair array; consecutive calls use
+    its two halves."""
     hidden, inner = 1024, 3840
     gate = oracle.make_weights(inner, hidden, seed=41)
     up = oracle.make_weights(inner, hidden, seed=42)
     down = oracle.make_weights(hidden, inner, seed=43)
     wg, wu, wd = (dev.weights(m, r, c) for m, r, c in ((gate, inner, hidden), (up, inner, hidden),
                                                      (down, hidden, inner)))
-    slots = dev.to_device(np.zeros(2 * hidden, np.float32))
-    flags = dev.to_device(np.zeros(1, np.int32))
+    pairs = dev.to_device(np.zeros(4 * hidden, np.int32))       # 2 halves x 1 slot x hidden pairs
     for call in range(3):
         x = oracle.normal(hidden, seed=50 + call)
         expected = oracle.ffn(gate, up, down, inner, hidden, hidden, x)
         dout = dev.buffer(4 * hidden)
         stat = backend.cuda_q8_ffn_device_allreduce(context, wg, wu, wd, dev.to_device(x), hidden,
-                                                    [slots], [flags], 0, dout, hidden)
+                                                    [pairs], 0, dout, hidden)
         assert stat.is_ok(), stat
         assert context.synchronize().is_ok()
         plain = dev.buffer(4 * hidden)
         assert backend.cuda_q8_ffn_device(context, wg, wu, wd, dev.to_device(x), hidden, plain,
                                           hidden).is_ok()
-        assert float(np.abs(dev.floats(dout, hidden) - expected).max()) <= 2 * l2_tolerance(expected)
-        check = dev.floats(dev_slots_half(dev, slots, call & 1, hidden), hidden)
-        assert np.array_equal(check, dev.floats(dout, hidden))       # one slot: the sum is the slot
-    # refused: a rank outside the peer list, missing arrays
+        got = dev.floats(dout, hidden)
+        assert float(np.abs(got - expected).max()) <= 2 * l2_tolerance(expected)
+        assert np.array_equal(got, dev.floats(plain, hidden))    # one slot: the sum is the slot
+        # the half of the pair array this call used carries its number beside every value
+        half = dev.int32s(pairs, 4 * hidden).reshape(2, hidden, 2)[call & 1]
+        assert np.all(half[:, 1] == call + 1)
+        assert np.array_equal(half[:, 0].view(np.float32), got)
+    # refused: a rank outside the peer list, an unaligned array
     assert not backend.cuda_q8_ffn_device_allreduce(context, wg, wu, wd, dev.to_device(x), hidden,
-                                                    [slots], [flags], 1, dout, hidden).is_ok()
+                                                    [pairs], 1, dout, hidden).is_ok()
     assert not backend.cuda_q8_ffn_device_allreduce(context, wg, wu, wd, dev.to_device(x), hidden,
-                                                    [slots], [], 0, dout, hidden).is_ok()
-
-
-def dev_slots_half(dev, slots, half, hidden):
-    return slots + 4 * half * hidden
+                                                    [pairs + 4], 0, dout, hidden).is_ok()
 
 
 def _rank_main(rank, world, port, result_path):
@@ -282,6 +347,24 @@ def _rank_main(rank, world, port, result_path):
                 failures.append("fused all-gather reported a device-side timeout")
             if float(np.abs(buf.cpu().numpy() - expected).max()) > 1e-5 * float(np.linalg.norm(expected)):
                 failures.append("fused all-gather differs from the oracle")
+        # the all-gather whose data carries its own flag, three calls in a row (both halves
+        # of the pair arrays), each on another activation
+        pair_buffer = symm.empty(4 * rows, dtype=torch.int32, device=torch.device("cuda", rank))
+        pair_buffer.zero_()
+        pair_handle = symm.rendezvous(pair_buffer, dist.group.WORLD)
+        torch.cuda.synchronize()
+        dist.barrier()
+        shard.attach_pairs([int(p) for p in pair_handle.buffer_ptrs])
+        for call in range(3):
+            xc = o.normal(width, seed=30 + call)
+            want = o.matvec(weights, rows, width, xc)[0]
+            got = torch.zeros(rows, device="cuda")
+            shard.matvec_pairs(torch.from_numpy(xc).cuda(), got)
+            torch.cuda.synchronize()
+            if not ctx.synchronize().is_ok():
+                failures.append("pair all-gather reported a device-side timeout")
+            if float(np.abs(got.cpu().numpy() - want).max()) > 1e-5 * float(np.linalg.norm(want)):
+                failures.append("pair all-gather differs from the oracle")
     except Exception as error:  # symmetric memory is optional; say so rather than fail
         failures.append(f"SKIP-PEERS {type(error).__name__}: {error}")
     # FFN: rows of gate/up, columns of down, all-reduce
@@ -300,16 +383,12 @@ def _rank_main(rank, world, port, result_path):
         # the same with the partial vectors exchanged by the down GEMV itself, for both a
         # pipelined-width shard (3840 / world) and consecutive calls (slot parity)
         import torch.distributed._symmetric_memory as symm
-        slots = symm.empty(2 * world * hidden, dtype=torch.float32, device=torch.device("cuda", rank))
-        slots.zero_()
-        slot_handle = symm.rendezvous(slots, dist.group.WORLD)
-        ffn_flags = symm.empty(world, dtype=torch.int32, device=torch.device("cuda", rank))
-        ffn_flags.zero_()
-        ffn_flag_handle = symm.rendezvous(ffn_flags, dist.group.WORLD)
+        ffn_pairs = symm.empty(4 * world * hidden, dtype=torch.int32, device=torch.device("cuda", rank))
+        ffn_pairs.zero_()
+        ffn_pair_handle = symm.rendezvous(ffn_pairs, dist.group.WORLD)
         torch.cuda.synchronize()
         dist.barrier()
-        ffn.attach([int(p) for p in slot_handle.buffer_ptrs],
-                   [int(p) for p in ffn_flag_handle.buffer_ptrs])
+        ffn.attach([int(p) for p in ffn_pair_handle.buffer_ptrs])
         gathered = [torch.zeros(hidden, device="cuda") for _ in range(world)]
         for call in range(3):
             xc = o.normal(hidden, seed=20 + call)
