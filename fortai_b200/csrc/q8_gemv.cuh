@@ -620,7 +620,10 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
     // and stores them to every peer a group at a time, so that the link carries whole
     // sectors or lines, spread over the kernel's duration.
     int row, row_step, row_end, warp_first = 0;
-    if (EPI == kEpiPeers) {
+    // (pairs need no coalescing - every result is its own 8-byte store - so that form keeps
+    // the ordinary row order, which streams 1.5-2 us faster than contiguous runs)
+    const bool runs = EPI == kEpiPeers && p.ll_sequence == 0;
+    if (runs) {
         const long long warps = static_cast<long long>(gridDim.x) * kGemvWarps;
         const long long g = static_cast<long long>(blockIdx.x) * kGemvWarps + warp_in_cta;
         warp_first = static_cast<int>(g * p.total_rows / warps);
@@ -686,7 +689,7 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         float total[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) total[r] = warp_sum(partial[r]);
-        if (EPI == kEpiPeers) {
+        if (runs) {
             // every lane holds the sum (butterfly); lane i mod 32 keeps row i of the run
             const int done = finished - warp_first + 1;
             if (lane == ((done - 1) & 31)) held = total[0];
@@ -700,6 +703,8 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
         } else if (lane == 0) {
             if (EPI == kEpiSiluPair) {
                 p.outputs[0][finished] = silu_mul(total[0], total[ROWS - 1]);
+            } else if (EPI == kEpiPeers) {
+                peer_store(p, p.first_row + finished, total[0]);
             } else if (stacked) {
                 float value = total[0];
                 if (p.conv_weights && finished < p.conv_rows)
