@@ -622,8 +622,8 @@ q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
     // and stores them to every peer a group at a time, so that the link carries whole
     // sectors or lines, spread over the kernel's duration.
     int row, row_step, row_end, warp_first = 0;
-    // (Pairs with one other rank keep the ordinary row order, one 8-byte store per row: it
-    // streams 1.5-2 us faster than contiguous runs, 36.4 against 38.0 us per step on two GPUs.
+    // (Pairs with one other rank keep the ordinary row order, one 8-byte store per row:
+    // 36.4 against 38.0 us per step on two GPUs.
     // With more peers a store per row and peer is too many small packets: 24.3 against 18.0 us
     // on eight GPUs.)
     const bool runs = EPI == kEpiPeers && (p.ll_sequence == 0 || p.peers > 2);
