@@ -601,10 +601,8 @@ __device__ __forceinline__ const uint8_t *stacked_row(const GemvParams &p, int r
 // requested right after the current one has been consumed (64 registers, four
 // CTAs per SM for CPL = 5), 2 = it is requested one row earlier (register double
 // buffering, fewer resident warps).
-// (One row in flight and up to five chunks per lane fit 64 registers, four CTAs per SM: the
-// peer-output form would otherwise be given 76 and run three.)
 template <int CPL, int ACT, int EPI, int DEPTH>
-__global__ void __launch_bounds__(kGemvThreads, (DEPTH == 1 && CPL <= 5 && EPI == kEpiPeers) ? 4 : 1)
+__global__ void __launch_bounds__(kGemvThreads)
 q8_gemv_pipelined_kernel(const __grid_constant__ GemvParams p) {
     if (p.trigger_early) grid_dependents_may_launch();
     extern __shared__ __align__(16) uint8_t gemv_smem[];
